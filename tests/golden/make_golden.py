@@ -1,0 +1,113 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own functions.
+
+Run once in a container where the reference tree is mounted:
+
+    python tests/golden/make_golden.py /path/to/reference
+
+The reference's test modules cannot be imported (they import a CUDA extension that is
+not built and a module path that no longer exists), so the two pure-PyTorch functions
+are cut out of their files by AST and executed as they stand:
+
+* ``wf_embedding_torch``  from ``tests/wf_embed/wf_embed.py``
+* ``torch_attn``          from ``tests/attn/geo_attn.py``
+
+Inputs are seeded; inputs and the reference's outputs (and gradients obtained by
+autograd through the reference functions, as the reference's tests do) are stored in
+``.npz`` files which the CPU tests compare the oracle against, and the GPU tests compare
+the CUDA path against.
+"""
+import ast
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import chains  # noqa: E402
+
+
+def extract(path, name):
+    src = open(path).read()
+    tree = ast.parse(src)
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name == name:
+            ns = {"torch": torch, "math": __import__("math")}
+            exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), ns)
+            return ns[name]
+    raise KeyError(name)
+
+
+def we_cases():
+    g = torch.Generator().manual_seed(20240601)
+    cases = {}
+    # the reference test's own input style: coords = max_wl * randn, wavenumbers = randn
+    z, n, k = 2, 96, 16
+    coords = 20 * torch.randn((z, n, 3), generator=g)
+    wn = torch.randn((k,), generator=g)
+    mask = torch.zeros(z, n, dtype=torch.bool)
+    mask[0, 70:] = True
+    mask[1, 5] = True
+    mask[1, 40:44] = True
+    coords[1, 11] = coords[1, 10]  # coincident pair (d == 0 is excluded)
+    for mt in (0, 1, 3):
+        cases[f"randn_m{mt}"] = (coords, wn, mt, mask)
+    cases["randn_m2_nomask"] = (coords, wn.abs() + 0.1, 2, torch.zeros(z, n, dtype=torch.bool))
+    # chain-style inputs with the benchmark wavelength schedule
+    c, m = chains.chain_batch([160, 97], 160, seed=7)
+    cases["chain_m1"] = (torch.from_numpy(c), torch.from_numpy(chains.wavenumbers(64)), 1, torch.from_numpy(m))
+    return cases
+
+
+def attn_cases():
+    g = torch.Generator().manual_seed(20240602)
+    cases = {}
+    z, h, n, d = 2, 3, 48, 16
+    q, k, v = (torch.randn((z, h, n, d), generator=g) for _ in range(3))
+    # the reference test's own input style: collinear coords, spreads 3, betas 1, no padding
+    coords = 50 * torch.randn((z, n, 1), generator=g).expand(z, n, 3).contiguous()
+    spreads = torch.full((h,), 3.0)
+    betas = torch.full((h,), 1.0)
+    nomask = torch.zeros(z, n, dtype=torch.bool)
+    cases["collinear"] = (q, k, v, coords, spreads, betas, nomask, 0.0, 1.0)
+    c, m = chains.chain_batch([48, 29], 48, seed=11)
+    cases["chain_padded"] = (q, k, v, torch.from_numpy(c), torch.tensor([3.0, 8.0, 15.0]),
+                             torch.tensor([0.5, 1.0, 2.0]), torch.from_numpy(m), 0.001, 0.99)
+    return cases
+
+
+def main(ref_root):
+    wf_embedding_torch = extract(os.path.join(ref_root, "tests/wf_embed/wf_embed.py"), "wf_embedding_torch")
+    torch_attn = extract(os.path.join(ref_root, "tests/attn/geo_attn.py"), "torch_attn")
+    torch.set_num_threads(1)  # reductions stay in one fixed order
+
+    blob = {}
+    for name, (coords, wn, mt, mask) in we_cases().items():
+        wn_g = wn.clone().requires_grad_(True)
+        out = wf_embedding_torch(coords, wn_g, mt, 0.0, mask)
+        out.sum().backward()  # the reference test's backward check, wf_embed.py:60-68
+        blob.update({f"{name}.coords": coords.numpy(), f"{name}.wn": wn.numpy(), f"{name}.mag": np.int64(mt),
+                     f"{name}.mask": mask.numpy(), f"{name}.out": out.detach().numpy(),
+                     f"{name}.dk_sum": wn_g.grad.numpy()})
+    np.savez_compressed(os.path.join(HERE, "we_reference.npz"), **blob)
+
+    blob = {}
+    for name, (q, k, v, coords, spreads, betas, mask, lo, hi) in attn_cases().items():
+        leaves = [t.clone().requires_grad_(True) for t in (q, k, v, spreads, betas)]
+        out = torch_attn(leaves[0], leaves[1], leaves[2], coords, leaves[3], leaves[4], mask, lo, hi)
+        valid_rows = (~mask)[:, None, :, None].expand_as(out)
+        out[valid_rows].sum().backward()
+        blob.update({f"{name}.q": q.numpy(), f"{name}.k": k.numpy(), f"{name}.v": v.numpy(),
+                     f"{name}.coords": coords.numpy(), f"{name}.spreads": spreads.numpy(),
+                     f"{name}.betas": betas.numpy(), f"{name}.mask": mask.numpy(),
+                     f"{name}.min_rbf": np.float64(lo), f"{name}.max_rbf": np.float64(hi),
+                     f"{name}.out": out.detach().numpy()})
+        for nm, t in zip(("dq", "dk", "dv", "dspreads", "dbetas"), leaves):
+            blob[f"{name}.{nm}"] = t.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "geoattn_reference.npz"), **blob)
+    print("wrote", sorted(os.listdir(HERE)))
+
+
+if __name__ == "__main__":
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")

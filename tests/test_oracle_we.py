@@ -1,0 +1,90 @@
+"""The WE oracle against the reference's own function (golden vectors) and against itself."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import chains
+from oracle.we_ref import dk_analytic, dk_autograd, rel_l2, wf_embedding_ref
+
+torch.set_num_threads(max(1, min(8, os.cpu_count() or 1)))
+
+
+def _cases(golden_dir):
+    g = np.load(os.path.join(golden_dir, "we_reference.npz"))
+    for name in sorted({k.split(".")[0] for k in g.files}):
+        yield name, {x: torch.from_numpy(np.asarray(g[f"{name}.{x}"])) for x in
+                     ("coords", "wn", "mag", "mask", "out", "dk_sum")}
+
+
+def test_golden_bit_exact(golden_dir):
+    torch.set_num_threads(1)
+    n = 0
+    for name, t in _cases(golden_dir):
+        for chunk in (32, 128):
+            out = wf_embedding_ref(t["coords"], t["wn"], int(t["mag"]), t["mask"], chunk=chunk)
+            assert torch.equal(out, t["out"]), (name, chunk)
+        n += 1
+    assert n == 5
+
+
+def test_golden_dk_from_stored_sums(golden_dir):
+    # the analytic backward (stored cos/sin sums) against autograd through the reference function
+    for name, t in _cases(golden_dir):
+        out, cs, sn = wf_embedding_ref(t["coords"], t["wn"], int(t["mag"]), t["mask"], return_sums=True)
+        dk = dk_analytic(torch.ones_like(out), cs, sn)
+        assert rel_l2(t["dk_sum"], dk) < 1e-5, name
+
+
+def test_row_slices_match_full():
+    c, m = chains.chain_batch([100, 61], 100, seed=3)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    wn = torch.from_numpy(chains.wavenumbers(32))
+    full = wf_embedding_ref(c, wn, 1, m, chunk=100)
+    part = wf_embedding_ref(c, wn, 1, m, rows=(17, 83), chunk=16)
+    assert torch.equal(full[:, 17:83], part)
+
+
+def test_fp64_truth_and_autograd_dk():
+    c, m = chains.chain_batch([72, 40], 72, seed=4)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    wn = torch.from_numpy(chains.wavenumbers(16))
+    o32, cs, sn = wf_embedding_ref(c, wn, 1, m, return_sums=True)
+    o64 = wf_embedding_ref(c, wn, 1, m, dtype=torch.float64)
+    assert rel_l2(o64, o32) < 1e-5
+    g = torch.Generator().manual_seed(0)
+    d_out = torch.randn(o32.shape, generator=g)
+    assert rel_l2(dk_autograd(c, wn, d_out, 1, m), dk_analytic(d_out, cs, sn)) < 1e-5
+
+
+def test_masked_rows_and_single_token_are_zero():
+    c, m = chains.chain_batch([1, 5], 8, seed=5)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    wn = torch.from_numpy(chains.wavenumbers(8))
+    out = wf_embedding_ref(c, wn, 1, m)
+    assert torch.all(out[0] == 0)  # one valid token: no pair at all
+    assert torch.all(out[1, 5:] == 0)
+
+
+def test_rigid_motion_invariance_and_permutation_equivariance():
+    c, _ = chains.chain_batch([64], 64, seed=6)
+    c = torch.from_numpy(c).double()
+    wn = torch.from_numpy(chains.wavenumbers(16)).double()
+    q, _ = torch.linalg.qr(torch.randn(3, 3, dtype=torch.float64, generator=torch.Generator().manual_seed(1)))
+    moved = c @ q.T + torch.tensor([10.0, -3.0, 7.0], dtype=torch.float64)
+    base = wf_embedding_ref(c, wn)
+    assert rel_l2(base, wf_embedding_ref(moved, wn)) < 1e-10
+    perm = torch.randperm(64, generator=torch.Generator().manual_seed(2))
+    assert rel_l2(base[:, perm], wf_embedding_ref(c[:, perm], wn)) < 1e-10
+
+
+def test_chain_geometry():
+    rng = np.random.default_rng(0)
+    r = chains.random_walk_chain(200, rng)
+    steps = np.linalg.norm(np.diff(r, axis=0), axis=1)
+    assert np.allclose(steps, 3.8, atol=1e-9)
+    d2 = np.linalg.norm(r[2:] - r[:-2], axis=1)  # bond angle 90..120 deg -> 5.37..6.58 A
+    assert d2.min() > 5.3 and d2.max() < 6.6
+    wn = chains.wavenumbers(512)
+    assert wn.shape == (256,) and abs(wn[0] - 2 * np.pi / 3.7) < 1e-6 and wn[-1] > 2 * np.pi / 20.0
