@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""Benchmark of the Wavefunction Embedding forward on the long-sequence configuration
+(one random-walk chain, N = 16384, d_model = 512, fp32), the configuration the headline
+metric "pair.wavenumber evaluations per second" is quoted on.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 ... bench.py --gpus 8 ...
+    python bench.py --impl reference          # the reference's CPU formulation on the host cores
+
+One step = one forward over all N observers.  With G ranks the observer rows are sharded
+(coordinates replicated) and the output is reassembled with one NCCL all-gather, so the total
+work is fixed ("strong" scaling).  Rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_SEQ, D_MODEL, SEED = 16384, 512, 1004
+K_WN = D_MODEL // 2
+EVALS_PER_STEP = N_SEQ * (N_SEQ - 1) * K_WN  # observer i, source j != i, wavenumber k
+H100_PUBLISHED_EVALS_PER_S = 16384 * 16383 * 256 / 0.386  # reference README.md:34, 386 ms on an H100
+
+
+def set_sequence_length(n):
+    """Profiling aid: a shorter chain of the same kind (the headline workload is N = 16384)."""
+    global N_SEQ, EVALS_PER_STEP
+    N_SEQ = n
+    EVALS_PER_STEP = N_SEQ * (N_SEQ - 1) * K_WN
+
+SFU_NOMINAL_PAIRS_PER_CLK_SM = 8.0  # 16 SFU results per clock per SM = 8 sin+cos pairs
+
+
+def workload():
+    from oracle import chains
+    coords, _ = chains.chain_batch([N_SEQ], N_SEQ, seed=SEED)
+    return torch.from_numpy(coords), torch.from_numpy(chains.wavenumbers(D_MODEL))
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, device_index):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz, self._stop_evt = [], set(), None, threading.Event()
+        self.err = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as exc:  # noqa: BLE001
+            self.err = repr(exc)
+            self.nv = None
+
+    def run(self):
+        if self.nv is None:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop_evt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except AttributeError:
+                    bits = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if bits & bit:
+                        self.reasons.add(name)
+            except Exception as exc:  # noqa: BLE001
+                self.err = repr(exc)
+                return
+            time.sleep(0.02)
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2.0)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+               "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if self.err:
+            out["error"] = self.err
+        return out
+
+
+def cpu_port_rate(coords, wn, target_s=12.0, chunk=32):
+    """Times the oracle (the reference's dense PyTorch formulation, observer-chunked) on the host
+    cores on a bounded run of observer rows.  Returns (evals/s, rows used, seconds)."""
+    from oracle.we_ref import wf_embedding_ref
+    torch.set_num_threads(os.cpu_count() or 1)
+    n = coords.shape[1]
+    start = n // 2
+    wf_embedding_ref(coords, wn, 1, rows=(start, start + chunk), chunk=chunk)  # warm-up
+    t0 = time.perf_counter()
+    wf_embedding_ref(coords, wn, 1, rows=(start, start + chunk), chunk=chunk)
+    per_chunk = time.perf_counter() - t0
+    chunks = int(max(1, min(64, target_s / max(per_chunk, 1e-3))))
+    rows = chunks * chunk
+    t0 = time.perf_counter()
+    wf_embedding_ref(coords, wn, 1, rows=(start, start + rows), chunk=chunk)
+    dt = time.perf_counter() - t0
+    return rows * (n - 1) * wn.shape[0] / dt, rows, dt
+
+
+def run_reference(args):
+    """The reference arm: the reference's own CPU path for this metric is its dense PyTorch
+    formulation; its restatement in oracle/ is timed on all host cores.  Each step is a bounded
+    run of observer rows of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    coords, wn = workload()
+    from oracle.we_ref import wf_embedding_ref
+    torch.set_num_threads(os.cpu_count() or 1)
+    chunk, rows = 32, 64
+    start = N_SEQ // 2
+    for _ in range(max(1, min(args.warmup, 2))):
+        wf_embedding_ref(coords, wn, 1, rows=(start, start + chunk), chunk=chunk)
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        wf_embedding_ref(coords, wn, 1, rows=(start, start + rows), chunk=chunk)
+        times.append(time.perf_counter() - t0)
+    evals = rows * (N_SEQ - 1) * K_WN
+    value = evals * len(times) / sum(times)
+    line = {
+        "impl": "reference", "metric": "WE pair*wavenumber evals/s @N=16384,d=512", "value": value, "unit": "evals/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * EVALS_PER_STEP / value, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "WE forward, Z=1, N=16384, d_model=512, random-walk chain, seed 1004",
+                   "note": "ms_per_step is the full workload extrapolated from the sample"},
+        "cpu_baseline": {"value": value, "unit": "evals/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{rows} of {N_SEQ} observer rows x all sources x {K_WN} wavenumbers per step"},
+        "e2e": {"value": value, "unit": "evals/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--n-seq", type=int, default=N_SEQ, help="sequence length (default: the headline 16384)")
+    args = ap.parse_args()
+    if args.n_seq != N_SEQ:
+        set_sequence_length(args.n_seq)
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    from proteusai_b200 import _lib
+    from proteusai_b200.utils.model_utils.wf_embedding.isotropic.cuda.wf_embedding import we_forward_rows, wf_embedding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fail loudly if the native library is missing
+    warmup = max(args.warmup, 3)
+
+    coords_h, wn_h = workload()
+    coords_pin, wn_pin = coords_h.pin_memory(), wn_h.pin_memory()
+    coords_d, wn_d = coords_h.to(dev), wn_h.to(dev)
+    rows_per = (N_SEQ + world - 1) // world
+    r0, r1 = rank * rows_per, min(N_SEQ, (rank + 1) * rows_per)
+    out = torch.empty(1, N_SEQ, 2 * K_WN, device=dev)
+    cs = torch.empty(1, N_SEQ, K_WN, device=dev)
+    sn = torch.empty(1, N_SEQ, K_WN, device=dev)
+    out_flat = out.view(-1)
+    shard_flat = out_flat[r0 * 2 * K_WN:r1 * 2 * K_WN]
+    even = (N_SEQ % world) == 0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
+    out_host = torch.empty(r1 - r0, 2 * K_WN).pin_memory()
+
+    def step_resident():
+        we_forward_rows(coords_d, wn_d, 1, None, r0, r1, out, cs, sn)
+        if world > 1:
+            if even:
+                dist.all_gather_into_tensor(out_flat, shard_flat)
+            else:
+                parts = [out_flat[i * rows_per * 2 * K_WN:min(N_SEQ, (i + 1) * rows_per) * 2 * K_WN] for i in range(world)]
+                dist.all_gather(parts, shard_flat)
+
+    def step_e2e():
+        c = coords_pin.to(dev, non_blocking=True)
+        w = wn_pin.to(dev, non_blocking=True)
+        if world == 1:
+            o = wf_embedding(c, w, 1, 0.0, None)  # the public call
+            out_host.copy_(o[0], non_blocking=True)
+        else:
+            we_forward_rows(c, w, 1, None, r0, r1, out, cs, sn)
+            if even:
+                dist.all_gather_into_tensor(out_flat, shard_flat)
+            out_host.copy_(out[0, r0:r1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, use_events=True):
+        """Sum of per-step device times (ms); L2 is flushed between steps outside the timed spans."""
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        barrier()
+        wall = 0.0
+        for a, b in evs:
+            flush.zero_()
+            if use_events:
+                a.record()
+                fn()
+                b.record()
+            else:
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                wall += (time.perf_counter() - t0) * 1e3
+        barrier()
+        total = sum(a.elapsed_time(b) for a, b in evs) if use_events else wall
+        if world > 1:
+            t = torch.tensor([total], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total = float(t.item())
+        return total
+
+    for _ in range(warmup):
+        step_resident()
+    sampler = ClockSampler(local)
+    sampler.start()
+    total_ms = timed(step_resident, args.steps)
+    clocks = sampler.stop()
+    _lib.device_status()
+
+    # kernel alone (no collective), for the roofline
+    def kernel_only():
+        we_forward_rows(coords_d, wn_d, 1, None, r0, r1, out, cs, sn)
+    kern_ms = timed(kernel_only, args.steps) / args.steps
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps, use_events=False)
+
+    value = EVALS_PER_STEP * args.steps / (total_ms * 1e-3)
+    e2e_value = EVALS_PER_STEP * args.steps / (e2e_ms * 1e-3)
+    line = None
+    if rank == 0:
+        sfu_rate, _ = _lib.measure_sfu_peak()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        evals_per_launch = (r1 - r0) * (N_SEQ - 1) * K_WN
+        achieved = evals_per_launch / (kern_ms * 1e-3)
+        nominal = SFU_NOMINAL_PAIRS_PER_CLK_SM * sms * (clocks["sm_max_mhz"] or 1965) * 1e6
+        line = {
+            "metric": "WE pair*wavenumber evals/s @N=16384,d=512", "value": value, "unit": "evals/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": value / H100_PUBLISHED_EVALS_PER_S if N_SEQ == 16384 else None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"WE forward, Z=1, N={N_SEQ}, d_model=512 (256 wavenumbers), random-walk chain, seed 1004",
+                       "sharding": f"observer rows over {world} rank(s), coordinates replicated, NCCL all-gather of the output",
+                       "l2": "flushed between timed steps (256 MB memset outside the timed spans)"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "evals/s",
+                    "h2d_bytes_per_step": int(coords_pin.numel() * 4 + wn_pin.numel() * 4) * world,
+                    "d2h_bytes_per_step": int(N_SEQ * 2 * K_WN * 4), "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": args.steps,
+            "roofline": {"bound": "sfu", "achieved": achieved / 1e9, "peak": sfu_rate / 1e9, "unit": "Geval/s",
+                         "frac": achieved / sfu_rate, "traffic": None,
+                         "peak_source": "measured live: register-only sin+cos loop on this GPU (pai_measure_sfu_peak)",
+                         "peak_nominal": nominal / 1e9, "frac_of_nominal": achieved / nominal,
+                         "kernel": "we_fwd_kernel", "kernel_ms": kern_ms,
+                         "evals_per_launch": evals_per_launch},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            rate, rows, secs = cpu_port_rate(coords_h, wn_h)
+            line["cpu_baseline"] = {"value": rate, "unit": "evals/s", "cores": torch.get_num_threads(), "kind": "port",
+                                    "sample": f"{rows} of {N_SEQ} observer rows x all sources x {K_WN} wavenumbers, {secs:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

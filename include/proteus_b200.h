@@ -1,0 +1,102 @@
+/*
+ * proteus_b200 -- C ABI of the B200 (sm_100a) kernels for proteusAI's two hot paths:
+ * the isotropic Wavefunction Embedding (WE) and the Geometric Attention.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer on the current CUDA device unless stated otherwise;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *   - calls are asynchronous: they enqueue work on `stream` and return;
+ *   - the caller allocates every buffer; the callee writes every element of the outputs it
+ *     owns (rows of padded tokens are written as zeros), so outputs need no zero-fill;
+ *   - return value: 0 = ok, negative = argument error (pai_status), positive = cudaError_t;
+ *     nothing throws, aborts or traps across this boundary;
+ *   - the library allocates no device memory.
+ *
+ * Each entry point cites the reference interface it replaces (path inside jaimec00/proteusAI).
+ */
+#ifndef PROTEUS_B200_H
+#define PROTEUS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum pai_status {
+    PAI_OK = 0,
+    PAI_ERR_NULL_POINTER = -1,
+    PAI_ERR_BAD_SHAPE = -2,
+    PAI_ERR_MISALIGNED = -3,
+    PAI_ERR_UNSUPPORTED = -4,
+    PAI_ERR_WORKSPACE_TOO_SMALL = -5,
+    PAI_ERR_BAD_ROW_RANGE = -6,
+    PAI_ERR_NOT_SM100 = -7,
+    PAI_ERR_DEVICE_WAIT_TIMEOUT = -8
+};
+
+/* ABI version of this header (bumped on any signature change). */
+int pai_abi_version(void);
+
+/* Human-readable text for a value returned by any entry point (static storage). */
+const char *pai_status_str(int status);
+
+/* Synchronises `stream` and returns, then clears, the device-side status word of the
+ * current device: PAI_OK, or PAI_ERR_DEVICE_WAIT_TIMEOUT when a kernel gave up on a
+ * bounded wait (it then wrote nothing further and returned). */
+int pai_device_status(void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Wavefunction Embedding, forward.
+ * Replaces wf_embedding_kernel_forward()
+ *   (utils/model_utils/wf_embedding/isotropic/cuda/wf_embedding_kernel.cu:295-344), the function
+ *   behind the pybind11 entry `wf_embedding_kernel.forward`
+ *   (utils/model_utils/wf_embedding/isotropic/cuda/wf_embedding_if.cpp:20-77).
+ *
+ *   coords_soa  [Z,3,N] fp32   coordinates, x/y/z planes (the reference's transposed layout)
+ *   valid       [Z,N]   u8     1 = real token, 0 = padding; NULL = all valid
+ *                              (replaces the reference's x == 12345 sentinel)
+ *   wavenumbers [K]     fp32
+ *   out         [Z,N,2K] fp32  interleaved: [2k] = sum_j mag*cos(k r_ij), [2k+1] = sum_j mag*sin(k r_ij)
+ *   cos_sums    [Z,N,K] fp32   sum_j mag*r*cos(k r_ij)   (stored for the backward)
+ *   sin_sums    [Z,N,K] fp32   sum_j mag*r*sin(k r_ij)
+ *   row_begin,row_end          observer rows [row_begin,row_end) of every batch element are
+ *                              computed and written; other rows are not touched (multi-GPU shard)
+ *   magnitude_type             0: 1, 1: 1/r, 2: 1/log2(r), 3: 1/sqrt(r)
+ *   dropout_p, seed            only dropout_p == 0 is supported (PAI_ERR_UNSUPPORTED otherwise)
+ * Pairs with j == i, coincident points (r == 0) and padded tokens contribute nothing.
+ * Requires 1 <= N, 1 <= K, 1 <= Z <= 65535.
+ */
+int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *wavenumbers,
+               float *out, float *cos_sums, float *sin_sums,
+               int Z, int N, int K, int row_begin, int row_end,
+               int magnitude_type, float dropout_p, uint32_t seed, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Wavefunction Embedding, backward w.r.t. the wavenumbers.
+ * Replaces the PyTorch expression in _wf_embedding.backward
+ *   (utils/model_utils/wf_embedding/isotropic/cuda/wf_embedding.py:64-83):
+ *   dk[k] = sum_{z, n in [row_begin,row_end)} dO[z,n,2k+1]*cos_sums[z,n,k] - dO[z,n,2k]*sin_sums[z,n,k]
+ *
+ *   dO [Z,N,2K], cos_sums/sin_sums [Z,N,K], dk [K] (overwritten), all fp32.
+ *   workspace: scratch of at least pai_we_bwd_dk_workspace_bytes(Z,N,K) bytes, 16-byte aligned;
+ *   it holds per-block partial sums that a second pass adds in a fixed order (bit-reproducible).
+ */
+size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K);
+int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums, float *dk,
+                  void *workspace, size_t workspace_bytes,
+                  int Z, int N, int K, int row_begin, int row_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and
+ * returns results per second through *sincos_pairs_per_s (one pair = one sin and one cos, which is
+ * what one WE evaluation needs) and the elapsed device time.  Synchronous.  Used as the
+ * denominator of the WE roofline; has no counterpart in the reference.
+ */
+int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PROTEUS_B200_H */

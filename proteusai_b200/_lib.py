@@ -1,0 +1,73 @@
+"""ctypes binding of libproteus_b200.so (the C ABI declared in include/proteus_b200.h).
+
+There is no fallback: if the library is missing or an entry point reports an error, the call
+raises.  Pointers are raw device addresses (``tensor.data_ptr()``), the stream is the raw
+``cudaStream_t`` of PyTorch's current stream.
+"""
+import ctypes
+import os
+from ctypes import c_char_p, c_double, c_float, c_int, c_size_t, c_uint32, c_void_p
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("PROTEUS_B200_LIB", os.path.join(_PKG, "libproteus_b200.so"))
+
+# name -> (restype, argtypes); mirrors include/proteus_b200.h
+SIGNATURES = {
+    "pai_abi_version": (c_int, []),
+    "pai_status_str": (c_char_p, [c_int]),
+    "pai_device_status": (c_int, [c_void_p]),
+    "pai_we_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_uint32, c_void_p]),
+    "pai_we_bwd_dk_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "pai_we_bwd_dk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                              c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "pai_measure_sfu_peak": (c_int, [ctypes.POINTER(c_double), ctypes.POINTER(c_double)]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded library (loads on first use; raises if it has not been built)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} not found: build it with `python -m proteusai_b200.build` "
+                "(nvcc, sm_100a).  There is no CPU or PyTorch fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(status, what):
+    """Raise RuntimeError for a non-zero status returned by an entry point."""
+    if status != 0:
+        msg = lib().pai_status_str(int(status)).decode()
+        raise RuntimeError(f"{what} failed: {msg} (status {status})")
+
+
+def ptr(t):
+    """Device address of a tensor (None -> NULL)."""
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def current_stream():
+    import torch
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def device_status():
+    """Synchronise the current stream and raise if a kernel reported a bounded-wait timeout."""
+    check(lib().pai_device_status(current_stream()), "device status")
+
+
+def measure_sfu_peak():
+    """(sin+cos pairs per second, elapsed ms) of the register-only SFU loop on the current device."""
+    rate, ms = c_double(0.0), c_double(0.0)
+    check(lib().pai_measure_sfu_peak(ctypes.byref(rate), ctypes.byref(ms)), "pai_measure_sfu_peak")
+    return rate.value, ms.value

@@ -1,0 +1,197 @@
+// C ABI of the proteus_b200 library (see include/proteus_b200.h).  Single translation unit:
+// the kernels are header files so that the device status word needs no relocatable device code.
+#include "common.cuh"
+
+#include "we_bwd.cuh"
+#include "we_fwd.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace {
+
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+// Compute capability of the current device, cached per device ordinal.
+int current_device_cc(int *cc_out) {
+    static int cache[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64 && cache[dev]) {
+        *cc_out = cache[dev];
+        return 0;
+    }
+    int major = 0, minor = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    if (e != cudaSuccess) return (int)e;
+    *cc_out = major * 10 + minor;
+    if (dev >= 0 && dev < 64) cache[dev] = *cc_out;
+    return 0;
+}
+
+int require_sm100() {
+    int cc = 0;
+    int e = current_device_cc(&cc);
+    if (e) return e;
+    return cc == 100 ? 0 : (int)PAI_ERR_NOT_SM100;
+}
+
+int env_int(const char *name, int dflt) {
+    const char *v = std::getenv(name);
+    return v && *v ? std::atoi(v) : dflt;
+}
+
+// register-only sin+cos loop: 8 independent chains per thread
+__global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
+    float x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = seed + 0.001f * (threadIdx.x + 17 * i);
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float s, c;
+            pai::sfu_sincos(x[i], s, c);
+            x[i] = s + c;
+        }
+    }
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += x[i];
+    if (t == 123456.789f) pai::g_sink = t;
+}
+
+}  // namespace
+
+extern "C" {
+
+int pai_abi_version(void) { return 1; }
+
+const char *pai_status_str(int status) {
+    switch (status) {
+        case PAI_OK: return "ok";
+        case PAI_ERR_NULL_POINTER: return "null pointer argument";
+        case PAI_ERR_BAD_SHAPE: return "bad shape (sizes must be positive and within limits)";
+        case PAI_ERR_MISALIGNED: return "pointer not aligned as required";
+        case PAI_ERR_UNSUPPORTED: return "unsupported option";
+        case PAI_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+        case PAI_ERR_BAD_ROW_RANGE: return "bad row range (need 0 <= begin <= end <= N)";
+        case PAI_ERR_NOT_SM100: return "current device is not sm_100 (B200)";
+        case PAI_ERR_DEVICE_WAIT_TIMEOUT: return "a kernel gave up on a bounded device-side wait";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString((cudaError_t)status);
+    return "unknown status";
+}
+
+int pai_device_status(void *stream) {
+    cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, pai::g_device_status, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    if (v != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(pai::g_device_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return (int)e;
+    }
+    return v;
+}
+
+int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *wavenumbers, float *out, float *cos_sums,
+               float *sin_sums, int Z, int N, int K, int row_begin, int row_end, int magnitude_type, float dropout_p,
+               uint32_t seed, void *stream) {
+    (void)seed;
+    if (!coords_soa || !wavenumbers || !out || !cos_sums || !sin_sums) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || Z > 65535 || N < 1 || K < 1 || (long long)N * K > (1ll << 40)) return PAI_ERR_BAD_SHAPE;
+    if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (magnitude_type < 0 || magnitude_type > 3) return PAI_ERR_UNSUPPORTED;
+    if (dropout_p != 0.0f) return PAI_ERR_UNSUPPORTED;
+    if (!aligned(coords_soa, 4) || !aligned(wavenumbers, 4)) return PAI_ERR_MISALIGNED;
+    if ((K & 1) == 0 ? (!aligned(out, 16) || !aligned(cos_sums, 8) || !aligned(sin_sums, 8))
+                     : (!aligned(out, 4) || !aligned(cos_sums, 4) || !aligned(sin_sums, 4)))
+        return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    if (row_begin == row_end) return PAI_OK;
+    pai::WeFwdParams p;
+    p.coords = coords_soa;
+    p.valid = valid;
+    p.wn = wavenumbers;
+    p.out = out;
+    p.cos_sums = cos_sums;
+    p.sin_sums = sin_sums;
+    p.N = N;
+    p.K = K;
+    p.row_begin = row_begin;
+    p.row_end = row_end;
+    p.mag_type = magnitude_type;
+    // bulk copies need 16-byte aligned plane segments: base aligned and N a multiple of 4
+    p.use_tma = (aligned(coords_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
+    return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_RANGE_REDUCE", 0) != 0,
+                              (cudaStream_t)stream);
+}
+
+size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {
+    (void)Z;
+    (void)N;
+    if (K < 1) return 0;
+    return (size_t)pai::WE_BWD_MAX_BLOCKS * (size_t)K * sizeof(float);
+}
+
+int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums, float *dk, void *workspace,
+                  size_t workspace_bytes, int Z, int N, int K, int row_begin, int row_end, void *stream) {
+    if (!dO || !cos_sums || !sin_sums || !dk || !workspace) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || (long long)Z * N > (1ll << 30)) return PAI_ERR_BAD_SHAPE;
+    if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(dO, 8) || !aligned(cos_sums, 4) || !aligned(sin_sums, 4) || !aligned(dk, 4) || !aligned(workspace, 16))
+        return PAI_ERR_MISALIGNED;
+    if (workspace_bytes < pai_we_bwd_dk_workspace_bytes(Z, N, K)) return PAI_ERR_WORKSPACE_TOO_SMALL;
+    if (int e = require_sm100()) return e;
+    if (row_begin == row_end) {
+        cudaError_t e = cudaMemsetAsync(dk, 0, (size_t)K * sizeof(float), (cudaStream_t)stream);
+        return (int)e;
+    }
+    return pai::we_bwd_launch(dO, cos_sums, sin_sums, dk, (float *)workspace, Z, N, K, row_begin, row_end,
+                              (cudaStream_t)stream);
+}
+
+int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {
+    if (!sincos_pairs_per_s || !elapsed_ms) return PAI_ERR_NULL_POINTER;
+    if (int e = require_sm100()) return e;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int blocks = sms * 8, threads = 256, iters = 4096;
+    cudaEvent_t a, b;
+    cudaError_t e = cudaEventCreate(&a);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaEventCreate(&b);
+    if (e != cudaSuccess) {
+        cudaEventDestroy(a);
+        return (int)e;
+    }
+    sfu_peak_kernel<<<blocks, threads>>>(256, 0.5f);  // warm-up
+    float best = 1e30f;
+    for (int rep = 0; rep < 3; ++rep) {
+        cudaEventRecord(a);
+        sfu_peak_kernel<<<blocks, threads>>>(iters, 0.5f);
+        cudaEventRecord(b);
+        e = cudaEventSynchronize(b);
+        if (e != cudaSuccess) break;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, a, b);
+        if (ms < best) best = ms;
+    }
+    cudaEventDestroy(a);
+    cudaEventDestroy(b);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    *elapsed_ms = best;
+    *sincos_pairs_per_s = (double)blocks * threads * iters * 8.0 / (best * 1e-3);
+    return PAI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,86 @@
+"""CPU-only checks of the C ABI: the library loads, exports every symbol the header declares, and
+rejects bad arguments with status codes before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from proteusai_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def _declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(pai_\w+)\s*\(", text))
+    return names
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/ but not exported"
+    assert declared == set(_lib.SIGNATURES), "ctypes table and header disagree"
+
+
+def test_version_and_status_strings(lib):
+    assert lib.pai_abi_version() >= 1
+    assert lib.pai_status_str(0) == b"ok"
+    for code in range(-8, 0):
+        assert lib.pai_status_str(code) not in (b"", b"unknown status")
+
+
+def test_we_fwd_argument_errors(lib):
+    p = ctypes.c_void_p(0x1000)  # never dereferenced: validation fails first
+    null = None
+    f = lib.pai_we_fwd
+    assert f(null, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, None) == -1
+    assert f(p, null, p, p, p, p, 0, 8, 4, 0, 8, 1, 0.0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 0, 4, 0, 0, 1, 0.0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 8, 0, 0, 8, 1, 0.0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 8, 4, 5, 4, 1, 0.0, 0, None) == -6
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 9, 1, 0.0, 0, None) == -6
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 7, 0.0, 0, None) == -4
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.1, 0, None) == -4
+    assert f(p, null, p, ctypes.c_void_p(0x1004), p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, None) == -3
+
+
+def test_we_bwd_argument_errors(lib):
+    p = ctypes.c_void_p(0x1000)
+    f = lib.pai_we_bwd_dk
+    need = lib.pai_we_bwd_dk_workspace_bytes(2, 16, 8)
+    assert need >= 8 * 4
+    assert f(None, p, p, p, p, need, 2, 16, 8, 0, 16, None) == -1
+    assert f(p, p, p, p, p, need, 2, 16, 0, 0, 16, None) == -2
+    assert f(p, p, p, p, p, need, 2, 16, 8, 3, 2, None) == -6
+    assert f(p, p, p, p, p, need - 1, 2, 16, 8, 0, 16, None) == -5
+    assert f(p, p, p, p, ctypes.c_void_p(0x1008), need, 2, 16, 8, 0, 16, None) == -3
+
+
+def test_no_cpu_fallback():
+    import torch
+    from proteusai_b200.utils.model_utils.wf_embedding.isotropic.cuda.wf_embedding import wf_embedding
+    with pytest.raises(RuntimeError):
+        wf_embedding(torch.zeros(1, 4, 3), torch.ones(2), mask=None)
+
+
+def test_dropin_aliases():
+    import sys
+
+    import proteusai_b200
+    proteusai_b200.install_dropin(force=True)
+    mod = sys.modules["utils.model_utils.wf_embedding.isotropic.cuda.wf_embedding"]
+    assert hasattr(mod, "wf_embedding") and hasattr(mod, "_wf_embedding")

@@ -1,0 +1,194 @@
+"""Parity of the CUDA Wavefunction Embedding (through the C ABI) with the CPU oracle.
+
+Tolerances are the ones the path is specified to: output within 1e-4 relative L2 of the
+reference's PyTorch arithmetic, wavenumber gradient within 1e-3 relative L2."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import chains
+from oracle.we_ref import dk_analytic, rel_l2, wf_embedding_ref
+
+pytestmark = pytest.mark.gpu
+
+OUT_TOL = 1e-4
+DK_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def we():
+    from proteusai_b200 import _lib
+    from proteusai_b200.utils.model_utils.wf_embedding.isotropic.cuda import wf_embedding as mod
+    assert torch.cuda.is_available()
+    _lib.lib()
+    return mod
+
+
+def _golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "we_reference.npz"))
+    for name in sorted({k.split(".")[0] for k in g.files}):
+        yield name, {x: torch.from_numpy(np.asarray(g[f"{name}.{x}"])) for x in
+                     ("coords", "wn", "mag", "mask", "out", "dk_sum")}
+
+
+def test_golden_forward_and_dk(we, golden_dir):
+    for name, t in _golden(golden_dir):
+        wn = t["wn"].cuda().requires_grad_(True)
+        out = we.wf_embedding(t["coords"].cuda(), wn, int(t["mag"]), 0.0, t["mask"].cuda())
+        assert rel_l2(t["out"], out.detach().cpu()) < OUT_TOL, name
+        out.sum().backward()  # the reference test's backward check
+        assert rel_l2(t["dk_sum"], wn.grad.cpu()) < DK_TOL, name
+
+
+def test_config1_chain_n512(we):
+    c, m = chains.chain_batch([512], 512, seed=1001)
+    wn = chains.wavenumbers(512)
+    c_t, wn_t = torch.from_numpy(c), torch.from_numpy(wn)
+    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, torch.from_numpy(m).cuda())
+    ref32 = wf_embedding_ref(c_t, wn_t, 1)
+    ref64, cs64, sn64 = wf_embedding_ref(c_t, wn_t, 1, dtype=torch.float64, return_sums=True)
+    assert rel_l2(ref32, out.cpu()) < OUT_TOL
+    assert rel_l2(ref64, out.cpu()) < OUT_TOL
+    assert rel_l2(cs64, cs.cpu()) < OUT_TOL and rel_l2(sn64, sn.cpu()) < OUT_TOL
+
+
+def test_config2_padded_batch_fwd_bwd(we):
+    lengths = chains.draw_lengths(8, 128, 1024, seed=1002)
+    c, m = chains.chain_batch(lengths, 1024, seed=1002)
+    c_t, m_t, wn_t = torch.from_numpy(c), torch.from_numpy(m), torch.from_numpy(chains.wavenumbers(512))
+    g = torch.Generator().manual_seed(1002)
+    d_out = torch.randn(8, 1024, 512, generator=g)
+    wn = wn_t.cuda().requires_grad_(True)
+    out = we.wf_embedding(c_t.cuda(), wn, 1, 0.0, m_t.cuda())
+    out.backward(d_out.cuda())
+    # oracle one sample at a time (the dense intermediate of the whole batch would not fit)
+    dk_ref = torch.zeros(256, dtype=torch.float64)
+    for b in range(8):
+        ref, cs, sn = wf_embedding_ref(c_t[b:b + 1], wn_t, 1, m_t[b:b + 1], return_sums=True)
+        assert rel_l2(ref, out[b:b + 1].detach().cpu()) < OUT_TOL, b
+        assert torch.all(out[b, lengths[b]:] == 0), "padded rows must be written as zeros"
+        dk_ref += dk_analytic(d_out[b:b + 1].double(), cs.double(), sn.double())
+    assert rel_l2(dk_ref, wn.grad.cpu()) < DK_TOL
+
+
+@pytest.mark.parametrize("n", [1, 2, 31, 33, 64, 65, 127, 129, 1000])
+@pytest.mark.parametrize("k", [1, 3, 64])
+def test_edge_shapes(we, n, k):
+    g = torch.Generator().manual_seed(n * 131 + k)
+    z = 2
+    coords = 15 * torch.randn(z, n, 3, generator=g)
+    wn = torch.rand(k, generator=g) * 1.5 + 0.2
+    mask = torch.rand(z, n, generator=g) > 0.8
+    out, cs, sn = we.we_forward_rows(coords.cuda(), wn.cuda(), 1, mask.cuda())
+    ref, rcs, rsn = wf_embedding_ref(coords, wn, 1, mask, return_sums=True, dtype=torch.float64)
+    denom = max(float(torch.norm(ref)), 1e-30)
+    assert float(torch.norm(ref - out.cpu().double())) / denom < OUT_TOL or float(torch.norm(ref)) == 0
+    assert torch.all(out.cpu()[mask] == 0)
+    if n > 2:
+        assert rel_l2(rcs, cs.cpu()) < OUT_TOL and rel_l2(rsn, sn.cpu()) < OUT_TOL
+
+
+@pytest.mark.parametrize("mag", [0, 2, 3])
+def test_magnitude_types(we, mag):
+    c, m = chains.chain_batch([200, 77], 200, seed=21)
+    c_t, m_t = torch.from_numpy(c), torch.from_numpy(m)
+    wn = torch.from_numpy(chains.wavenumbers(64))
+    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn.cuda(), mag, m_t.cuda())
+    ref, rcs, rsn = wf_embedding_ref(c_t, wn, mag, m_t, return_sums=True, dtype=torch.float64)
+    assert rel_l2(ref, out.cpu()) < OUT_TOL
+    assert rel_l2(rcs, cs.cpu()) < OUT_TOL and rel_l2(rsn, sn.cpu()) < OUT_TOL
+
+
+def test_degenerate_inputs(we):
+    wn = torch.from_numpy(chains.wavenumbers(32)).cuda()
+    # all padded / a single valid token: exactly zero everywhere (no self term)
+    coords = torch.randn(2, 40, 3)
+    mask = torch.ones(2, 40, dtype=torch.bool)
+    mask[1, 7] = False
+    out, cs, sn = we.we_forward_rows(coords.cuda(), wn, 1, mask.cuda())
+    assert torch.all(out == 0) and torch.all(cs == 0) and torch.all(sn == 0)
+    # all points coincide: every pair has r == 0 and is excluded
+    same = torch.ones(1, 50, 3) * 3.25
+    out, _, _ = we.we_forward_rows(same.cuda(), wn, 1, None)
+    assert torch.all(out == 0)
+    # garbage (NaN, inf, huge) under the padding must not leak into valid rows
+    c, m = chains.chain_batch([90], 128, seed=5)
+    c_t, m_t = torch.from_numpy(c), torch.from_numpy(m)
+    clean, _, _ = we.we_forward_rows(c_t.cuda(), wn, 1, m_t.cuda())
+    dirty = c_t.clone()
+    dirty[0, 90:100] = float("nan")
+    dirty[0, 100:110] = float("inf")
+    dirty[0, 110:] = 1e30
+    got, _, _ = we.we_forward_rows(dirty.cuda(), wn, 1, m_t.cuda())
+    assert torch.equal(clean, got)
+
+
+def test_row_shards_and_code_paths_agree(we, monkeypatch):
+    c, m = chains.chain_batch([700, 333], 700, seed=8)
+    c_t, m_t = torch.from_numpy(c).cuda(), torch.from_numpy(m).cuda()
+    wn = torch.from_numpy(chains.wavenumbers(128)).cuda()
+    full, fcs, fsn = we.we_forward_rows(c_t, wn, 1, m_t)
+    # the union of row shards reproduces the full result bit for bit
+    out = torch.full_like(full, float("nan"))
+    cs, sn = torch.full_like(fcs, float("nan")), torch.full_like(fsn, float("nan"))
+    for a, b in ((0, 175), (175, 350), (350, 525), (525, 700)):
+        we.we_forward_rows(c_t, wn, 1, m_t, a, b, out, cs, sn)
+    assert torch.equal(out, full) and torch.equal(cs, fcs) and torch.equal(sn, fsn)
+    ref = wf_embedding_ref(c_t.cpu(), wn.cpu(), 1, m_t.cpu(), dtype=torch.float64)
+    for env in ({"PAI_WE_NO_TMA": "1"}, {"PAI_WE_KS": "8"}, {"PAI_WE_KS": "2"}, {"PAI_WE_RANGE_REDUCE": "1"},
+                {"PAI_WE_KS": "16"}):
+        for key, val in env.items():
+            monkeypatch.setenv(key, val)
+        alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
+        for key in env:
+            monkeypatch.delenv(key)
+        assert rel_l2(ref, alt.cpu()) < OUT_TOL, env
+    from proteusai_b200 import _lib
+    _lib.device_status()
+
+
+def test_unaligned_n_uses_plain_loads(we):
+    c, _ = chains.chain_batch([1021], 1021, seed=9)  # N % 4 != 0: bulk copies are not legal
+    c_t = torch.from_numpy(c)
+    wn = torch.from_numpy(chains.wavenumbers(32))
+    out, _, _ = we.we_forward_rows(c_t.cuda(), wn.cuda(), 1, None)
+    assert rel_l2(wf_embedding_ref(c_t, wn, 1, dtype=torch.float64), out.cpu()) < OUT_TOL
+
+
+def test_config4_long_sequence_slice_and_properties(we):
+    n = 16384
+    c, _ = chains.chain_batch([n], n, seed=1004)
+    c_t, wn_t = torch.from_numpy(c), torch.from_numpy(chains.wavenumbers(512))
+    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
+    again, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
+    assert torch.equal(out, again), "the forward is deterministic"
+    rows = (8000, 8256)
+    ref64 = wf_embedding_ref(c_t, wn_t, 1, rows=rows, chunk=32, dtype=torch.float64)
+    err = rel_l2(ref64, out[:, rows[0]:rows[1]].cpu())
+    print(f"N=16384 rel-L2 vs fp64 oracle on rows {rows}: {err:.3e}")
+    assert err < OUT_TOL
+    ref32 = wf_embedding_ref(c_t, wn_t, 1, rows=(8000, 8064), chunk=16)
+    assert rel_l2(ref32, out[:, 8000:8064].cpu()) < OUT_TOL
+    # rigid motion leaves the features unchanged (up to fp32 rounding of the moved coordinates)
+    q, _ = torch.linalg.qr(torch.randn(3, 3, dtype=torch.float64, generator=torch.Generator().manual_seed(3)))
+    moved = (c_t.double() @ q.T + torch.tensor([3.0, -2.0, 1.0], dtype=torch.float64)).float()
+    out_m, _, _ = we.we_forward_rows(moved.cuda(), wn_t.cuda(), 1, None)
+    assert rel_l2(out, out_m) < 5e-4
+    # token permutation permutes the rows
+    perm = torch.randperm(n, generator=torch.Generator().manual_seed(4))
+    out_p, _, _ = we.we_forward_rows(c_t[:, perm].cuda(), wn_t.cuda(), 1, None)
+    assert rel_l2(out[:, perm.cuda()], out_p) < 1e-5
+
+
+def test_module_matches_reference_schedule(we):
+    from proteusai_b200.utils.model_utils.wf_embedding.wf_embedding import WaveFunctionEmbedding
+    mod = WaveFunctionEmbedding(d_wf=64, anisotropic=False, learn_wl=True).cuda()
+    c, m = chains.chain_batch([120, 64], 120, seed=12)
+    c_t, m_t = torch.from_numpy(c), torch.from_numpy(m)
+    out = mod(c_t.cuda(), None, key_padding_mask=m_t.cuda())
+    ref = wf_embedding_ref(c_t, mod.get_wavenumbers().detach().cpu(), 1, m_t)
+    assert rel_l2(ref, out.detach().cpu()) < OUT_TOL
+    out.square().sum().backward()
+    assert mod.wavenumbers.grad is not None and torch.isfinite(mod.wavenumbers.grad).all()
