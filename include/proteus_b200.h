@@ -89,6 +89,28 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
                   int Z, int N, int K, int row_begin, int row_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Geometric attention, forward.
+ * Replaces the Triton launch `_attn_fwd[grid](...)` in _geometric_attn.forward
+ *   (old/old_scripts/attn/geometric_attn.py:553-607; kernel :57-260), with the logit form of the
+ *   reference README (README.md:40):  SR_ij = (q_i.k_j * scale) * (1 + exp(-|r_i-r_j|^2 / (2 sigma_h^2))),
+ *   softmax over the keys j, a pair (i,j) valid iff both tokens are unpadded.
+ *
+ *   Q, K, V  [Z,H,N,d] bf16, contiguous     (d must be 64)
+ *   coords   [Z,N,3]   fp32                 C-alpha coordinates
+ *   sigma    [H]       fp32                 per-head RBF spread
+ *   valid    [Z,N]     u8                   1 = real token, 0 = padding; NULL = all valid
+ *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros
+ *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for padded queries
+ *   scale                                    softmax scale, 1/sqrt(d) in the reference
+ *   zh_begin, zh_end                         only the (batch, head) pairs z*H + h in [zh_begin, zh_end) are
+ *                                            computed and written (multi-GPU shard); other rows are not touched
+ * bf16 x bf16 -> fp32 tensor-core products, fp32 softmax, P rounded to bf16 before P V.
+ */
+int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
+                    const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale,
+                    int zh_begin, int zh_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and
  * returns results per second through *sincos_pairs_per_s (one pair = one sin and one cos, which is
  * what one WE evaluation needs) and the elapsed device time.  Synchronous.  Used as the

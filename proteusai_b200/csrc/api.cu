@@ -2,6 +2,7 @@
 // the kernels are header files so that the device status word needs no relocatable device code.
 #include "common.cuh"
 
+#include "geoattn_fwd.cuh"
 #include "we_bwd.cuh"
 #include "we_fwd.cuh"
 
@@ -155,6 +156,49 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
     }
     return pai::we_bwd_launch(dO, cos_sums, sin_sums, dk, (float *)workspace, Z, N, K, row_begin, row_end,
                               (cudaStream_t)stream);
+}
+
+int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
+                    const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale, int zh_begin,
+                    int zh_end, void *stream) {
+    if (!Q || !K || !V || !coords || !sigma || !O || !L) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
+    if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
+    if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(coords, 4) ||
+        !aligned(sigma, 4) || !aligned(L, 4))
+        return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    if (zh_begin == zh_end) return PAI_OK;
+    const int nzh = zh_end - zh_begin;
+    const size_t off = (size_t)zh_begin * N * d * 2;
+    CUtensorMap mq, mk, mv;
+    if (int e = pai::make_map_bf16_rows(&mq, (const char *)Q + off, nzh, N, d, pai::GA_BM)) return e;
+    if (int e = pai::make_map_bf16_rows(&mk, (const char *)K + off, nzh, N, d, pai::GA_BN)) return e;
+    if (int e = pai::make_map_bf16_rows(&mv, (const char *)V + off, nzh, N, d, pai::GA_BN)) return e;
+    const int smem = (int)sizeof(pai::GaFwdSmem) + 1024;
+    static bool attr_done[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(pai::geoattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    pai::GaFwdParams p;
+    p.coords = coords;
+    p.valid = valid;
+    p.sigma = sigma;
+    p.out = (__nv_bfloat16 *)O;
+    p.lse = L;
+    p.Z = Z;
+    p.H = H;
+    p.N = N;
+    p.zh_begin = zh_begin;
+    p.scale = scale;
+    dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
+    pai::geoattn_fwd_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    return (int)cudaPeekAtLastError();
 }
 
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {

@@ -1,6 +1,7 @@
 // Shared device helpers: packed fp32x2 arithmetic, mbarrier + bulk-copy (TMA) wrappers with
 // bounded waits, and the device status word.  sm_100a only.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 

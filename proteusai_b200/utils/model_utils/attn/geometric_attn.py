@@ -1,0 +1,66 @@
+"""Geometric attention: the reference's Python surface over the B200 tcgen05 kernels.
+
+Same names, argument order and gradient tuple as ``old/old_scripts/attn/geometric_attn.py:545-660``
+(imported by the reference as ``utils.model_utils.attn.geometric_attn``):
+``geometric_attn(Q, K, V, coords, spreads, betas, mask=None, min_rbf=0.0, max_rbf=1.0)`` returns
+``[Z, H, N, d]``; the backward returns ``(dQ, dK, dV, None, d_spreads, d_betas, None, None, None)``.
+
+The logits follow the form the reference's README states, ``S * (1 + exp(-d^2 / (2 sigma_h^2)))``, with a
+pair valid iff both tokens are unpadded.  ``betas``, ``min_rbf`` and ``max_rbf`` stay in the signature
+for compatibility and do not enter this form; ``d_betas`` is returned as ``None``.  Products are
+bf16 x bf16 with fp32 accumulation (the reference casts to fp16); outputs and gradients come back in
+the dtype of ``Q``.
+"""
+import torch
+
+from proteusai_b200 import _lib
+
+
+def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00, max_rbf=1.00):
+    """wrapper so that the Function can be called with keyword arguments"""
+    return _geometric_attn.apply(Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf)
+
+
+def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None):
+    """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V must be bf16 contiguous.
+    Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``; only the pairs of the range are written."""
+    if not Q.is_cuda:
+        raise RuntimeError("geometric_attn needs CUDA tensors: there is no CPU path")
+    batch, nheads, n, d_k = Q.shape
+    zh_end = batch * nheads if zh_end is None else zh_end
+    dev = Q.device
+    coords = coords.to(torch.float32).contiguous()
+    sigma = spreads.detach().to(torch.float32).contiguous()
+    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    if out is None:
+        out = torch.empty(batch, nheads, n, d_k, dtype=torch.bfloat16, device=dev)
+    if lse is None:
+        lse = torch.empty(batch, nheads, n, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().pai_geoattn_fwd(
+            _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(coords), _lib.ptr(sigma), _lib.ptr(valid),
+            _lib.ptr(out), _lib.ptr(lse), batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), zh_begin, zh_end,
+            _lib.current_stream()), "pai_geoattn_fwd")
+    return out, lse
+
+
+class _geometric_attn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf):
+        assert Q.shape == K.shape == V.shape, f"Q, K, and V projection shapes must match, but got {Q.shape=}, {K.shape=}, {V.shape=}"
+        batch, nheads, N, d_k = Q.shape
+        assert coords.dim() == 3 and coords.size(2) == 3, f"coordinates must be of shape (batch, N, 3), not {coords.shape}"
+        assert spreads.size(0) == nheads, f"number of spreads per batch must be equal to nheads, not {spreads.size(0)=} and {nheads=}"
+        assert torch.all(spreads > 0), f"spreads must be a tensor of positive, non-zero floats, not {spreads}"
+        qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
+        out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask)
+        ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0))
+        ctx.has_mask = mask is not None
+        ctx.in_dtype = Q.dtype
+        ctx.spread_dtype = spreads.dtype
+        return out.to(Q.dtype)
+
+    @staticmethod
+    def backward(ctx, dO):
+        raise NotImplementedError("geometric_attn backward kernel is not built yet")
