@@ -100,6 +100,83 @@ class ClockSampler(threading.Thread):
         return out
 
 
+GA_Z, GA_H, GA_N, GA_D, GA_SEED = 8, 8, 1024, 64, 1003
+
+
+def geoattn_workload():
+    """Config: B=8, H=8, N=1024, d_head=64, bf16; Q,K,V ~ N(0,1)/sqrt(d); random-walk chains with lengths
+    uniform in 256..1024 (key-padding mask); sigma_h linear 3..15 A; upstream gradient N(0,1)."""
+    from oracle import chains
+    lengths = chains.draw_lengths(GA_Z, 256, 1024, seed=GA_SEED)
+    coords, mask = chains.chain_batch(lengths, GA_N, seed=GA_SEED)
+    g = torch.Generator().manual_seed(GA_SEED)
+    q, k, v = (torch.randn(GA_Z, GA_H, GA_N, GA_D, generator=g) / GA_D ** 0.5 for _ in range(3))
+    d_out = torch.randn(GA_Z, GA_H, GA_N, GA_D, generator=g)
+    q, k, v, d_out = (t.to(torch.bfloat16) for t in (q, k, v, d_out))
+    return q, k, v, d_out, torch.from_numpy(coords), torch.from_numpy(mask), torch.from_numpy(chains.sigmas(GA_H)), lengths
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        return float(pk["bf16_tflops"]), "measured (MEASURED_PEAKS.json, cuBLAS bf16 burst)"
+    except Exception:  # noqa: BLE001
+        return 1590.0, "fallback (earlier measurement on this pool)"
+
+
+def bench_geoattn(dev, world, rank, steps, dist):
+    """Geometric attention forward+backward, (batch, head) pairs sharded over the ranks.
+    Returns a dict for the JSON line (rank 0) with TFLOP/s on the valid pairs and on the padded shape."""
+    from proteusai_b200.utils.model_utils.attn.geometric_attn import geoattn_backward, geoattn_forward
+    q, k, v, d_out, coords, mask, sig, lengths = geoattn_workload()
+    q, k, v, d_out, coords, mask, sig = (t.to(dev) for t in (q, k, v, d_out, coords, mask, sig))
+    zh = GA_Z * GA_H
+    per = (zh + world - 1) // world
+    z0, z1 = min(zh, rank * per), min(zh, (rank + 1) * per)
+    out = torch.empty(GA_Z, GA_H, GA_N, GA_D, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(GA_Z, GA_H, GA_N, dtype=torch.float32, device=dev)
+
+    def step():
+        geoattn_forward(q, k, v, coords, sig, mask, z0, z1, out, lse)
+        geoattn_backward(q, k, v, out, d_out, lse, coords, sig, mask, z0, z1)
+
+    for _ in range(3):
+        step()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    for a, b in evs:
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    total = sum(a.elapsed_time(b) for a, b in evs)
+    fa, fb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fa.record()
+    for _ in range(steps):
+        geoattn_forward(q, k, v, coords, sig, mask, z0, z1, out, lse)
+    fb.record()
+    torch.cuda.synchronize()
+    fwd_ms = fa.elapsed_time(fb) / steps
+    if world > 1:
+        t = torch.tensor([total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total = float(t.item())
+    ms = total / steps
+    valid_flop = 14.0 * GA_H * GA_D * float((lengths.astype(np.float64) ** 2).sum())
+    padded_flop = 14.0 * GA_Z * GA_H * GA_N * GA_N * GA_D
+    peak, src = measured_peaks()
+    return {"metric": "geo-attn fwd+bwd TFLOP/s (valid pairs)", "value": valid_flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "padded_tflops": padded_flop / (ms * 1e-3) / 1e12, "ms_per_step": ms, "fwd_ms": fwd_ms, "dtype": "bf16",
+            "config": {"workload": "geometric attention fwd+bwd, B=8, H=8, N=1024, d_head=64, lengths U{256..1024}, seed 1003",
+                       "sharding": f"(batch, head) pairs over {world} rank(s)"},
+            "roofline": {"bound": "tensor", "achieved": valid_flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                         "frac": valid_flop / (ms * 1e-3) / 1e12 / peak, "peak_source": src, "traffic": None},
+            "gpu_launches": 3 * steps}
+
+
 def cpu_port_rate(coords, wn, target_s=12.0, chunk=32):
     """Times the oracle (the reference's dense PyTorch formulation, observer-chunked) on the host
     cores on a bounded run of observer rows.  Returns (evals/s, rows used, seconds)."""
@@ -162,6 +239,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--geoattn", action="store_true", help="also run the attention leg when --n-seq is not the default")
     ap.add_argument("--n-seq", type=int, default=N_SEQ, help="sequence length (default: the headline 16384)")
     args = ap.parse_args()
     if args.n_seq != N_SEQ:
@@ -295,10 +373,16 @@ def main():
                          "kernel": "we_fwd_kernel", "kernel_ms": kern_ms,
                          "evals_per_launch": evals_per_launch},
         }
+        line["geoattn"] = None
         if world == 1 and not args.no_cpu_baseline:
             rate, rows, secs = cpu_port_rate(coords_h, wn_h)
             line["cpu_baseline"] = {"value": rate, "unit": "evals/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"{rows} of {N_SEQ} observer rows x all sources x {K_WN} wavenumbers, {secs:.1f} s"}
+    ga = None
+    if N_SEQ == 16384 or args.geoattn:
+        ga = bench_geoattn(dev, world, rank, args.steps, dist)
+    if rank == 0:
+        line["geoattn"] = ga
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -111,6 +111,28 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
                     int zh_begin, int zh_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Geometric attention, backward.
+ * Replaces _geometric_attn.backward (old/old_scripts/attn/geometric_attn.py:610-660): the PyTorch row-sum
+ *   D = sum(O * dO) (:616) and the Triton launch `_attn_bwd[grid](...)` (:640-657; kernel :265-543), for the
+ *   logit form of pai_geoattn_fwd.
+ *
+ *   Q, K, V, O, dO [Z,H,N,d] bf16 contiguous (d must be 64); L [Z,H,N] fp32 as written by the forward
+ *   dQ, dK, dV     [Z,H,N,d] fp32, like the reference's gradients (:626-628); every row of the
+ *                  (batch, head) range is written, rows of padded tokens as zeros; dQ is accumulated
+ *                  across key tiles with reduce-add copies, so its summation order is not fixed
+ *   dsigma         [H] fp32, overwritten: gradient w.r.t. the spreads summed over the (batch, head) range
+ *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned
+ *                  (holds D, one fp32 per query row)
+ *   zh_begin, zh_end  as in the forward
+ */
+size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d);
+int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
+                    const float *coords, const float *sigma, const uint8_t *valid,
+                    float *dQ, float *dK, float *dV, float *dsigma,
+                    void *workspace, size_t workspace_bytes,
+                    int Z, int H, int N, int d, float scale, int zh_begin, int zh_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and
  * returns results per second through *sincos_pairs_per_s (one pair = one sin and one cos, which is
  * what one WE evaluation needs) and the elapsed device time.  Synchronous.  Used as the

@@ -2,6 +2,7 @@
 // the kernels are header files so that the device status word needs no relocatable device code.
 #include "common.cuh"
 
+#include "geoattn_bwd.cuh"
 #include "geoattn_fwd.cuh"
 #include "we_bwd.cuh"
 #include "we_fwd.cuh"
@@ -198,6 +199,74 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     p.scale = scale;
     dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
     pai::geoattn_fwd_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    return (int)cudaPeekAtLastError();
+}
+
+size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
+    (void)d;
+    if (Z < 1 || H < 1 || N < 1) return 0;
+    return (size_t)Z * H * N * sizeof(float);
+}
+
+int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
+                    const float *coords, const float *sigma, const uint8_t *valid, float *dQ, float *dK, float *dV,
+                    float *dsigma, void *workspace, size_t workspace_bytes, int Z, int H, int N, int d, float scale,
+                    int zh_begin, int zh_end, void *stream) {
+    if (!Q || !K || !V || !O || !dO || !L || !coords || !sigma || !dQ || !dK || !dV || !dsigma || !workspace)
+        return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
+    if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
+    if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(dO, 16) || !aligned(dQ, 16) ||
+        !aligned(dK, 16) || !aligned(dV, 16) || !aligned(L, 4) || !aligned(coords, 4) || !aligned(sigma, 4) ||
+        !aligned(dsigma, 4) || !aligned(workspace, 16))
+        return PAI_ERR_MISALIGNED;
+    if (workspace_bytes < pai_geoattn_bwd_workspace_bytes(Z, H, N, d)) return PAI_ERR_WORKSPACE_TOO_SMALL;
+    if (int e = require_sm100()) return e;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce = cudaMemsetAsync(dsigma, 0, (size_t)H * sizeof(float), st);
+    if (ce != cudaSuccess) return (int)ce;
+    if (zh_begin == zh_end) return PAI_OK;
+    const int nzh = zh_end - zh_begin;
+    const size_t rows0 = (size_t)zh_begin * N;
+    const size_t off = rows0 * d * 2;
+    ce = cudaMemsetAsync(dQ + rows0 * d, 0, (size_t)nzh * N * d * sizeof(float), st);
+    if (ce != cudaSuccess) return (int)ce;
+    CUtensorMap mq, mk, mv, mdo;
+    if (int e = pai::make_map_bf16_rows(&mq, (const char *)Q + off, nzh, N, d, pai::GA_BM)) return e;
+    if (int e = pai::make_map_bf16_rows(&mk, (const char *)K + off, nzh, N, d, pai::GA_BN)) return e;
+    if (int e = pai::make_map_bf16_rows(&mv, (const char *)V + off, nzh, N, d, pai::GA_BN)) return e;
+    if (int e = pai::make_map_bf16_rows(&mdo, (const char *)dO + off, nzh, N, d, pai::GA_BM)) return e;
+    const int smem = (int)sizeof(pai::GaBwdSmem) + 1024;
+    static bool attr_done[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_done[dev]) {
+        ce = cudaFuncSetAttribute(pai::geoattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (ce != cudaSuccess) return (int)ce;
+        if (dev >= 0 && dev < 64) attr_done[dev] = true;
+    }
+    float *dsum = (float *)workspace;
+    const long long rows = (long long)nzh * N;
+    pai::geoattn_bwd_dsum_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+        (const __nv_bfloat16 *)O + rows0 * d, (const __nv_bfloat16 *)dO + rows0 * d, dsum, rows);
+    pai::GaBwdParams p;
+    p.coords = coords;
+    p.valid = valid;
+    p.sigma = sigma;
+    p.lse = L;
+    p.dsum = dsum;
+    p.dq = dQ;
+    p.dk = dK;
+    p.dv = dV;
+    p.dsigma = dsigma;
+    p.Z = Z;
+    p.H = H;
+    p.N = N;
+    p.zh_begin = zh_begin;
+    p.scale = scale;
+    dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
+    pai::geoattn_bwd_kernel<<<grid, 128, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();
 }
 

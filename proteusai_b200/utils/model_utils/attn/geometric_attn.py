@@ -44,6 +44,29 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     return out, lse
 
 
+def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0, zh_end=None):
+    """Gradients on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V, O, dO bf16 contiguous.
+    Returns fp32 ``(dQ, dK, dV [Z,H,N,d], d_spreads [H])``; only the pairs of the range are written."""
+    batch, nheads, n, d_k = Q.shape
+    zh_end = batch * nheads if zh_end is None else zh_end
+    dev = Q.device
+    coords = coords.to(torch.float32).contiguous()
+    sigma = spreads.detach().to(torch.float32).contiguous()
+    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    dq, dk, dv = (torch.empty(batch, nheads, n, d_k, dtype=torch.float32, device=dev) for _ in range(3))
+    dsig = torch.empty(nheads, dtype=torch.float32, device=dev)
+    lib = _lib.lib()
+    ws_bytes = lib.pai_geoattn_bwd_workspace_bytes(batch, nheads, n, d_k)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(lib.pai_geoattn_bwd(
+            _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(dO), _lib.ptr(lse), _lib.ptr(coords),
+            _lib.ptr(sigma), _lib.ptr(valid), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig),
+            _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), zh_begin, zh_end,
+            _lib.current_stream()), "pai_geoattn_bwd")
+    return dq, dk, dv, dsig
+
+
 class _geometric_attn(torch.autograd.Function):
 
     @staticmethod
@@ -63,4 +86,8 @@ class _geometric_attn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dO):
-        raise NotImplementedError("geometric_attn backward kernel is not built yet")
+        qb, kb, vb, out, lse, coords, spreads, mask = ctx.saved_tensors
+        mask = mask if ctx.has_mask else None
+        dq, dk, dv, dsig = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads, mask)
+        dt = ctx.in_dtype
+        return dq.to(dt), dk.to(dt), dv.to(dt), None, dsig.to(ctx.spread_dtype), None, None, None, None

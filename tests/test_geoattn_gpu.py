@@ -55,3 +55,45 @@ def test_forward_public_call_and_no_mask(ga):
     assert out.dtype == torch.float32
     ref = geoattn_ref(q.float(), k.float(), v.float(), c, sig)
     assert (out.cpu() - ref).abs().max().item() < ABS_TOL
+
+
+@pytest.mark.parametrize("z,h,n,lengths", [
+    (1, 1, 128, [128]), (1, 2, 256, [256]), (2, 3, 384, [384, 200]), (2, 2, 200, [200, 77]), (3, 2, 513, [513, 129, 1]),
+])
+def test_backward_matches_oracle(ga, z, h, n, lengths):
+    q, k, v, d_out, c, m, sig = _inputs(z, h, n, lengths, seed=7 * n + h, std=1.0)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    sd = sig.cuda().requires_grad_(True)
+    out = ga.geometric_attn(qd, kd, vd, c.cuda(), sd, None, m.cuda())
+    out.backward(d_out.cuda())
+    _, _, dq, dk, dv, dsig = geoattn_grads_closed_form(q.float(), k.float(), v.float(), c, sig, d_out.float(), m, dtype=torch.float64)
+    for name, got, ref in (("dQ", qd.grad, dq), ("dK", kd.grad, dk), ("dV", vd.grad, dv)):
+        err = (got.float().cpu().double() - ref).abs().max().item()
+        # gradients come back in bf16 (the dtype of Q): allow their rounding on top of the 2e-2 budget
+        assert err < ABS_TOL + ref.abs().max().item() * 2 ** -8, (name, err)
+    # 2e-2 relative, plus a floor for sums that nearly cancel (P and dS are rounded to bf16)
+    assert torch.all((sd.grad.cpu().double() - dsig).abs() <= 2e-2 * dsig.abs() + 5e-3), (sd.grad, dsig)
+    pad = m[:, None, :, None].expand(z, h, n, 64)
+    assert torch.all(qd.grad.cpu()[pad] == 0) and torch.all(kd.grad.cpu()[pad] == 0) and torch.all(vd.grad.cpu()[pad] == 0)
+    from proteusai_b200 import _lib
+    _lib.device_status()
+
+
+def test_config3_forward_backward(ga):
+    # B=8, H=8, N=1024, d=64, bf16, lengths uniform in 256..1024, sigma 3..15 A, N(0,1)/sqrt(d) inputs
+    lengths = chains.draw_lengths(8, 256, 1024, seed=1003)
+    q, k, v, d_out, c, m, sig = _inputs(8, 8, 1024, lengths, seed=1003)
+    out, lse = ga.geoattn_forward(q.cuda(), k.cuda(), v.cuda(), c.cuda(), sig.cuda(), m.cuda())
+    dq, dk, dv, dsig = ga.geoattn_backward(q.cuda(), k.cuda(), v.cuda(), out, d_out.cuda(), lse, c.cuda(), sig.cuda(), m.cuda())
+    for b in range(8):  # oracle one sample at a time (fp32 on the bf16-rounded inputs)
+        sl = slice(b, b + 1)
+        o_r, _, dq_r, dk_r, dv_r, ds_r = geoattn_grads_closed_form(
+            q[sl].float(), k[sl].float(), v[sl].float(), c[sl], sig, d_out[sl].float(), m[sl], dtype=torch.float32)
+        assert (out[sl].float().cpu() - o_r).abs().max().item() < ABS_TOL
+        for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r)):
+            assert (got[sl].cpu() - ref).abs().max().item() < ABS_TOL
+        if b == 0:
+            ds_tot = ds_r.double()
+        else:
+            ds_tot += ds_r.double()
+    assert torch.all((dsig.cpu().double() - ds_tot).abs() <= 2e-2 * ds_tot.abs() + 1e-5), (dsig, ds_tot)
