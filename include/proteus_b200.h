@@ -33,7 +33,8 @@ enum pai_status {
     PAI_ERR_WORKSPACE_TOO_SMALL = -5,
     PAI_ERR_BAD_ROW_RANGE = -6,
     PAI_ERR_NOT_SM100 = -7,
-    PAI_ERR_DEVICE_WAIT_TIMEOUT = -8
+    PAI_ERR_DEVICE_WAIT_TIMEOUT = -8,
+    PAI_ERR_EXCEEDS_STATIC_SCRATCH = -9
 };
 
 /* ABI version of this header (bumped on any signature change). */
@@ -87,6 +88,31 @@ size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K);
 int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums, float *dk,
                   void *workspace, size_t workspace_bytes,
                   int Z, int N, int K, int row_begin, int row_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Wavefunction Embedding, backward w.r.t. the wavenumbers, without any caller-provided scratch.
+ * No counterpart in the reference: this entry point exists for callers that cannot allocate device
+ * memory at the time of the call, for example a serving process that handed the whole GPU to its own
+ * memory pool at start-up and treats any later cudaMalloc as an error, or code that runs where the
+ * implicit device-wide synchronisation of cudaMalloc/cudaFree is not acceptable.  Such a caller has no
+ * buffer to pass as `workspace` to pai_we_bwd_dk, so the partial sums go to an array that is part of
+ * the library image.
+ *
+ * Same arguments, same arithmetic and same result as pai_we_bwd_dk minus (workspace, workspace_bytes).
+ *   - Limit: K <= pai_we_bwd_dk_static_max_k() (1024, i.e. d_model <= 2048); a larger K returns
+ *     PAI_ERR_EXCEEDS_STATIC_SCRATCH and nothing is launched.  Every GPU that loads the library holds the
+ *     array (592 * 1024 floats, about 2.3 MiB) until the process exits, used or not.
+ *   - The call itself performs no cudaMalloc, cudaFree or other allocation.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current) and keeps it; make that first call before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the last call left in it.
+ *     Nothing in it needs clearing between calls (each call overwrites every element it later reads),
+ *     but two calls that overlap in time on the same GPU, e.g. on two streams, race on it and
+ *     give wrong results: serialise them, or use pai_we_bwd_dk with separate workspaces.
+ */
+int pai_we_bwd_dk_static_max_k(void);
+int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *sin_sums, float *dk,
+                         int Z, int N, int K, int row_begin, int row_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, forward.

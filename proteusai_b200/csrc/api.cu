@@ -82,6 +82,8 @@ const char *pai_status_str(int status) {
         case PAI_ERR_BAD_ROW_RANGE: return "bad row range (need 0 <= begin <= end <= N)";
         case PAI_ERR_NOT_SM100: return "current device is not sm_100 (B200)";
         case PAI_ERR_DEVICE_WAIT_TIMEOUT: return "a kernel gave up on a bounded device-side wait";
+        case PAI_ERR_EXCEEDS_STATIC_SCRATCH:
+            return "size exceeds the built-in scratch of the allocation-free entry point (K > 1024); use the workspace variant";
         default: break;
     }
     if (status > 0) return cudaGetErrorString((cudaError_t)status);
@@ -268,6 +270,46 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
     pai::geoattn_bwd_kernel<<<grid, 128, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();
+}
+
+// ---- allocation-free variant of the WE backward --------------------------------------------------
+// Scratch for the per-block partial sums lives in the library image instead of a caller buffer.
+// Every GPU that loads the library carries this array (about 2.3 MiB) until the process exits.
+#define PAI_WE_BWD_STATIC_MAX_K 1024
+static __device__ __align__(256) float g_we_bwd_static_scratch[pai::WE_BWD_MAX_BLOCKS * PAI_WE_BWD_STATIC_MAX_K];
+
+int pai_we_bwd_dk_static_max_k(void) { return PAI_WE_BWD_STATIC_MAX_K; }
+
+int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *sin_sums, float *dk, int Z, int N, int K,
+                         int row_begin, int row_end, void *stream) {
+    if (!dO || !cos_sums || !sin_sums || !dk) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || (long long)Z * N > (1ll << 30)) return PAI_ERR_BAD_SHAPE;
+    if (K > PAI_WE_BWD_STATIC_MAX_K) return PAI_ERR_EXCEEDS_STATIC_SCRATCH;
+    if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(dO, 8) || !aligned(cos_sums, 4) || !aligned(sin_sums, 4) || !aligned(dk, 4)) return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    // The array's name is only a host-side handle here; the kernels need its device address, which
+    // differs per GPU.  Looked up once per device, with that device current, and kept.
+    static float *scratch_on_device[64];
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return (int)ce;
+    if (dev < 0 || dev >= 64) return PAI_ERR_UNSUPPORTED;
+    float *scratch = scratch_on_device[dev];
+    if (!scratch) {
+        ce = cudaGetSymbolAddress((void **)&scratch, g_we_bwd_static_scratch);
+        if (ce != cudaSuccess) return (int)ce;
+        if (!scratch) return PAI_ERR_UNSUPPORTED;
+        scratch_on_device[dev] = scratch;
+    }
+    if (row_begin == row_end) {
+        // nothing to sum: the result is zero; written by the final-pass kernel over zero partial rows
+        pai::we_bwd_final_kernel<<<(K + pai::WE_BWD_THREADS - 1) / pai::WE_BWD_THREADS, pai::WE_BWD_THREADS, 0,
+                                   (cudaStream_t)stream>>>(scratch, dk, K, 0);
+        return (int)cudaPeekAtLastError();
+    }
+    // Pass 1 overwrites every partial row that pass 2 reads, so nothing in the array has to start at zero.
+    return pai::we_bwd_launch(dO, cos_sums, sin_sums, dk, scratch, Z, N, K, row_begin, row_end, (cudaStream_t)stream);
 }
 
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {
