@@ -131,9 +131,8 @@ def bench_geoattn(dev, world, rank, steps, dist):
     from proteusai_b200.utils.model_utils.attn.geometric_attn import geoattn_backward, geoattn_forward
     q, k, v, d_out, coords, mask, sig, lengths = geoattn_workload()
     q, k, v, d_out, coords, mask, sig = (t.to(dev) for t in (q, k, v, d_out, coords, mask, sig))
-    zh = GA_Z * GA_H
-    per = (zh + world - 1) // world
-    z0, z1 = min(zh, rank * per), min(zh, (rank + 1) * per)
+    from proteusai_b200 import sharding
+    z0, z1 = sharding.shard_range(GA_Z * GA_H, world, rank)
     out = torch.empty(GA_Z, GA_H, GA_N, GA_D, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(GA_Z, GA_H, GA_N, dtype=torch.float32, device=dev)
 
@@ -266,25 +265,17 @@ def main():
     coords_h, wn_h = workload()
     coords_pin, wn_pin = coords_h.pin_memory(), wn_h.pin_memory()
     coords_d, wn_d = coords_h.to(dev), wn_h.to(dev)
-    rows_per = (N_SEQ + world - 1) // world
-    r0, r1 = rank * rows_per, min(N_SEQ, (rank + 1) * rows_per)
+    from proteusai_b200 import sharding
+    r0, r1 = sharding.shard_range(N_SEQ, world, rank)
     out = torch.empty(1, N_SEQ, 2 * K_WN, device=dev)
     cs = torch.empty(1, N_SEQ, K_WN, device=dev)
     sn = torch.empty(1, N_SEQ, K_WN, device=dev)
-    out_flat = out.view(-1)
-    shard_flat = out_flat[r0 * 2 * K_WN:r1 * 2 * K_WN]
-    even = (N_SEQ % world) == 0
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
-    out_host = torch.empty(r1 - r0, 2 * K_WN).pin_memory()
+    out_host = torch.empty(max(r1 - r0, 1), 2 * K_WN).pin_memory()
 
     def step_resident():
         we_forward_rows(coords_d, wn_d, 1, None, r0, r1, out, cs, sn)
-        if world > 1:
-            if even:
-                dist.all_gather_into_tensor(out_flat, shard_flat)
-            else:
-                parts = [out_flat[i * rows_per * 2 * K_WN:min(N_SEQ, (i + 1) * rows_per) * 2 * K_WN] for i in range(world)]
-                dist.all_gather(parts, shard_flat)
+        sharding.all_gather_rows(out[0], N_SEQ, r0, r1)
 
     def step_e2e():
         c = coords_pin.to(dev, non_blocking=True)
@@ -294,9 +285,8 @@ def main():
             out_host.copy_(o[0], non_blocking=True)
         else:
             we_forward_rows(c, w, 1, None, r0, r1, out, cs, sn)
-            if even:
-                dist.all_gather_into_tensor(out_flat, shard_flat)
-            out_host.copy_(out[0, r0:r1], non_blocking=True)
+            sharding.all_gather_rows(out[0], N_SEQ, r0, r1)
+            out_host[:r1 - r0].copy_(out[0, r0:r1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     def barrier():

@@ -34,6 +34,24 @@ int current_device_cc(int *cc_out) {
     return 0;
 }
 
+int current_device_sms(int *sms_out) {
+    static int cache[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64 && cache[dev]) {
+        *sms_out = cache[dev];
+        return 0;
+    }
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (sms < 1) return (int)PAI_ERR_UNSUPPORTED;
+    *sms_out = sms;
+    if (dev >= 0 && dev < 64) cache[dev] = sms;
+    return 0;
+}
+
 int require_sm100() {
     int cc = 0;
     int e = current_device_cc(&cc);
@@ -133,8 +151,22 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     p.mag_type = magnitude_type;
     // bulk copies need 16-byte aligned plane segments: base aligned and N a multiple of 4
     p.use_tma = (aligned(coords_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
-    return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_RANGE_REDUCE", 0) != 0,
-                              (cudaStream_t)stream);
+    // the kernel adds partial sums into the outputs: zero the rows of the shard first
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t rows = (size_t)(row_end - row_begin);
+    cudaError_t ce = cudaMemset2DAsync(out + (size_t)row_begin * 2 * K, (size_t)N * 2 * K * sizeof(float), 0,
+                                       rows * 2 * K * sizeof(float), (size_t)Z, st);
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaMemset2DAsync(cos_sums + (size_t)row_begin * K, (size_t)N * K * sizeof(float), 0, rows * K * sizeof(float),
+                           (size_t)Z, st);
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaMemset2DAsync(sin_sums + (size_t)row_begin * K, (size_t)N * K * sizeof(float), 0, rows * K * sizeof(float),
+                           (size_t)Z, st);
+    if (ce != cudaSuccess) return (int)ce;
+    int sms = 0;
+    if (int e = current_device_sms(&sms)) return e;
+    return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_TJ", 0), env_int("PAI_WE_WAVES", 0),
+                              env_int("PAI_WE_REPRODUCIBLE", 0) != 0, env_int("PAI_WE_RANGE_REDUCE", 0) != 0, sms, st);
 }
 
 size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {

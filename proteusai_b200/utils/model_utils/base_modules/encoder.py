@@ -1,0 +1,98 @@
+"""``GeoAttention`` and ``Encoder`` modules over the B200 geometric-attention kernel, and the small
+encoder-only model used as the end-to-end inference configuration.
+
+``GeoAttention`` keeps the reference's constructor, parameter names and semantics
+(``old/old_scripts/encoder.py:43-121``): per-head projection weights ``q_proj/k_proj/v_proj [H, d_model, d_k]``
+with biases ``[H, d_k]``, ``spreads = min_spread + exp(spread_weights)``, ``betas = exp(beta_weights)``,
+heads concatenated d_k-major / head-minor before the bias-free ``out_proj``.  The three projections run as one
+batched GEMM each that writes ``[Z, H, N, d_k]`` directly, the layout the kernel's TMA maps read.
+
+``Encoder`` is the reference's post-norm block (``old/old_scripts/encoder.py:8-41``): ``LN(x + drop(attn))``
+then ``LN(x + drop(ffn))``.  The reference's ``forward`` passes ``coords_beta`` positionally into a
+``GeoAttention.forward`` that has no such parameter (a TypeError there); here it is accepted and unused.
+"""
+import torch
+import torch.nn as nn
+
+from proteusai_b200.utils.model_utils.attn.geometric_attn import geometric_attn
+from proteusai_b200.utils.model_utils.base_modules.base_modules import MLP
+from proteusai_b200.utils.model_utils.wf_embedding.wf_embedding import WaveFunctionEmbedding
+
+
+class GeoAttention(nn.Module):
+
+    def __init__(self, d_model=512, heads=8, min_spread=2.0, min_rbf=0.001, max_rbf=1.00, learn_spreads=True):
+        super().__init__()
+        if d_model % heads != 0:
+            raise ValueError(f"number of dimensions ({d_model}) must be divisible by number of attention heads ({heads})")
+        self.heads, self.d_model, self.d_k = heads, d_model, d_model // heads
+        self.spread_weights = nn.Parameter(torch.zeros(heads), requires_grad=learn_spreads)
+        self.beta_weights = nn.Parameter(torch.zeros(heads))
+        self.min_spread, self.min_rbf, self.max_rbf = min_spread, min_rbf, max_rbf
+        bound = (6 / (self.d_k + d_model)) ** 0.5  # Xavier-uniform
+        for name in ("q", "k", "v"):
+            setattr(self, f"{name}_proj", nn.Parameter((torch.rand(heads, d_model, self.d_k) * 2 - 1) * bound))
+            setattr(self, f"{name}_bias", nn.Parameter(torch.zeros(heads, self.d_k)))
+        self.out_proj = nn.Linear(d_model, d_model, bias=False)
+
+    def get_spreads(self):
+        return self.min_spread + torch.exp(self.spread_weights)
+
+    def get_betas(self):
+        return torch.exp(self.beta_weights)
+
+    def _project(self, x, w, b):
+        # [Z,N,D] x [H,D,dk] -> [Z,H,N,dk]
+        return torch.matmul(x.unsqueeze(1), w.to(x.dtype).unsqueeze(0)) + b.to(x.dtype)[None, :, None, :]
+
+    def forward(self, q, k, v, coords, mask=None, flash=True):
+        assert q.shape == k.shape == v.shape and q.dim() == 3 and q.shape[2] == self.d_model
+        batch, n, _ = q.shape
+        Q = self._project(q, self.q_proj, self.q_bias)
+        K = self._project(k, self.k_proj, self.k_bias)
+        V = self._project(v, self.v_proj, self.v_bias)
+        out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
+                             min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
+        out = out.permute(0, 2, 3, 1).reshape(batch, n, self.d_model)  # d_k-major, head-minor
+        return self.out_proj(out)
+
+
+class Encoder(nn.Module):
+
+    def __init__(self, d_model=512, heads=8, min_spread=2.0, min_rbf=0.001, d_hidden=2048, hidden_layers=0,
+                 dropout=0.10, learn_spreads=True):
+        super().__init__()
+        self.attn = GeoAttention(d_model=d_model, heads=heads, min_spread=min_spread, min_rbf=min_rbf, learn_spreads=learn_spreads)
+        self.attn_norm = nn.LayerNorm(d_model)
+        self.ffn = MLP(d_in=d_model, d_out=d_model, d_hidden=d_hidden, hidden_layers=hidden_layers, dropout=dropout)
+        self.ffn_norm = nn.LayerNorm(d_model)
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, q, k, v, coords, coords_beta=None, mask=None):
+        q = self.attn_norm(q + self.dropout(self.attn(q, k, v, coords, mask=mask)))
+        return self.ffn_norm(q + self.dropout(self.ffn(q)))
+
+
+class ProteusEncoderModel(nn.Module):
+    """Token embedding (vocabulary 33) added to the wavefunction embedding, ``layers`` post-norm encoder
+    blocks with geometric attention, a linear head to 20 amino-acid logits (the model of the reference
+    README, ``README.md:38,48``, from the modules above)."""
+
+    def __init__(self, d_model=512, heads=8, layers=4, d_hidden=2048, vocab=33, n_out=20, sigma_lo=3.0, sigma_hi=15.0,
+                 min_wl=3.7, max_wl=20.0, base_wl=20.0):
+        super().__init__()
+        self.embed = nn.Embedding(vocab, d_model)
+        self.wf_embedding = WaveFunctionEmbedding(d_wf=d_model, min_wl=min_wl, max_wl=max_wl, base_wl=base_wl, anisotropic=False)
+        self.encoders = nn.ModuleList(Encoder(d_model=d_model, heads=heads, d_hidden=d_hidden, dropout=0.0) for _ in range(layers))
+        self.head = nn.Linear(d_model, n_out)
+        # spreads linearly spaced in [sigma_lo, sigma_hi]: spread = min_spread + exp(w)
+        sig = torch.linspace(sigma_lo, sigma_hi, heads)
+        for enc in self.encoders:
+            enc.attn.spread_weights.data = torch.log(sig - enc.attn.min_spread)
+
+    def forward(self, tokens, coords, mask=None):
+        wf = self.wf_embedding(coords, None, key_padding_mask=mask)  # fp32 [Z,N,d_model]
+        x = self.embed(tokens) + wf.to(self.embed.weight.dtype)
+        for enc in self.encoders:
+            x = enc(x, x, x, coords, mask=mask)
+        return self.head(x)

@@ -130,15 +130,17 @@ def test_row_shards_and_code_paths_agree(we, monkeypatch):
     c_t, m_t = torch.from_numpy(c).cuda(), torch.from_numpy(m).cuda()
     wn = torch.from_numpy(chains.wavenumbers(128)).cuda()
     full, fcs, fsn = we.we_forward_rows(c_t, wn, 1, m_t)
-    # the union of row shards reproduces the full result bit for bit
+    # the union of row shards reproduces the full result (the even partition of the work cuts the sums at
+    # different places for different shard sizes, so agreement is to rounding, not bit for bit)
     out = torch.full_like(full, float("nan"))
     cs, sn = torch.full_like(fcs, float("nan")), torch.full_like(fsn, float("nan"))
     for a, b in ((0, 175), (175, 350), (350, 525), (525, 700)):
         we.we_forward_rows(c_t, wn, 1, m_t, a, b, out, cs, sn)
-    assert torch.equal(out, full) and torch.equal(cs, fcs) and torch.equal(sn, fsn)
+    assert not torch.isnan(out).any()
+    assert rel_l2(full, out) < 1e-6 and rel_l2(fcs, cs) < 1e-6 and rel_l2(fsn, sn) < 1e-6
     ref = wf_embedding_ref(c_t.cpu(), wn.cpu(), 1, m_t.cpu(), dtype=torch.float64)
     for env in ({"PAI_WE_NO_TMA": "1"}, {"PAI_WE_KS": "8"}, {"PAI_WE_KS": "2"}, {"PAI_WE_RANGE_REDUCE": "1"},
-                {"PAI_WE_KS": "16"}):
+                {"PAI_WE_KS": "16"}, {"PAI_WE_TJ": "64"}, {"PAI_WE_TJ": "512"}, {"PAI_WE_TJ": "36", "PAI_WE_NO_TMA": "1"}):
         for key, val in env.items():
             monkeypatch.setenv(key, val)
         alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
@@ -157,13 +159,19 @@ def test_unaligned_n_uses_plain_loads(we):
     assert rel_l2(wf_embedding_ref(c_t, wn, 1, dtype=torch.float64), out.cpu()) < OUT_TOL
 
 
-def test_config4_long_sequence_slice_and_properties(we):
+def test_config4_long_sequence_slice_and_properties(we, monkeypatch):
     n = 16384
     c, _ = chains.chain_batch([n], n, seed=1004)
     c_t, wn_t = torch.from_numpy(c), torch.from_numpy(chains.wavenumbers(512))
-    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
+    # reproducible mode: bit-identical from run to run
+    monkeypatch.setenv("PAI_WE_REPRODUCIBLE", "1")
+    first, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
     again, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
-    assert torch.equal(out, again), "the forward is deterministic"
+    assert torch.equal(first, again)
+    monkeypatch.delenv("PAI_WE_REPRODUCIBLE")
+    # default mode: more, shorter runs; sums may differ in the last bit only
+    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
+    assert rel_l2(first, out) < 1e-6
     rows = (8000, 8256)
     ref64 = wf_embedding_ref(c_t, wn_t, 1, rows=rows, chunk=32, dtype=torch.float64)
     err = rel_l2(ref64, out[:, rows[0]:rows[1]].cpu())
