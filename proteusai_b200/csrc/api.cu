@@ -232,7 +232,7 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     p.zh_begin = zh_begin;
     p.scale = scale;
     dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
-    pai::geoattn_fwd_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
 }
 
