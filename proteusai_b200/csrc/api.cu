@@ -300,7 +300,7 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.zh_begin = zh_begin;
     p.scale = scale;
     dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
-    pai::geoattn_bwd_kernel<<<grid, 128, smem, st>>>(mq, mk, mv, mdo, p);
+    pai::geoattn_bwd_kernel<<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();
 }
 

@@ -11,24 +11,30 @@
 //     dS    = dSR (1 + R) scale        -> dQ_i = sum_j dS_ij K_j,   dK_j = sum_i dS_ij Q_i
 //     dsigma_h = sum_{z,i,j} dSR S R d^2 / sigma_h^3
 //
-// One CTA = 128 keys of one (batch, head); it loops over the 128-row query tiles.  Thread t owns
-// query row t of the current tile = TMEM lane t.  Five MMAs per query tile, all operands straight
-// from the TMA-written swizzled tiles, transposes expressed through the operand major-ness:
+// One CTA = 128 keys of one (batch, head); it loops over the 128-row query tiles.  16 math warps and one
+// producer warp: query row r = TMEM lane r of the current tile is shared by four math threads (warps
+// w, w+4, w+8, w+12), each taking 32 of the 128 key columns; no row reduction is needed in the backward
+// because the log-sum-exp L and D are known.  Lane 0 of the producer warp issues every TMA load and MMA.
+// Five MMAs per query tile, all operands straight from the TMA-written swizzled tiles, transposes
+// expressed through the operand major-ness:
 //     S   = Q_i K_j^T     A K-major,  B K-major     -> TMEM [128 x 128]
 //     dP  = dO_i V_j^T    A K-major,  B K-major     -> TMEM [128 x 128]
 //     dV += P^T dO_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
 //     dK += dS^T Q_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
 //     dQ_i = dS K_j       A K-major,  B MN-major    -> TMEM [128 x 64], reduced into global fp32 dQ
-//                                                      with bulk reduce-add copies (one per warp)
-// P and dS are written by the threads as bf16 into shared memory in the swizzled [i][j] layout,
-// which serves both as K-major (dQ) and MN-major (dV, dK) operand.  Query tiles without a valid
-// query are skipped, a key tile without a valid key only writes zeros.
+//                                                      with bulk reduce-add copies (one per 32 rows)
+// P and dS are written by the math threads as bf16 into shared memory in the swizzled [i][j] layout,
+// which serves both as K-major (dQ) and MN-major (dV, dK) operand.  The element-wise stage runs in
+// packed fp32x2 arithmetic with |r_i - r_j|^2 from centred coordinates (three FMAs).  Query tiles
+// without a valid query are skipped, a key tile without a valid key only writes zeros.
 #pragma once
 #include "geoattn_fwd.cuh"
 
 namespace pai {
 
 constexpr uint32_t GA_BWD_TMEM_COLS = 512;
+constexpr int GA_BWD_MATH_THREADS = 512;
+constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 32;  // + the producer warp
 
 struct GaBwdSmem {
     alignas(1024) uint8_t k[GA_TILE_BYTES];
@@ -38,12 +44,17 @@ struct GaBwdSmem {
     alignas(1024) uint8_t p[2 * GA_TILE_BYTES];
     alignas(1024) uint8_t ds[2 * GA_TILE_BYTES];
     alignas(1024) float dq[GA_BM * GA_D];  // fp32 staging for the reduce-add, row-major
-    float4 kc[GA_BN];                      // key {x, y, z, valid}
+    // centred key coordinates, two keys per entry:
+    float4 ka[GA_BN / 2];                  // {x_j, x_j+1, y_j, y_j+1}
+    float4 kc[GA_BN / 2];                  // {z_j, z_j+1, |k_j|^2, |k_j+1|^2}
+    alignas(16) float kb[GA_BN];           // additive mask: 0 for a valid key, -inf for a padded one
     uint16_t tiles[GA_MAX_TILES];          // query tiles that hold at least one valid query
-    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_g;
+    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_g, bar_pds, bar_dqr;
     uint32_t tmem_base;
     int ntiles;
-    float dsig[4];
+    int first_k;                           // first valid key of the tile (origin of the centring)
+    int has_hole;                          // the key tile holds a padded or out-of-range key
+    float dsig[GA_BWD_MATH_THREADS / 32];
 };
 
 struct GaBwdParams {
@@ -83,12 +94,93 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-__global__ void __launch_bounds__(128, 1)
+// barrier among the four math warps that share 32 query rows (immediate ids, see named_bar_sync)
+__device__ __forceinline__ void group_bar_sync(int quarter) {
+    switch (quarter) {
+        case 0: named_bar_sync<1>(128); break;
+        case 1: named_bar_sync<2>(128); break;
+        case 2: named_bar_sync<3>(128); break;
+        default: named_bar_sync<4>(128); break;
+    }
+}
+
+struct GaBwdRow {  // per-thread constants of the current query row, packed for fp32x2 arithmetic
+    f2_t qx2, qy2, qz2, cqn2, l22, dsum2;
+};
+
+// 16 key columns (8 pairs) of one query row: recompute P, form dS and the spread-gradient term, write P and
+// dS as bf16 into the swizzled [i][j] tiles.  `chunk0` is the index of the first 16-byte chunk (8 keys).
+template <bool MASKED>
+__device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const float4 *ka, const float4 *kc, const float *kb,
+                                             const GaBwdRow &rw, f2_t crbf2, f2_t cs2, f2_t scale2, f2_t &dsig2, uint8_t *p_tile,
+                                             uint8_t *ds_tile, int r, int chunk0) {
+    uint32_t sv[16], dpv[16];
+    tmem_ld16(t_s, sv);
+    tmem_ld16(t_dp, dpv);
+    const f2_t one2 = f2_pack(1.f, 1.f);
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {  // 8 keys = one 16-byte chunk
+        f2_t arg[4], rb[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float4 a = ka[g * 4 + e], k4 = kc[g * 4 + e];
+            f2_t d2 = f2_fma(rw.qz2, f2_pack(k4.x, k4.y), f2_pack(k4.z, k4.w));
+            d2 = f2_fma(rw.qy2, f2_pack(a.z, a.w), d2);
+            d2 = f2_fma(rw.qx2, f2_pack(a.x, a.y), d2);
+            arg[e] = f2_fma(d2, crbf2, rw.cqn2);  // c_rbf * d^2
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float a0, a1;
+            f2_unpack(arg[e], a0, a1);
+            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
+        }
+        if (g == 0) tmem_wait_ld();
+        uint32_t pw[4], dw[4];
+        f2_t x[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
+            const f2_t t2 = f2_mul(s_raw, cs2);
+            f2_t sr = f2_fma(t2, rb[e], t2);
+            if (MASKED) sr = f2_add(sr, *reinterpret_cast<const f2_t *>(kb + g * 8 + 2 * e));
+            x[e] = f2_sub(sr, rw.l22);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float a0, a1;
+            f2_unpack(x[e], a0, a1);
+            x[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // P
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
+            const f2_t dp = f2_pack(__uint_as_float(dpv[g * 8 + 2 * e]), __uint_as_float(dpv[g * 8 + 2 * e + 1]));
+            const f2_t dsr = f2_mul(x[e], f2_sub(dp, rw.dsum2));
+            const f2_t ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
+            dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
+            float p0, p1, d0, d1;
+            f2_unpack(x[e], p0, p1);
+            f2_unpack(ds, d0, d1);
+            pw[e] = pack_bf16x2(p0, p1);
+            dw[e] = pack_bf16x2(d0, d1);
+        }
+        const int chunk = chunk0 + g;
+        const uint32_t off = (chunk >> 3) * GA_TILE_BYTES + sw128_offset(r, chunk & 7);
+        *reinterpret_cast<uint4 *>(p_tile + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+        *reinterpret_cast<uint4 *>(ds_tile + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+    }
+}
+
+__global__ void __launch_bounds__(GA_BWD_THREADS, 1)
 geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const GaBwdParams p) {
     extern __shared__ uint8_t smem_raw[];
     GaBwdSmem &sm = *reinterpret_cast<GaBwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
+    const int qtr = (warp >> 2) & 3;              // which 32 key columns / which 16 output columns
+    const int r = (warp & 3) * 32 + lane;         // row inside a tile = TMEM lane
     const int zh_local = blockIdx.y;
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
@@ -97,21 +189,25 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float *cz = p.coords + (size_t)z * N * 3;
     const uint8_t *vz = p.valid ? p.valid + (size_t)z * N : nullptr;
 
-    // ---- this thread's key (for the staging of coordinates and the final dK / dV row) -------------
-    const int jrow = j0 + tid;
-    const bool k_ok = jrow < N && (vz ? vz[jrow] != 0 : true);
-    {
-        float4 c = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (k_ok) c = make_float4(cz[jrow * 3], cz[jrow * 3 + 1], cz[jrow * 3 + 2], 1.f);
-        sm.kc[tid] = c;
+    // ---- this CTA's keys ---------------------------------------------------------------------------
+    const int jrow = j0 + r;  // the key whose dK / dV row this thread writes (16 of its 64 columns)
+    const bool k_ok = is_math && jrow < N && (vz ? vz[jrow] != 0 : true);
+    if (tid == 0) {
+        sm.first_k = 0x7fffffff;
+        sm.has_hole = 0;
     }
     // ---- query tiles with at least one valid query --------------------------------------------------
     const int all_tiles = (N + GA_BM - 1) / GA_BM;
-    for (int t = warp; t < all_tiles; t += 4) {
+    for (int t = warp; t < all_tiles; t += GA_BWD_THREADS / 32) {
         bool any = false;
         for (int i = t * GA_BM + lane; i < min(N, (t + 1) * GA_BM); i += 32) any |= vz ? (vz[i] != 0) : true;
         any = __any_sync(0xffffffffu, any);
         if (lane == 0) sm.tiles[t] = any ? 1 : 0;
+    }
+    __syncthreads();
+    if (is_math && qtr == 0) {
+        if (k_ok) atomicMin(&sm.first_k, r);
+        else sm.has_hole = 1;
     }
     const bool cta_has_key = __syncthreads_or(k_ok ? 1 : 0) != 0;
     if (tid == 0) {
@@ -123,213 +219,241 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     const int nt = sm.ntiles;
 
-    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D;
-    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D;
+    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + qtr * 16;
+    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + qtr * 16;
     if (!cta_has_key || nt == 0) {
-        if (jrow < N) {
+        if (is_math && jrow < N) {
 #pragma unroll
-            for (int c = 0; c < GA_D / 4; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 reinterpret_cast<float4 *>(dk_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
                 reinterpret_cast<float4 *>(dv_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
         return;
     }
+    // origin of the centred coordinates: the first valid key of this tile
+    const int ok_row = j0 + sm.first_k;
+    const float orx = cz[ok_row * 3], ory = cz[ok_row * 3 + 1], orz = cz[ok_row * 3 + 2];
+    const bool has_hole = sm.has_hole != 0;
+    if (is_math && qtr == 0) {  // stage the centred keys
+        const float x = k_ok ? cz[jrow * 3] - orx : 0.f, y = k_ok ? cz[jrow * 3 + 1] - ory : 0.f, zc = k_ok ? cz[jrow * 3 + 2] - orz : 0.f;
+        float *a = reinterpret_cast<float *>(&sm.ka[r >> 1]);
+        float *c = reinterpret_cast<float *>(&sm.kc[r >> 1]);
+        a[r & 1] = x;
+        a[2 + (r & 1)] = y;
+        c[r & 1] = zc;
+        c[2 + (r & 1)] = x * x + y * y + zc * zc;
+        sm.kb[r] = k_ok ? 0.f : -INFINITY;
+    }
 
     // ---- set-up ------------------------------------------------------------------------------------
-    if (warp == 0) {
+    if (!is_math) {
         tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
         tmem_relinquish();
-    }
-    if (tid == 0) {
-        mbar_init(&sm.bar_kv, 1);
-        mbar_init(&sm.bar_qdo[0], 1);
-        mbar_init(&sm.bar_qdo[1], 1);
-        mbar_init(&sm.bar_sp, 1);
-        mbar_init(&sm.bar_g, 1);
-        mbar_fence_init();
-        fence_proxy_async();
-        tma_prefetch_desc(&map_q);
-        tma_prefetch_desc(&map_k);
-        tma_prefetch_desc(&map_v);
-        tma_prefetch_desc(&map_do);
+        if (lane == 0) {
+            mbar_init(&sm.bar_kv, 1);
+            mbar_init(&sm.bar_qdo[0], 1);
+            mbar_init(&sm.bar_qdo[1], 1);
+            mbar_init(&sm.bar_sp, 1);
+            mbar_init(&sm.bar_g, 1);
+            mbar_init(&sm.bar_pds, GA_BWD_MATH_THREADS);
+            mbar_init(&sm.bar_dqr, GA_BWD_MATH_THREADS);
+            mbar_fence_init();
+            fence_proxy_async();
+            tma_prefetch_desc(&map_q);
+            tma_prefetch_desc(&map_k);
+            tma_prefetch_desc(&map_v);
+            tma_prefetch_desc(&map_do);
+        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
     const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_dv = tmem + 256, tm_dk = tmem + 320, tm_dq = tmem + 384;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p), ds_addr = smem_u32(sm.ds);
-    constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, 128, false, false);
-    constexpr uint32_t IDESC_TT = umma_idesc_bf16(128, GA_D, true, true);   // dV, dK
-    constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, GA_D, false, true);  // dQ
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-    auto load_qdo = [&](int buf, int tile) {  // thread 0 only
-        mbar_expect_tx(&sm.bar_qdo[buf], 2 * GA_TILE_BYTES);
-        tma_load_3d(sm.q[buf], &map_q, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
-        tma_load_3d(sm.dout[buf], &map_do, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
-    };
-    auto issue_s_dp = [&](int buf) {
-        const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
-#pragma unroll
-        for (int kk = 0; kk < GA_D / 16; ++kk)
-            umma_ss(tm_s, umma_desc_sw128(q_addr + kk * 32, 16, 1024), umma_desc_sw128(k_addr + kk * 32, 16, 1024), IDESC_SP,
-                    kk > 0 ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < GA_D / 16; ++kk)
-            umma_ss(tm_dp, umma_desc_sw128(do_addr + kk * 32, 16, 1024), umma_desc_sw128(v_addr + kk * 32, 16, 1024), IDESC_SP,
-                    kk > 0 ? 1u : 0u);
-        umma_commit(&sm.bar_sp);
-    };
-    auto issue_grads = [&](int buf, bool first) {
-        const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
-#pragma unroll
-        for (int kk = 0; kk < GA_BM / 16; ++kk) {  // K = 16 query rows per step: 2 KiB down the [i][j] tiles
-            umma_ss(tm_dv, umma_desc_sw128(p_addr + kk * 2048, GA_TILE_BYTES, 1024), umma_desc_sw128(do_addr + kk * 2048, 0, 1024),
-                    IDESC_TT, (first && kk == 0) ? 0u : 1u);
-            umma_ss(tm_dk, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024), umma_desc_sw128(q_addr + kk * 2048, 0, 1024),
-                    IDESC_TT, (first && kk == 0) ? 0u : 1u);
-        }
-#pragma unroll
-        for (int kk = 0; kk < GA_BN / 16; ++kk)  // K = 16 keys per step
-            umma_ss(tm_dq, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                    umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_DQ, kk > 0 ? 1u : 0u);
-        umma_commit(&sm.bar_g);
-    };
-
-    if (tid == 0) {
-        mbar_expect_tx(&sm.bar_kv, 2 * GA_TILE_BYTES);
-        tma_load_3d(sm.k, &map_k, 0, j0, zh_local, &sm.bar_kv);
-        tma_load_3d(sm.v, &map_v, 0, j0, zh_local, &sm.bar_kv);
-        load_qdo(0, sm.tiles[0]);
-        if (nt > 1) load_qdo(1, sm.tiles[1]);
-        mbar_wait_timed(&sm.bar_kv, 0);
-        mbar_wait_timed(&sm.bar_qdo[0], 0);
-        tc_fence_after();
-        issue_s_dp(0);
-    }
-
-    const float sig = p.sigma[h];
-    const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
-    const float c_s = p.scale * 1.4426950408889634f;
-    float dsig_acc = 0.f;
-    float *stage = sm.dq + warp * 32 * GA_D;  // this warp's 32 rows of the reduce-add staging
-
-    for (int t = 0; t < nt; ++t) {
-        const int buf = t & 1;
-        const uint32_t par = (uint32_t)(t & 1);
-        const int i0 = sm.tiles[t] * GA_BM;
-        const int row = i0 + tid;
-        // per-row inputs of this query tile (overlaps the S / dP MMAs)
-        const bool q_ok = row < N && (vz ? vz[row] != 0 : true);
-        float qx = 0.f, qy = 0.f, qz = 0.f, l2 = 0.f, dsum = 0.f;
-        if (q_ok) {
-            qx = cz[row * 3];
-            qy = cz[row * 3 + 1];
-            qz = cz[row * 3 + 2];
-            l2 = p.lse[(size_t)zh * N + row] * 1.4426950408889634f;
-            dsum = p.dsum[(size_t)zh_local * N + row];
-        }
-        mbar_wait_timed(&sm.bar_sp, par);
-        tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < GA_BN / 32; ++c) {
-            uint32_t sv[32], dpv[32];
-            tmem_ld32(tm_s + lane_base + c * 32, sv);
-            tmem_ld32(tm_dp + lane_base + c * 32, dpv);
-            tmem_wait_ld();
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {  // 8 keys = one 16-byte chunk
-                float pe[8], de[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int j = c * 32 + g * 8 + q;
-                    const float4 kj = sm.kc[j];
-                    const float dx = qx - kj.x, dy = qy - kj.y, dz = qz - kj.z;
-                    const float d2 = dx * dx + dy * dy + dz * dz;
-                    const float r = ex2_approx(d2 * c_rbf);
-                    const float s_raw = __uint_as_float(sv[g * 8 + q]);
-                    const float t2 = s_raw * c_s;
-                    const bool ok = q_ok && kj.w != 0.f;
-                    const float pr = ok ? ex2_approx(fmaf(t2, r, t2) - l2) : 0.f;
-                    const float dsr = pr * (__uint_as_float(dpv[g * 8 + q]) - dsum);
-                    pe[q] = pr;
-                    de[q] = dsr * (1.f + r) * p.scale;
-                    dsig_acc = fmaf(dsr * (s_raw * p.scale), r * d2, dsig_acc);
-                }
-                const int chunk = c * 4 + g;  // 16-byte chunk index along the 128 keys
-                const uint32_t off = (chunk >> 3) * GA_TILE_BYTES + sw128_offset(tid, chunk & 7);
-                *reinterpret_cast<uint4 *>(sm.p + off) = make_uint4(pack_bf16x2(pe[0], pe[1]), pack_bf16x2(pe[2], pe[3]),
-                                                                     pack_bf16x2(pe[4], pe[5]), pack_bf16x2(pe[6], pe[7]));
-                *reinterpret_cast<uint4 *>(sm.ds + off) = make_uint4(pack_bf16x2(de[0], de[1]), pack_bf16x2(de[2], de[3]),
-                                                                      pack_bf16x2(de[4], de[5]), pack_bf16x2(de[6], de[7]));
-            }
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();  // P and dS complete; S and dP have been read by everyone
-        if (tid == 0) {
-            tc_fence_after();
-            issue_grads(buf, t == 0);
-            if (t + 1 < nt) {
-                mbar_wait_timed(&sm.bar_qdo[buf ^ 1], (uint32_t)(((t + 1) >> 1) & 1));
-                issue_s_dp(buf ^ 1);  // next tile's S / dP run behind the gradient MMAs
-            }
-        }
-        mbar_wait_timed(&sm.bar_g, par);
-        tc_fence_after();
-        if (tid == 0 && t + 2 < nt) load_qdo(buf, sm.tiles[t + 2]);  // Q / dO buffer `buf` is free again
-        // dQ tile: TMEM -> fp32 staging -> bulk reduce-add into global dQ (one copy per warp)
-        if (lane == 0) bulk_wait_group_read0();  // the previous copy has finished reading the staging
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < GA_D / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tm_dq + lane_base + c * 32, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-                *reinterpret_cast<uint4 *>(stage + lane * GA_D + c * 32 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-        }
-        fence_proxy_async();
-        __syncwarp();
+    if (!is_math) {
+        // ================================ producer warp ==============================================
         if (lane == 0) {
-            const int r0 = i0 + warp * 32;
-            const int nrows = min(32, N - r0);
-            if (nrows > 0) {
-                bulk_reduce_add_f32(p.dq + ((size_t)zh * N + r0) * GA_D, stage, (uint32_t)nrows * GA_D * 4);
-                bulk_commit_group();
+            const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p), ds_addr = smem_u32(sm.ds);
+            constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, 128, false, false);
+            constexpr uint32_t IDESC_TT = umma_idesc_bf16(128, GA_D, true, true);   // dV, dK
+            constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, GA_D, false, true);  // dQ
+            auto load_qdo = [&](int buf, int tile) {
+                mbar_expect_tx(&sm.bar_qdo[buf], 2 * GA_TILE_BYTES);
+                tma_load_3d(sm.q[buf], &map_q, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
+                tma_load_3d(sm.dout[buf], &map_do, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
+            };
+            auto issue_s_dp = [&](int buf) {
+                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
+#pragma unroll
+                for (int kk = 0; kk < GA_D / 16; ++kk)
+                    umma_ss(tm_s, umma_desc_sw128(q_addr + kk * 32, 16, 1024), umma_desc_sw128(k_addr + kk * 32, 16, 1024),
+                            IDESC_SP, kk > 0 ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < GA_D / 16; ++kk)
+                    umma_ss(tm_dp, umma_desc_sw128(do_addr + kk * 32, 16, 1024), umma_desc_sw128(v_addr + kk * 32, 16, 1024),
+                            IDESC_SP, kk > 0 ? 1u : 0u);
+                umma_commit(&sm.bar_sp);
+            };
+            auto issue_grads = [&](int buf, bool first) {
+                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
+#pragma unroll
+                for (int kk = 0; kk < GA_BN / 16; ++kk)  // dQ first: the math warps wait for it; K = 16 keys per step
+                    umma_ss(tm_dq, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                            umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_DQ, kk > 0 ? 1u : 0u);
+                umma_commit(&sm.bar_g);
+#pragma unroll
+                for (int kk = 0; kk < GA_BM / 16; ++kk) {  // K = 16 query rows per step: 2 KiB down the [i][j] tiles
+                    umma_ss(tm_dv, umma_desc_sw128(p_addr + kk * 2048, GA_TILE_BYTES, 1024),
+                            umma_desc_sw128(do_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
+                    umma_ss(tm_dk, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024),
+                            umma_desc_sw128(q_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
+                }
+            };
+            mbar_expect_tx(&sm.bar_kv, 2 * GA_TILE_BYTES);
+            tma_load_3d(sm.k, &map_k, 0, j0, zh_local, &sm.bar_kv);
+            tma_load_3d(sm.v, &map_v, 0, j0, zh_local, &sm.bar_kv);
+            load_qdo(0, sm.tiles[0]);
+            if (nt > 1) load_qdo(1, sm.tiles[1]);
+            mbar_wait_timed(&sm.bar_kv, 0);
+            mbar_wait_timed(&sm.bar_qdo[0], 0);
+            tc_fence_after();
+            issue_s_dp(0);
+            for (int t = 0; t < nt; ++t) {
+                const int buf = t & 1;
+                const uint32_t par = (uint32_t)(t & 1);
+                mbar_wait_timed(&sm.bar_pds, par);  // P, dS(t) written; S, dP(t) consumed
+                if (t > 0) mbar_wait_timed(&sm.bar_dqr, par ^ 1);  // dQ(t-1) has been read out of TMEM
+                tc_fence_after();
+                issue_grads(buf, t == 0);
+                if (t + 1 < nt) {
+                    mbar_wait_timed(&sm.bar_qdo[buf ^ 1], (uint32_t)(((t + 1) >> 1) & 1));
+                    issue_s_dp(buf ^ 1);  // the next tile's S / dP run behind the gradient MMAs
+                    // everything issued so far (grads(t) included) completes before bar_sp(t+1) fires
+                } else {
+                    umma_commit(&sm.bar_sp);  // final completion signal for the dV / dK accumulation
+                }
+                if (t + 2 < nt) {  // Q / dO buffer `buf` is free once S, dP(t) and the gradient MMAs(t) are done
+                    mbar_wait_timed(&sm.bar_sp, par ^ 1);
+                    load_qdo(buf, sm.tiles[t + 2]);
+                }
             }
         }
-        tc_fence_before();
-        __syncthreads();  // dQ tile has been read by everyone before the next gradient MMAs overwrite it
-    }
+        __syncwarp();
+    } else {
+        // ================================ math warps ==================================================
+        const float sig = p.sigma[h];
+        const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
+        const float c_s = p.scale * 1.4426950408889634f;
+        const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cs2 = f2_pack(c_s, c_s), scale2 = f2_pack(p.scale, p.scale);
+        f2_t dsig2 = 0ull;
+        float *stage = sm.dq + (warp & 3) * 32 * GA_D;  // the 32 rows this warp shares with three others
+        const bool copy_lane = qtr == 0 && lane == 0;   // issues the reduce-add copy of those 32 rows
 
-    // ---- epilogue: dV, dK rows of this key tile; dsigma -----------------------------------------------
-    // (the last bar_g wait above covers the final accumulation)
+        for (int t = 0; t < nt; ++t) {
+            const uint32_t par = (uint32_t)(t & 1);
+            const int i0 = sm.tiles[t] * GA_BM;
+            const int row = i0 + r;
+            // per-row inputs of this query tile (overlaps the S / dP MMAs)
+            const bool q_ok = row < N && (vz ? vz[row] != 0 : true);
+            float qcx = 0.f, qcy = 0.f, qcz = 0.f, l2 = INFINITY, dsum = 0.f;  // l2 = +inf: P = 0 for a padded query
+            if (q_ok) {
+                qcx = cz[row * 3] - orx;
+                qcy = cz[row * 3 + 1] - ory;
+                qcz = cz[row * 3 + 2] - orz;
+                l2 = p.lse[(size_t)zh * N + row] * 1.4426950408889634f;
+                dsum = p.dsum[(size_t)zh_local * N + row];
+            }
+            GaBwdRow rw;
+            rw.qx2 = f2_pack(-2.f * qcx, -2.f * qcx);
+            rw.qy2 = f2_pack(-2.f * qcy, -2.f * qcy);
+            rw.qz2 = f2_pack(-2.f * qcz, -2.f * qcz);
+            const float cqn = c_rbf * (qcx * qcx + qcy * qcy + qcz * qcz);
+            rw.cqn2 = f2_pack(cqn, cqn);
+            rw.l22 = f2_pack(l2, l2);
+            rw.dsum2 = f2_pack(dsum, dsum);
+            mbar_wait_timed(&sm.bar_sp, par);
+            tc_fence_after();
+            if (has_hole) {
 #pragma unroll
-    for (int c = 0; c < GA_D / 32; ++c) {
-        uint32_t a[32], b[32];
-        tmem_ld32(tm_dv + lane_base + c * 32, a);
-        tmem_ld32(tm_dk + lane_base + c * 32, b);
-        tmem_wait_ld();
-        if (jrow < N) {
+                for (int c = 0; c < 2; ++c)
+                    ga_bwd_chunk<true>(tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16,
+                                       &sm.ka[qtr * 16 + c * 8], &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2,
+                                       scale2, dsig2, sm.p, sm.ds, r, qtr * 4 + c * 2);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 32; e += 4) {
-                *reinterpret_cast<uint4 *>(dv_row + c * 32 + e) = make_uint4(a[e], a[e + 1], a[e + 2], a[e + 3]);
-                *reinterpret_cast<uint4 *>(dk_row + c * 32 + e) = make_uint4(b[e], b[e + 1], b[e + 2], b[e + 3]);
+                for (int c = 0; c < 2; ++c)
+                    ga_bwd_chunk<false>(tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16,
+                                        &sm.ka[qtr * 16 + c * 8], &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2,
+                                        scale2, dsig2, sm.p, sm.ds, r, qtr * 4 + c * 2);
+            }
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(&sm.bar_pds);
+            // dQ tile: TMEM -> fp32 staging -> bulk reduce-add into global dQ (one copy per 32 rows)
+            mbar_wait_timed(&sm.bar_g, par);
+            tc_fence_after();
+            if (copy_lane) bulk_wait_group_read0();  // the previous copy has finished reading the staging
+            group_bar_sync(warp & 3);
+            {
+                uint32_t v[16];
+                tmem_ld16(tm_dq + lane_base + qtr * 16, v);
+                tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(&sm.bar_dqr);
+#pragma unroll
+                for (int e = 0; e < 16; e += 4)
+                    *reinterpret_cast<uint4 *>(stage + lane * GA_D + qtr * 16 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            }
+            fence_proxy_async();
+            group_bar_sync(warp & 3);
+            if (copy_lane) {
+                const int r0 = i0 + (warp & 3) * 32;
+                const int nrows = min(32, N - r0);
+                if (nrows > 0) {
+                    bulk_reduce_add_f32(p.dq + ((size_t)zh * N + r0) * GA_D, stage, (uint32_t)nrows * GA_D * 4);
+                    bulk_commit_group();
+                }
             }
         }
-    }
+
+        // ---- epilogue: dV, dK rows of this key tile; dsigma -------------------------------------------
+        mbar_wait_timed(&sm.bar_sp, (uint32_t)(nt & 1));  // the last commit: every accumulation has completed
+        tc_fence_after();
+        {
+            uint32_t a[16], b[16];
+            tmem_ld16(tm_dv + lane_base + qtr * 16, a);
+            tmem_ld16(tm_dk + lane_base + qtr * 16, b);
+            tmem_wait_ld();
+            if (jrow < N) {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) dsig_acc += __shfl_xor_sync(0xffffffffu, dsig_acc, off);
-    if (lane == 0) sm.dsig[warp] = dsig_acc;
-    if (lane == 0) bulk_wait_group0();  // the reduce-add copies of this warp have completed
+                for (int e = 0; e < 16; e += 4) {
+                    *reinterpret_cast<uint4 *>(dv_row + e) = make_uint4(a[e], a[e + 1], a[e + 2], a[e + 3]);
+                    *reinterpret_cast<uint4 *>(dk_row + e) = make_uint4(b[e], b[e + 1], b[e + 2], b[e + 3]);
+                }
+            }
+        }
+        float d0, d1;
+        f2_unpack(dsig2, d0, d1);
+        float dsig_acc = d0 + d1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) dsig_acc += __shfl_xor_sync(0xffffffffu, dsig_acc, off);
+        if (lane == 0) sm.dsig[warp] = dsig_acc;
+        if (copy_lane) bulk_wait_group0();  // the reduce-add copies issued by this lane have completed
+    }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) atomicAdd(p.dsigma + h, (sm.dsig[0] + sm.dsig[1] + sm.dsig[2] + sm.dsig[3]) / (sig * sig * sig));
-    if (warp == 0) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
+    if (tid == 0) {
+        float tot = 0.f;
+        for (int w = 0; w < GA_BWD_MATH_THREADS / 32; ++w) tot += sm.dsig[w];
+        // sum of dSR * S_raw * R * (c_rbf d^2), S = scale * S_raw:  dsigma = sum dSR S R d^2 / sigma^3
+        const float sig = p.sigma[h];
+        const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
+        atomicAdd(p.dsigma + h, tot * p.scale / (c_rbf * sig * sig * sig));
+    }
+    if (warp == GA_BWD_MATH_THREADS / 32) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
 }
 
 }  // namespace pai
