@@ -166,7 +166,8 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     int sms = 0;
     if (int e = current_device_sms(&sms)) return e;
     return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_TJ", 0), env_int("PAI_WE_WAVES", 0),
-                              env_int("PAI_WE_REPRODUCIBLE", 0) != 0, env_int("PAI_WE_RANGE_REDUCE", 0) != 0, sms, st);
+                              env_int("PAI_WE_REPRODUCIBLE", 0) != 0, env_int("PAI_WE_RANGE_REDUCE", 0) != 0,
+                              env_int("PAI_WE_POLY_PAIRS", 1), sms, st);
 }
 
 size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {

@@ -140,7 +140,7 @@ def test_row_shards_and_code_paths_agree(we, monkeypatch):
     assert rel_l2(full, out) < 1e-5 and rel_l2(fcs, cs) < 1e-5 and rel_l2(fsn, sn) < 1e-5
     ref = wf_embedding_ref(c_t.cpu(), wn.cpu(), 1, m_t.cpu(), dtype=torch.float64)
     for env in ({"PAI_WE_NO_TMA": "1"}, {"PAI_WE_KS": "8"}, {"PAI_WE_KS": "2"}, {"PAI_WE_RANGE_REDUCE": "1"},
-                {"PAI_WE_KS": "16"}, {"PAI_WE_TJ": "64"}, {"PAI_WE_TJ": "512"}, {"PAI_WE_TJ": "36", "PAI_WE_NO_TMA": "1"}):
+                {"PAI_WE_KS": "16"}, {"PAI_WE_TJ": "64"}, {"PAI_WE_TJ": "512"}, {"PAI_WE_TJ": "36", "PAI_WE_NO_TMA": "1"}, {"PAI_WE_POLY_PAIRS": "0"}, {"PAI_WE_POLY_PAIRS": "3"}):
         for key, val in env.items():
             monkeypatch.setenv(key, val)
         alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
