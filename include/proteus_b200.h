@@ -117,46 +117,54 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, forward.
  * Replaces the Triton launch `_attn_fwd[grid](...)` in _geometric_attn.forward
- *   (old/old_scripts/attn/geometric_attn.py:553-607; kernel :57-260), with the logit form of the
- *   reference README (README.md:40):  SR_ij = (q_i.k_j * scale) * (1 + exp(-|r_i-r_j|^2 / (2 sigma_h^2))),
- *   softmax over the keys j, a pair (i,j) valid iff both tokens are unpadded.
+ *   (old/old_scripts/attn/geometric_attn.py:553-607; kernel :57-260).  Two logit forms:
+ *   logit_form 0  SR_ij = S_ij * (1 + R_ij), the form of the reference README (README.md:40);
+ *                 betas, min_rbf, max_rbf are ignored (betas may be NULL);
+ *   logit_form 1  SR_ij = S_ij + beta_h * Rn_ij * |S_ij|, Rn = 2 (R - min_rbf) / (max_rbf - min_rbf) - 1, and pairs with
+ *                 R outside [min_rbf, max_rbf] masked out: the form the reference tree's kernel and test implement
+ *                 (geometric_attn.py:193-201, tests/attn/geo_attn.py:202-207);
+ *   with S_ij = q_i.k_j * scale, R_ij = exp(-|r_i-r_j|^2 / (2 sigma_h^2)), softmax over the keys j, a pair (i,j) valid
+ *   iff both tokens are unpadded.
  *
  *   Q, K, V  [Z,H,N,d] bf16, contiguous     (d must be 64)
  *   coords   [Z,N,3]   fp32                 C-alpha coordinates
  *   sigma    [H]       fp32                 per-head RBF spread
+ *   betas    [H]       fp32                 per-head RBF weight (logit_form 1)
  *   valid    [Z,N]     u8                   1 = real token, 0 = padding; NULL = all valid
  *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros
- *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for padded queries
+ *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for rows without a valid pair
  *   scale                                    softmax scale, 1/sqrt(d) in the reference
  *   zh_begin, zh_end                         only the (batch, head) pairs z*H + h in [zh_begin, zh_end) are
  *                                            computed and written (multi-GPU shard); other rows are not touched
  * bf16 x bf16 -> fp32 tensor-core products, fp32 softmax, P rounded to bf16 before P V.
  */
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale,
-                    int zh_begin, int zh_end, void *stream);
+                    const float *betas, const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d,
+                    float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, backward.
  * Replaces _geometric_attn.backward (old/old_scripts/attn/geometric_attn.py:610-660): the PyTorch row-sum
  *   D = sum(O * dO) (:616) and the Triton launch `_attn_bwd[grid](...)` (:640-657; kernel :265-543), for the
- *   logit form of pai_geoattn_fwd.
+ *   logit forms of pai_geoattn_fwd.
  *
  *   Q, K, V, O, dO [Z,H,N,d] bf16 contiguous (d must be 64); L [Z,H,N] fp32 as written by the forward
  *   dQ, dK, dV     [Z,H,N,d] fp32, like the reference's gradients (:626-628); every row of the
  *                  (batch, head) range is written, rows of padded tokens as zeros; dQ is accumulated
  *                  across key tiles with reduce-add copies, so its summation order is not fixed
  *   dsigma         [H] fp32, overwritten: gradient w.r.t. the spreads summed over the (batch, head) range
+ *   dbetas         [H] fp32, overwritten: gradient w.r.t. betas (logit_form 1; may be NULL for logit_form 0)
  *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned
  *                  (holds D, one fp32 per query row)
  *   zh_begin, zh_end  as in the forward
  */
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d);
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
-                    const float *coords, const float *sigma, const uint8_t *valid,
-                    float *dQ, float *dK, float *dV, float *dsigma,
+                    const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
+                    float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
                     void *workspace, size_t workspace_bytes,
-                    int Z, int H, int N, int d, float scale, int zh_begin, int zh_end, void *stream);
+                    int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
+                    int zh_begin, int zh_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and

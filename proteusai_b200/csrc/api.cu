@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
 
 extern "C" {
 
-int pai_abi_version(void) { return 1; }
+int pai_abi_version(void) { return 2; }
 
 const char *pai_status_str(int status) {
     switch (status) {
@@ -195,9 +195,12 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
 }
 
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale, int zh_begin,
-                    int zh_end, void *stream) {
+                    const float *betas, const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale,
+                    float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream) {
     if (!Q || !K || !V || !coords || !sigma || !O || !L) return PAI_ERR_NULL_POINTER;
+    if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
+    if (logit_form == 1 && !betas) return PAI_ERR_NULL_POINTER;
+    if (logit_form == 1 && !(max_rbf > min_rbf)) return PAI_ERR_BAD_SHAPE;
     if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
     if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
     if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
@@ -232,6 +235,10 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     p.N = N;
     p.zh_begin = zh_begin;
     p.scale = scale;
+    p.form = logit_form;
+    p.beta = betas;
+    p.min_rbf = min_rbf;
+    p.max_rbf = max_rbf;
     dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
     pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
@@ -244,11 +251,14 @@ size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
 }
 
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
-                    const float *coords, const float *sigma, const uint8_t *valid, float *dQ, float *dK, float *dV,
-                    float *dsigma, void *workspace, size_t workspace_bytes, int Z, int H, int N, int d, float scale,
-                    int zh_begin, int zh_end, void *stream) {
+                    const float *coords, const float *sigma, const float *betas, const uint8_t *valid, float *dQ, float *dK,
+                    float *dV, float *dsigma, float *dbetas, void *workspace, size_t workspace_bytes, int Z, int H, int N,
+                    int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream) {
     if (!Q || !K || !V || !O || !dO || !L || !coords || !sigma || !dQ || !dK || !dV || !dsigma || !workspace)
         return PAI_ERR_NULL_POINTER;
+    if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
+    if (logit_form == 1 && (!betas || !dbetas)) return PAI_ERR_NULL_POINTER;
+    if (logit_form == 1 && !(max_rbf > min_rbf)) return PAI_ERR_BAD_SHAPE;
     if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
     if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
     if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
@@ -261,6 +271,10 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t ce = cudaMemsetAsync(dsigma, 0, (size_t)H * sizeof(float), st);
     if (ce != cudaSuccess) return (int)ce;
+    if (dbetas) {
+        ce = cudaMemsetAsync(dbetas, 0, (size_t)H * sizeof(float), st);
+        if (ce != cudaSuccess) return (int)ce;
+    }
     if (zh_begin == zh_end) return PAI_OK;
     const int nzh = zh_end - zh_begin;
     const size_t rows0 = (size_t)zh_begin * N;
@@ -295,6 +309,11 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.dk = dK;
     p.dv = dV;
     p.dsigma = dsigma;
+    p.dbeta = dbetas;
+    p.form = logit_form;
+    p.beta = betas;
+    p.min_rbf = min_rbf;
+    p.max_rbf = max_rbf;
     p.Z = Z;
     p.H = H;
     p.N = N;

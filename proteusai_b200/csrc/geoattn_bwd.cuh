@@ -55,6 +55,7 @@ struct GaBwdSmem {
     int first_k;                           // first valid key of the tile (origin of the centring)
     int has_hole;                          // the key tile holds a padded or out-of-range key
     float dsig[GA_BWD_MATH_THREADS / 32];
+    float dbeta[GA_BWD_MATH_THREADS / 32];
 };
 
 struct GaBwdParams {
@@ -67,8 +68,12 @@ struct GaBwdParams {
     float *dk;             // [Z,H,N,64] fp32
     float *dv;             // [Z,H,N,64] fp32
     float *dsigma;         // [H] fp32, zeroed before launch
+    float *dbeta;          // [H] fp32, zeroed before launch (form 1 only; may be nullptr for form 0)
     int Z, H, N, zh_begin;
     float scale;
+    int form;              // logit form, as in the forward
+    const float *beta;     // [H], form 1 only
+    float min_rbf, max_rbf;
 };
 
 // D[zh_local, i] = sum_d O * dO; one warp per row, 2 elements per lane.
@@ -110,10 +115,10 @@ struct GaBwdRow {  // per-thread constants of the current query row, packed for 
 
 // 16 key columns (8 pairs) of one query row: recompute P, form dS and the spread-gradient term, write P and
 // dS as bf16 into the swizzled [i][j] tiles.  `chunk0` is the index of the first 16-byte chunk (8 keys).
-template <bool MASKED>
+template <bool MASKED, int FORM>
 __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const float4 *ka, const float4 *kc, const float *kb,
-                                             const GaBwdRow &rw, f2_t crbf2, f2_t cs2, f2_t scale2, f2_t &dsig2, uint8_t *p_tile,
-                                             uint8_t *ds_tile, int r, int chunk0) {
+                                             const GaBwdRow &rw, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
+                                             f2_t &dbeta2, uint8_t *p_tile, uint8_t *ds_tile, int r, int chunk0) {
     uint32_t sv[16], dpv[16];
     tmem_ld16(t_s, sv);
     tmem_ld16(t_dp, dpv);
@@ -133,6 +138,10 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const 
         for (int e = 0; e < 4; ++e) {
             float a0, a1;
             f2_unpack(arg[e], a0, a1);
+            if (FORM == 1) {
+                a0 = fminf(a0, 0.f);
+                a1 = fminf(a1, 0.f);
+            }
             rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
         }
         if (g == 0) tmem_wait_ld();
@@ -142,7 +151,17 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const 
         for (int e = 0; e < 4; ++e) {
             const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
             const f2_t t2 = f2_mul(s_raw, cs2);
-            f2_t sr = f2_fma(t2, rb[e], t2);
+            f2_t sr;
+            if (FORM == 0) {
+                sr = f2_fma(t2, rb[e], t2);
+            } else {
+                float t0, t1, r0, r1;
+                f2_unpack(t2, t0, t1);
+                f2_unpack(rb[e], r0, r1);
+                const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
+                const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
+                sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
+            }
             if (MASKED) sr = f2_add(sr, *reinterpret_cast<const f2_t *>(kb + g * 8 + 2 * e));
             x[e] = f2_sub(sr, rw.l22);
         }
@@ -157,8 +176,25 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const 
             const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
             const f2_t dp = f2_pack(__uint_as_float(dpv[g * 8 + 2 * e]), __uint_as_float(dpv[g * 8 + 2 * e + 1]));
             const f2_t dsr = f2_mul(x[e], f2_sub(dp, rw.dsum2));
-            const f2_t ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
-            dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
+            f2_t ds;
+            if (FORM == 0) {
+                ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
+                dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
+            } else {  // dS = dSR (1 + beta Rn sign(S)),  dR = dSR |S| 2 beta / (max - min),  dbeta = sum dSR Rn |S|
+                float s0, s1, r0, r1, g0, g1, a0, a1;
+                f2_unpack(s_raw, s0, s1);
+                f2_unpack(rb[e], r0, r1);
+                f2_unpack(dsr, g0, g1);
+                f2_unpack(arg[e], a0, a1);
+                const float rn0 = fmaf(r0, fm.rn_a, fm.rn_b), rn1 = fmaf(r1, fm.rn_a, fm.rn_b);
+                const float sg0 = (s0 > 0.f) ? 1.f : ((s0 < 0.f) ? -1.f : 0.f), sg1 = (s1 > 0.f) ? 1.f : ((s1 < 0.f) ? -1.f : 0.f);
+                float sc0, sc1;
+                f2_unpack(scale2, sc0, sc1);
+                const float f0 = s0 != 0.f ? fmaf(fm.beta * rn0, sg0, 1.f) : 0.f, f1 = s1 != 0.f ? fmaf(fm.beta * rn1, sg1, 1.f) : 0.f;
+                ds = f2_pack(g0 * sc0 * f0, g1 * sc1 * f1);
+                dsig2 = f2_fma(f2_pack(g0 * fabsf(s0) * r0, g1 * fabsf(s1) * r1), f2_pack(fminf(a0, 0.f), fminf(a1, 0.f)), dsig2);
+                dbeta2 = f2_add(dbeta2, f2_pack(g0 * rn0 * fabsf(s0), g1 * rn1 * fabsf(s1)));
+            }
             float p0, p1, d0, d1;
             f2_unpack(x[e], p0, p1);
             f2_unpack(ds, d0, d1);
@@ -348,7 +384,15 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
         const float c_s = p.scale * 1.4426950408889634f;
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cs2 = f2_pack(c_s, c_s), scale2 = f2_pack(p.scale, p.scale);
-        f2_t dsig2 = 0ull;
+        f2_t dsig2 = 0ull, dbeta2 = 0ull;
+        GaForm fm = {0.f, 0.f, 0.f, 0.f, 1.f};
+        if (p.form == 1) {
+            fm.beta = p.beta[h];
+            fm.rn_a = 2.f / (p.max_rbf - p.min_rbf);
+            fm.rn_b = -2.f * p.min_rbf / (p.max_rbf - p.min_rbf) - 1.f;
+            fm.rmin = p.min_rbf;
+            fm.rmax = p.max_rbf;
+        }
         float *stage = sm.dq + (warp & 3) * 32 * GA_D;  // the 32 rows this warp shares with three others
         const bool copy_lane = qtr == 0 && lane == 0;   // issues the reduce-add copy of those 32 rows
 
@@ -363,7 +407,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 qcx = cz[row * 3] - orx;
                 qcy = cz[row * 3 + 1] - ory;
                 qcz = cz[row * 3 + 2] - orz;
-                l2 = p.lse[(size_t)zh * N + row] * 1.4426950408889634f;
+                const float lse = p.lse[(size_t)zh * N + row];
+                l2 = lse == -INFINITY ? INFINITY : lse * 1.4426950408889634f;  // a row without any valid pair: P = 0
                 dsum = p.dsum[(size_t)zh_local * N + row];
             }
             GaBwdRow rw;
@@ -376,19 +421,17 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             rw.dsum2 = f2_pack(dsum, dsum);
             mbar_wait_timed(&sm.bar_sp, par);
             tc_fence_after();
-            if (has_hole) {
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    ga_bwd_chunk<true>(tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16,
-                                       &sm.ka[qtr * 16 + c * 8], &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2,
-                                       scale2, dsig2, sm.p, sm.ds, r, qtr * 4 + c * 2);
+#define PAI_GA_BWD(MASKED, FORM)                                                                                             \
+    _Pragma("unroll") for (int c = 0; c < 2; ++c) ga_bwd_chunk<MASKED, FORM>(                                                \
+        tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16, &sm.ka[qtr * 16 + c * 8],               \
+        &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2, scale2, fm, dsig2, dbeta2, sm.p, sm.ds, r,       \
+        qtr * 4 + c * 2)
+            if (p.form == 0) {
+                if (has_hole) { PAI_GA_BWD(true, 0); } else { PAI_GA_BWD(false, 0); }
             } else {
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-                    ga_bwd_chunk<false>(tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16,
-                                        &sm.ka[qtr * 16 + c * 8], &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2,
-                                        scale2, dsig2, sm.p, sm.ds, r, qtr * 4 + c * 2);
+                if (has_hole) { PAI_GA_BWD(true, 1); } else { PAI_GA_BWD(false, 1); }
             }
+#undef PAI_GA_BWD
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&sm.bar_pds);
@@ -435,23 +478,39 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
         }
-        float d0, d1;
+        float d0, d1, b0, b1;
         f2_unpack(dsig2, d0, d1);
-        float dsig_acc = d0 + d1;
+        f2_unpack(dbeta2, b0, b1);
+        float dsig_acc = d0 + d1, dbeta_acc = b0 + b1;
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) dsig_acc += __shfl_xor_sync(0xffffffffu, dsig_acc, off);
-        if (lane == 0) sm.dsig[warp] = dsig_acc;
+        for (int off = 16; off > 0; off >>= 1) {
+            dsig_acc += __shfl_xor_sync(0xffffffffu, dsig_acc, off);
+            dbeta_acc += __shfl_xor_sync(0xffffffffu, dbeta_acc, off);
+        }
+        if (lane == 0) {
+            sm.dsig[warp] = dsig_acc;
+            sm.dbeta[warp] = dbeta_acc;
+        }
         if (copy_lane) bulk_wait_group0();  // the reduce-add copies issued by this lane have completed
     }
     tc_fence_before();
     __syncthreads();
     if (tid == 0) {
-        float tot = 0.f;
-        for (int w = 0; w < GA_BWD_MATH_THREADS / 32; ++w) tot += sm.dsig[w];
-        // sum of dSR * S_raw * R * (c_rbf d^2), S = scale * S_raw:  dsigma = sum dSR S R d^2 / sigma^3
+        float tot = 0.f, totb = 0.f;
+        for (int w = 0; w < GA_BWD_MATH_THREADS / 32; ++w) {
+            tot += sm.dsig[w];
+            totb += sm.dbeta[w];
+        }
         const float sig = p.sigma[h];
         const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
-        atomicAdd(p.dsigma + h, tot * p.scale / (c_rbf * sig * sig * sig));
+        if (p.form == 0) {
+            // sum of dSR * S_raw * R * (c_rbf d^2), S = scale * S_raw:  dsigma = sum dSR S R d^2 / sigma^3
+            atomicAdd(p.dsigma + h, tot * p.scale / (c_rbf * sig * sig * sig));
+        } else {
+            // sum of dSR * |S_raw| * R * (c_rbf d^2):  dsigma = sum dR R d^2 / sigma^3 with dR = dSR |S| 2 beta / (max - min)
+            atomicAdd(p.dsigma + h, tot * p.scale * 2.f * p.beta[h] / ((p.max_rbf - p.min_rbf) * c_rbf * sig * sig * sig));
+            if (p.dbeta) atomicAdd(p.dbeta + h, totb * p.scale);
+        }
     }
     if (warp == GA_BWD_MATH_THREADS / 32) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
 }

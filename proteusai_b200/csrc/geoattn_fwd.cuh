@@ -67,6 +67,15 @@ struct GaFwdParams {
     float *lse;            // [Z,H,N]  log-sum-exp of SR (natural log), -inf for padded queries
     int Z, H, N, zh_begin;
     float scale;
+    // logit form: 0 = S (1 + R);  1 = S + beta Rn |S| with Rn = 2 (R - min_rbf) / (max_rbf - min_rbf) - 1 and pairs
+    // with R outside [min_rbf, max_rbf] masked out (the form of old/old_scripts/attn/geometric_attn.py:193-201)
+    int form;
+    const float *beta;     // [H], form 1 only
+    float min_rbf, max_rbf;
+};
+
+struct GaForm {  // per-head constants of logit form 1
+    float beta, rn_a, rn_b, rmin, rmax;  // Rn = R * rn_a + rn_b
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -111,9 +120,9 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 // SR = (S * c_s) * (1 + R) with R = 2^(c_rbf * d^2), d^2 = |q|^2 + |k|^2 - 2 q.k from the centred
 // coordinates, optionally adds the key mask, writes SR back in place and returns the running maximum.
 // Written as three stages over the 8 pairs so that the independent chains overlap.
-template <bool MASKED>
+template <bool MASKED, int FORM>
 __device__ __forceinline__ float ga_scale_chunk(uint32_t taddr, const float4 *ka, const float4 *kc, const float *kb, f2_t qx2,
-                                                f2_t qy2, f2_t qz2, f2_t crbf2, f2_t cqn2, f2_t cs2, float m_loc) {
+                                                f2_t qy2, f2_t qz2, f2_t crbf2, f2_t cqn2, f2_t cs2, const GaForm &fm, float m_loc) {
     uint32_t v[16];
     tmem_ld16(taddr, v);
     f2_t arg[8];
@@ -129,13 +138,27 @@ __device__ __forceinline__ float ga_scale_chunk(uint32_t taddr, const float4 *ka
     for (int e = 0; e < 8; ++e) {
         float a0, a1;
         f2_unpack(arg[e], a0, a1);
+        if (FORM == 1) {  // keep R <= 1 exactly (the centred d^2 of a coincident pair can round below zero)
+            a0 = fminf(a0, 0.f);
+            a1 = fminf(a1, 0.f);
+        }
         arg[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
     }
     tmem_wait_ld();
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         const f2_t t2 = f2_mul(f2_pack(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1])), cs2);
-        f2_t sr = f2_fma(t2, arg[e], t2);
+        f2_t sr;
+        if (FORM == 0) {
+            sr = f2_fma(t2, arg[e], t2);
+        } else {
+            float t0, t1, r0, r1;
+            f2_unpack(t2, t0, t1);
+            f2_unpack(arg[e], r0, r1);
+            const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
+            const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
+            sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
+        }
         if (MASKED) sr = f2_add(sr, *reinterpret_cast<const f2_t *>(kb + 2 * e));
         float v0, v1;
         f2_unpack(sr, v0, v1);
@@ -320,6 +343,14 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const f2_t qx2 = f2_pack(-2.f * qcx, -2.f * qcx), qy2 = f2_pack(-2.f * qcy, -2.f * qcy), qz2 = f2_pack(-2.f * qcz, -2.f * qcz);
         const float cqn = c_rbf * (qcx * qcx + qcy * qcy + qcz * qcz);
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cqn2 = f2_pack(cqn, cqn), cs2 = f2_pack(c_s, c_s);
+        GaForm fm = {0.f, 0.f, 0.f, 0.f, 1.f};
+        if (p.form == 1) {
+            fm.beta = p.beta[h];
+            fm.rn_a = 2.f / (p.max_rbf - p.min_rbf);
+            fm.rn_b = -2.f * p.min_rbf / (p.max_rbf - p.min_rbf) - 1.f;
+            fm.rmin = p.min_rbf;
+            fm.rmax = p.max_rbf;
+        }
         float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's half of the row sum
 
         for (int t = 0; t < nt; ++t) {
@@ -344,19 +375,16 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // first pass, 32 logits at a time: scale by (1 + R), mask, write SR back to TMEM, track the maximum
             // (two copies of the loop so that the mask test is not a branch inside the unrolled body)
             float m_loc = -INFINITY;
-            if (has_hole) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    m_loc = ga_scale_chunk<true>(tmem_s + lane_base + half * 64 + c * 16, &sm.ka[cb][half * 32 + c * 8],
-                                                 &sm.kc[cb][half * 32 + c * 8], &sm.kb[cb][half * 64 + c * 16], qx2, qy2, qz2,
-                                                 crbf2, cqn2, cs2, m_loc);
+#define PAI_GA_PASS1(MASKED, FORM)                                                                                          \
+    _Pragma("unroll") for (int c = 0; c < 4; ++c) m_loc = ga_scale_chunk<MASKED, FORM>(                                      \
+        tmem_s + lane_base + half * 64 + c * 16, &sm.ka[cb][half * 32 + c * 8], &sm.kc[cb][half * 32 + c * 8],               \
+        &sm.kb[cb][half * 64 + c * 16], qx2, qy2, qz2, crbf2, cqn2, cs2, fm, m_loc)
+            if (p.form == 0) {
+                if (has_hole) { PAI_GA_PASS1(true, 0); } else { PAI_GA_PASS1(false, 0); }
             } else {
-#pragma unroll
-                for (int c = 0; c < 4; ++c)
-                    m_loc = ga_scale_chunk<false>(tmem_s + lane_base + half * 64 + c * 16, &sm.ka[cb][half * 32 + c * 8],
-                                                  &sm.kc[cb][half * 32 + c * 8], &sm.kb[cb][half * 64 + c * 16], qx2, qy2, qz2,
-                                                  crbf2, cqn2, cs2, m_loc);
+                if (has_hole) { PAI_GA_PASS1(true, 1); } else { PAI_GA_PASS1(false, 1); }
             }
+#undef PAI_GA_PASS1
             tmem_wait_st();
             if (stage_next) {  // the other buffer was last read during tile t-1
                 float *a = reinterpret_cast<float *>(&sm.ka[cb ^ 1][tid >> 1]);
@@ -369,7 +397,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
             sm.xch[half][r] = m_loc;
             pair_bar_sync(warp & 3);  // the two warps that share these 32 rows
-            // every listed tile holds a valid key, so the tile maximum is finite
+            // the tile maximum is finite for form 0 (every listed tile holds a valid key); form 1 can mask a whole row of a tile
             const float m_tile = fmaxf(m_loc, sm.xch[half ^ 1][r]);
             float alpha = 1.f;
             bool raise = false;
@@ -394,7 +422,8 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
             }
             // second pass: P = 2^(SR - m), row sum, bf16 P into the swizzled tile
-            const f2_t mn2 = f2_pack(m_run, m_run);
+            const float m_safe = m_run == -INFINITY ? 0.f : m_run;  // a row without any valid pair so far: P = 2^(-inf) = 0
+            const f2_t mn2 = f2_pack(m_safe, m_safe);
             f2_t l2 = 0ull;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {

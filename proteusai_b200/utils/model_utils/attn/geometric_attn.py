@@ -5,15 +5,40 @@ Same names, argument order and gradient tuple as ``old/old_scripts/attn/geometri
 ``geometric_attn(Q, K, V, coords, spreads, betas, mask=None, min_rbf=0.0, max_rbf=1.0)`` returns
 ``[Z, H, N, d]``; the backward returns ``(dQ, dK, dV, None, d_spreads, d_betas, None, None, None)``.
 
-The logits follow the form the reference's README states, ``S * (1 + exp(-d^2 / (2 sigma_h^2)))``, with a
-pair valid iff both tokens are unpadded.  ``betas``, ``min_rbf`` and ``max_rbf`` stay in the signature
-for compatibility and do not enter this form; ``d_betas`` is returned as ``None``.  Products are
-bf16 x bf16 with fp32 accumulation (the reference casts to fp16); outputs and gradients come back in
-the dtype of ``Q``.
+Two logit forms are available (``set_logit_form``):
+
+``"one_plus_rbf"`` (default)  the form the reference's README states, ``S * (1 + exp(-d^2 / (2 sigma_h^2)))``, a pair
+                              valid iff both tokens are unpadded; ``betas``, ``min_rbf`` and ``max_rbf`` stay in the
+                              signature for compatibility and do not enter; ``d_betas`` is ``None``.
+``"beta_abs"``                the form the reference tree's Triton kernel and its test implement,
+                              ``S + beta * Rn * |S|`` with ``Rn = 2 (R - min_rbf) / (max_rbf - min_rbf) - 1`` and pairs with
+                              ``R`` outside ``[min_rbf, max_rbf]`` masked out (``geometric_attn.py:193-201``); ``d_betas``
+                              is returned.
+
+Products are bf16 x bf16 with fp32 accumulation (the reference casts to fp16); outputs and gradients come
+back in the dtype of ``Q``.
 """
+import os
+
 import torch
 
 from proteusai_b200 import _lib
+
+_FORMS = {"one_plus_rbf": 0, "beta_abs": 1}
+_logit_form = os.environ.get("PROTEUS_GEOATTN_FORM", "one_plus_rbf")
+
+
+def set_logit_form(name):
+    """Select the logit form used by ``geometric_attn`` from now on; returns the previous one."""
+    global _logit_form
+    if name not in _FORMS:
+        raise ValueError(f"logit form must be one of {sorted(_FORMS)}, not {name!r}")
+    prev, _logit_form = _logit_form, name
+    return prev
+
+
+def get_logit_form():
+    return _logit_form
 
 
 def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00, max_rbf=1.00):
@@ -21,7 +46,8 @@ def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00
     return _geometric_attn.apply(Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf)
 
 
-def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None):
+def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None,
+                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf"):
     """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V must be bf16 contiguous.
     Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``; only the pairs of the range are written."""
     if not Q.is_cuda:
@@ -32,21 +58,24 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
     valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
     if out is None:
         out = torch.empty(batch, nheads, n, d_k, dtype=torch.bfloat16, device=dev)
     if lse is None:
         lse = torch.empty(batch, nheads, n, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().pai_geoattn_fwd(
-            _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(coords), _lib.ptr(sigma), _lib.ptr(valid),
-            _lib.ptr(out), _lib.ptr(lse), batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), zh_begin, zh_end,
-            _lib.current_stream()), "pai_geoattn_fwd")
+            _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(coords), _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(valid),
+            _lib.ptr(out), _lib.ptr(lse), batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf),
+            _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_fwd")
     return out, lse
 
 
-def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0, zh_end=None):
+def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0, zh_end=None,
+                     betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf"):
     """Gradients on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V, O, dO bf16 contiguous.
-    Returns fp32 ``(dQ, dK, dV [Z,H,N,d], d_spreads [H])``; only the pairs of the range are written."""
+    Returns fp32 ``(dQ, dK, dV [Z,H,N,d], d_spreads [H])`` and, for the ``beta_abs`` form, ``d_betas [H]`` as a fifth
+    element; only the pairs of the range are written."""
     batch, nheads, n, d_k = Q.shape
     zh_end = batch * nheads if zh_end is None else zh_end
     dev = Q.device
@@ -55,15 +84,19 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
     valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
     dq, dk, dv = (torch.empty(batch, nheads, n, d_k, dtype=torch.float32, device=dev) for _ in range(3))
     dsig = torch.empty(nheads, dtype=torch.float32, device=dev)
+    beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
+    dbeta = torch.empty(nheads, dtype=torch.float32, device=dev) if form == "beta_abs" else None
     lib = _lib.lib()
     ws_bytes = lib.pai_geoattn_bwd_workspace_bytes(batch, nheads, n, d_k)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
     with torch.cuda.device(dev):
         _lib.check(lib.pai_geoattn_bwd(
             _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(dO), _lib.ptr(lse), _lib.ptr(coords),
-            _lib.ptr(sigma), _lib.ptr(valid), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig),
-            _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), zh_begin, zh_end,
-            _lib.current_stream()), "pai_geoattn_bwd")
+            _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig),
+            _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), float(min_rbf),
+            float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_bwd")
+    if form == "beta_abs":
+        return dq, dk, dv, dsig, dbeta
     return dq, dk, dv, dsig
 
 
@@ -77,17 +110,26 @@ class _geometric_attn(torch.autograd.Function):
         assert spreads.size(0) == nheads, f"number of spreads per batch must be equal to nheads, not {spreads.size(0)=} and {nheads=}"
         assert torch.all(spreads > 0), f"spreads must be a tensor of positive, non-zero floats, not {spreads}"
         qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
-        out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask)
-        ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0))
+        form = _logit_form
+        if form == "beta_abs" and betas is None:
+            raise ValueError("the beta_abs logit form needs betas")
+        out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask, betas=betas, min_rbf=min_rbf, max_rbf=max_rbf, form=form)
+        ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0),
+                              betas if betas is not None else torch.empty(0))
         ctx.has_mask = mask is not None
+        ctx.form, ctx.min_rbf, ctx.max_rbf = form, min_rbf, max_rbf
         ctx.in_dtype = Q.dtype
         ctx.spread_dtype = spreads.dtype
         return out.to(Q.dtype)
 
     @staticmethod
     def backward(ctx, dO):
-        qb, kb, vb, out, lse, coords, spreads, mask = ctx.saved_tensors
+        qb, kb, vb, out, lse, coords, spreads, mask, betas = ctx.saved_tensors
         mask = mask if ctx.has_mask else None
-        dq, dk, dv, dsig = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads, mask)
         dt = ctx.in_dtype
+        if ctx.form == "beta_abs":
+            dq, dk, dv, dsig, dbeta = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads,
+                                                       mask, betas=betas, min_rbf=ctx.min_rbf, max_rbf=ctx.max_rbf, form=ctx.form)
+            return dq.to(dt), dk.to(dt), dv.to(dt), None, dsig.to(ctx.spread_dtype), dbeta.to(betas.dtype), None, None, None
+        dq, dk, dv, dsig = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads, mask)
         return dq.to(dt), dk.to(dt), dv.to(dt), None, dsig.to(ctx.spread_dtype), None, None, None, None

@@ -77,6 +77,25 @@ def attn_cases():
     return cases
 
 
+def attn_d64_cases():
+    """Head dimension 64 (what the CUDA kernel supports), inputs exactly representable in bf16 so that the kernel and
+    the reference function see identical values.  One case in the reference test's own style (collinear coordinates,
+    spreads 3, betas 1, no padding, window [0, 1]); one on a padded random-walk chain with the module's defaults
+    (min_rbf 0.001, max_rbf 1.0)."""
+    g = torch.Generator().manual_seed(20240603)
+    bf = lambda t: t.to(torch.bfloat16).float()
+    cases = {}
+    z, h, n, d = 1, 2, 144, 64
+    q, k, v = (bf(torch.randn((z, h, n, d), generator=g)) for _ in range(3))
+    coords = 50 * torch.randn((z, n, 1), generator=g).expand(z, n, 3).contiguous()
+    cases["d64_collinear"] = (q, k, v, coords, torch.full((h,), 3.0), torch.full((h,), 1.0),
+                              torch.zeros(z, n, dtype=torch.bool), 0.0, 1.0)
+    c, m = chains.chain_batch([120], n, seed=13)
+    cases["d64_chain_padded"] = (q, k, v, torch.from_numpy(c), torch.tensor([4.0, 12.0]), torch.tensor([0.7, 1.5]),
+                                 torch.from_numpy(m), 0.001, 1.0)
+    return cases
+
+
 def main(ref_root):
     wf_embedding_torch = extract(os.path.join(ref_root, "tests/wf_embed/wf_embed.py"), "wf_embedding_torch")
     torch_attn = extract(os.path.join(ref_root, "tests/attn/geo_attn.py"), "torch_attn")
@@ -106,6 +125,29 @@ def main(ref_root):
         for nm, t in zip(("dq", "dk", "dv", "dspreads", "dbetas"), leaves):
             blob[f"{name}.{nm}"] = t.grad.numpy()
     np.savez_compressed(os.path.join(HERE, "geoattn_reference.npz"), **blob)
+
+    blob = {}
+    g = torch.Generator().manual_seed(20240604)
+    for name, (q, k, v, coords, spreads, betas, mask, lo, hi) in attn_d64_cases().items():
+        # The dense reference gives NaN rows for padded queries, which poison dK and dV of the whole sample.  The
+        # reference function therefore runs, unmodified, on the valid prefix only (no mask needed); the stored
+        # inputs keep the padded length, so a kernel under test must also get the masking right.
+        nv = int((~mask[0]).sum())
+        assert not mask[0, :nv].any() and mask[0, nv:].all() and q.shape[0] == 1
+        leaves = [t.clone().requires_grad_(True) for t in (q[:, :, :nv], k[:, :, :nv], v[:, :, :nv], spreads, betas)]
+        out = torch_attn(leaves[0], leaves[1], leaves[2], coords[:, :nv], leaves[3], leaves[4],
+                         torch.zeros(1, nv, dtype=torch.bool), lo, hi)  # (mask=None trips a dtype bug in the reference)
+        d_out = torch.randn(q.shape, generator=g).to(torch.bfloat16).float()
+        out.mul(d_out[:, :, :nv]).sum().backward()
+        blob[f"{name}.n_valid"] = np.int64(nv)
+        to16 = lambda t: t.to(torch.bfloat16).view(torch.int16).numpy()  # bf16 bit patterns
+        blob.update({f"{name}.q": to16(q), f"{name}.k": to16(k), f"{name}.v": to16(v), f"{name}.d_out": to16(d_out),
+                     f"{name}.coords": coords.numpy(), f"{name}.spreads": spreads.numpy(), f"{name}.betas": betas.numpy(),
+                     f"{name}.mask": mask.numpy(), f"{name}.min_rbf": np.float64(lo), f"{name}.max_rbf": np.float64(hi),
+                     f"{name}.out": out.detach().numpy().astype(np.float32)})
+        for nm, t in zip(("dq", "dk", "dv", "dspreads", "dbetas"), leaves):
+            blob[f"{name}.{nm}"] = t.grad.numpy()
+    np.savez_compressed(os.path.join(HERE, "geoattn_reference_d64.npz"), **blob)
     print("wrote", sorted(os.listdir(HERE)))
 
 

@@ -97,3 +97,36 @@ def test_config3_forward_backward(ga):
         else:
             ds_tot += ds_r.double()
     assert torch.all((dsig.cpu().double() - ds_tot).abs() <= 2e-2 * ds_tot.abs() + 1e-5), (dsig, ds_tot)
+
+
+def test_in_tree_form_matches_reference_golden(ga, golden_dir):
+    """The logit form the reference tree implements (S + beta Rn |S| with the [min_rbf, max_rbf] window) against outputs
+    and gradients of the reference's own `torch_attn`, at the reference test's tolerance (atol 1e-2, tests/attn/geo_attn.py:39)."""
+    import os
+
+    import numpy as np
+    g = np.load(os.path.join(golden_dir, "geoattn_reference_d64.npz"))
+    bf = lambda a: torch.from_numpy(np.asarray(a)).view(torch.bfloat16)
+    prev = ga.set_logit_form("beta_abs")
+    try:
+        for name in sorted({k.split(".")[0] for k in g.files}):
+            t = {x: torch.from_numpy(np.asarray(g[f"{name}.{x}"])) for x in
+                 ("coords", "spreads", "betas", "mask", "min_rbf", "max_rbf", "n_valid", "out", "dq", "dk", "dv", "dspreads", "dbetas")}
+            nv = int(t["n_valid"])
+            q, k, v = (bf(g[f"{name}.{x}"]).cuda().requires_grad_(True) for x in ("q", "k", "v"))
+            sp, be = t["spreads"].cuda().requires_grad_(True), t["betas"].cuda().requires_grad_(True)
+            out = ga.geometric_attn(q, k, v, t["coords"].cuda(), sp, be, t["mask"].cuda(), float(t["min_rbf"]), float(t["max_rbf"]))
+            out.backward(bf(g[f"{name}.d_out"]).cuda())
+            assert (out[:, :, :nv].float().cpu() - t["out"]).abs().max().item() < 1e-2, name
+            assert torch.all(out[:, :, nv:] == 0)
+            for nm, got in (("dq", q.grad), ("dk", k.grad), ("dv", v.grad)):
+                ref = t[nm]
+                err = (got[:, :, :nv].float().cpu() - ref).abs().max().item()
+                assert err < 1e-2 + ref.abs().max().item() * 2 ** -8, (name, nm, err)  # + bf16 rounding of the returned gradient
+                assert torch.all(got[:, :, nv:] == 0), (name, nm)
+            assert torch.all((sp.grad.cpu() - t["dspreads"]).abs() <= 2e-2 * t["dspreads"].abs() + 5e-3), (name, sp.grad, t["dspreads"])
+            assert torch.all((be.grad.cpu() - t["dbetas"]).abs() <= 2e-2 * t["dbetas"].abs() + 5e-3), (name, be.grad, t["dbetas"])
+    finally:
+        ga.set_logit_form(prev)
+    from proteusai_b200 import _lib
+    _lib.device_status()

@@ -71,3 +71,32 @@ def test_rigid_motion_invariance_and_padding_content_ignored():
     v2[:, :, 20:] = -99.0
     c2[:, 20:] = 1e3
     assert torch.equal(base, geoattn_ref(q, k2, v2, c2, sp, mask=m))
+
+
+def _d64_cases(golden_dir):
+    g = np.load(os.path.join(golden_dir, "geoattn_reference_d64.npz"))
+    bf = lambda a: torch.from_numpy(np.asarray(a)).view(torch.bfloat16).float()
+    for name in sorted({k.split(".")[0] for k in g.files}):
+        t = {x: torch.from_numpy(np.asarray(g[f"{name}.{x}"])) for x in
+             ("coords", "spreads", "betas", "mask", "min_rbf", "max_rbf", "n_valid", "out", "dq", "dk", "dv", "dspreads", "dbetas")}
+        t.update({x: bf(g[f"{name}.{x}"]) for x in ("q", "k", "v", "d_out")})
+        yield name, t
+
+
+def test_golden_d64_in_tree_form(golden_dir):
+    """Head dimension 64: the oracle's in-tree form against the reference function run on the valid prefix."""
+    torch.set_num_threads(1)
+    n_cases = 0
+    for name, t in _d64_cases(golden_dir):
+        nv = int(t["n_valid"])
+        o, grads = geoattn_grads_autograd(t["q"], t["k"], t["v"], t["coords"], t["spreads"], t["d_out"], t["mask"], "beta_abs",
+                                          t["betas"], float(t["min_rbf"]), float(t["max_rbf"]))
+        assert torch.allclose(o[:, :, :nv], t["out"], atol=2e-6, rtol=1e-5), name
+        assert torch.all(o[:, :, nv:] == 0)
+        for nm, got in zip(("dq", "dk", "dv"), grads[:3]):
+            assert torch.allclose(got[:, :, :nv], t[nm], atol=2e-5, rtol=1e-4), (name, nm)
+            assert torch.all(got[:, :, nv:] == 0), (name, nm)
+        assert torch.allclose(grads[3], t["dspreads"], atol=1e-4, rtol=1e-3), name
+        assert torch.allclose(grads[4], t["dbetas"], atol=1e-4, rtol=1e-3), name
+        n_cases += 1
+    assert n_cases == 2
