@@ -176,6 +176,57 @@ def bench_geoattn(dev, world, rank, steps, dist):
             "gpu_launches": 3 * steps}
 
 
+EN_Z, EN_N, EN_SEED = 64, 1024, 1005
+
+
+def bench_encoder(dev, world, rank, steps, dist):
+    """Encoder inference (bf16, random weights): token embedding (vocabulary 33 -> 512) + wavefunction embedding, 4 post-norm
+    layers of geometric attention (H=8, sigma 3..15 A) and a 2048-wide GELU FFN, linear head to 20 logits.  64 chains with
+    lengths uniform in 64..1024 padded to 1024, data-parallel: each rank takes a contiguous slice of the batch.  Returns
+    tokens/s over valid tokens (rank 0)."""
+    from oracle import chains
+    from proteusai_b200 import sharding
+    from proteusai_b200.utils.model_utils.base_modules.encoder import ProteusEncoderModel
+    lengths = chains.draw_lengths(EN_Z, 64, 1024, seed=EN_SEED)
+    b0, b1 = sharding.shard_range(EN_Z, world, rank)
+    coords, mask = chains.chain_batch(lengths[b0:b1], EN_N, seed=EN_SEED + 1 + rank)
+    g = torch.Generator().manual_seed(EN_SEED)
+    tokens = torch.randint(0, 33, (EN_Z, EN_N), generator=g)[b0:b1]
+    torch.manual_seed(EN_SEED)
+    model = ProteusEncoderModel(d_model=512, heads=8, layers=4, d_hidden=2048).to(dev).eval().to_compute_dtype_(torch.bfloat16)
+    coords_p, mask_p, tokens_p = torch.from_numpy(coords).pin_memory(), torch.from_numpy(mask).pin_memory(), tokens.pin_memory()
+    out_host = torch.empty(b1 - b0, EN_N, 20, dtype=torch.bfloat16).pin_memory()
+
+    def step():
+        c, m, t = (x.to(dev, non_blocking=True) for x in (coords_p, mask_p, tokens_p))
+        with torch.no_grad():
+            logits = model(t, c, m)
+        out_host.copy_(logits, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    for a, b in evs:
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    total = sum(a.elapsed_time(b) for a, b in evs)
+    if world > 1:
+        t = torch.tensor([total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total = float(t.item())
+    ms = total / steps
+    valid_tokens = int(lengths.sum())
+    return {"metric": "encoder inference tokens/s (valid tokens, host inputs and outputs included)", "value": valid_tokens / (ms * 1e-3),
+            "unit": "tokens/s", "padded_tokens_per_s": EN_Z * EN_N / (ms * 1e-3), "ms_per_step": ms, "dtype": "bf16",
+            "config": {"workload": "4-layer geometric-attention encoder, d_model 512, H 8, FFN 2048, 64 chains of 64..1024 padded to 1024, seed 1005",
+                       "sharding": f"batch over {world} rank(s), no collective"}}
+
+
 def cpu_port_rate(coords, wn, target_s=12.0, chunk=32):
     """Times the oracle (the reference's dense PyTorch formulation, observer-chunked) on the host
     cores on a bounded run of observer rows.  Returns (evals/s, rows used, seconds)."""
@@ -371,8 +422,12 @@ def main():
     ga = None
     if N_SEQ == 16384 or args.geoattn:
         ga = bench_geoattn(dev, world, rank, args.steps, dist)
+    enc = None
+    if N_SEQ == 16384 or args.geoattn:
+        enc = bench_encoder(dev, world, rank, args.steps, dist)
     if rank == 0:
         line["geoattn"] = ga
+        line["encoder"] = enc
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -90,6 +90,16 @@ class ProteusEncoderModel(nn.Module):
         for enc in self.encoders:
             enc.attn.spread_weights.data = torch.log(sig - enc.attn.min_spread)
 
+    def to_compute_dtype_(self, dtype=torch.bfloat16):
+        """Cast the GEMM / LayerNorm weights to ``dtype`` for inference, keeping in fp32 what the kernels read as fp32
+        and what loses too much in 8 mantissa bits: the wavenumbers (phases reach hundreds of radians) and the spreads."""
+        self.to(dtype)
+        self.wf_embedding.float()
+        for enc in self.encoders:
+            enc.attn.spread_weights.data = enc.attn.spread_weights.data.float()
+            enc.attn.beta_weights.data = enc.attn.beta_weights.data.float()
+        return self
+
     def forward(self, tokens, coords, mask=None):
         wf = self.wf_embedding(coords, None, key_padding_mask=mask)  # fp32 [Z,N,d_model]
         x = self.embed(tokens) + wf.to(self.embed.weight.dtype)
