@@ -131,6 +131,9 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
  *   sigma    [H]       fp32                 per-head RBF spread
  *   betas    [H]       fp32                 per-head RBF weight (logit_form 1)
  *   valid    [Z,N]     u8                   1 = real token, 0 = padding; NULL = all valid
+ *   sample_order [Z]   i32                  optional permutation of the samples (NULL = natural order): CTAs are issued
+ *                                            sample by sample in this order; passing the samples longest-first evens out
+ *                                            the work of neighbouring CTAs on padded batches.  Needs the full zh range.
  *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros
  *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for rows without a valid pair
  *   scale                                    softmax scale, 1/sqrt(d) in the reference
@@ -139,8 +142,9 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
  * bf16 x bf16 -> fp32 tensor-core products, fp32 softmax, P rounded to bf16 before P V.
  */
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d,
-                    float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream);
+                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L,
+                    int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
+                    int zh_begin, int zh_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, backward.
@@ -156,12 +160,12 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
  *   dbetas         [H] fp32, overwritten: gradient w.r.t. betas (logit_form 1; may be NULL for logit_form 0)
  *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned
  *                  (holds D, one fp32 per query row)
- *   zh_begin, zh_end  as in the forward
+ *   sample_order, zh_begin, zh_end  as in the forward
  */
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d);
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
                     const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
-                    float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
+                    const int32_t *sample_order, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
                     void *workspace, size_t workspace_bytes,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
                     int zh_begin, int zh_end, void *stream);

@@ -23,9 +23,9 @@ SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_we_bwd_dk_static_max_k": (c_int, []),
     "pai_we_bwd_dk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "pai_geoattn_fwd": (c_int, [c_void_p] * 9 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+    "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
-    "pai_geoattn_bwd": (c_int, [c_void_p] * 15 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+    "pai_geoattn_bwd": (c_int, [c_void_p] * 16 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
                                 c_int, c_int, c_void_p]),
     "pai_measure_sfu_peak": (c_int, [ctypes.POINTER(c_double), ctypes.POINTER(c_double)]),
 }

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
 
 extern "C" {
 
-int pai_abi_version(void) { return 2; }
+int pai_abi_version(void) { return 3; }
 
 const char *pai_status_str(int status) {
     switch (status) {
@@ -195,8 +195,9 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
 }
 
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, void *O, float *L, int Z, int H, int N, int d, float scale,
-                    float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream) {
+                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L, int Z, int H,
+                    int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
+                    void *stream) {
     if (!Q || !K || !V || !coords || !sigma || !O || !L) return PAI_ERR_NULL_POINTER;
     if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
     if (logit_form == 1 && !betas) return PAI_ERR_NULL_POINTER;
@@ -204,6 +205,7 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
     if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
     if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (sample_order && (zh_begin != 0 || zh_end != Z * H)) return PAI_ERR_UNSUPPORTED;  // a permutation needs the full range
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(coords, 4) ||
         !aligned(sigma, 4) || !aligned(L, 4))
         return PAI_ERR_MISALIGNED;
@@ -239,6 +241,7 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     p.beta = betas;
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
+    p.order = sample_order;
     dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
     pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
@@ -251,9 +254,10 @@ size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
 }
 
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
-                    const float *coords, const float *sigma, const float *betas, const uint8_t *valid, float *dQ, float *dK,
-                    float *dV, float *dsigma, float *dbetas, void *workspace, size_t workspace_bytes, int Z, int H, int N,
-                    int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end, void *stream) {
+                    const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
+                    const int32_t *sample_order, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas, void *workspace,
+                    size_t workspace_bytes, int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf,
+                    int logit_form, int zh_begin, int zh_end, void *stream) {
     if (!Q || !K || !V || !O || !dO || !L || !coords || !sigma || !dQ || !dK || !dV || !dsigma || !workspace)
         return PAI_ERR_NULL_POINTER;
     if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
@@ -262,6 +266,7 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
     if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
     if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (sample_order && (zh_begin != 0 || zh_end != Z * H)) return PAI_ERR_UNSUPPORTED;  // a permutation needs the full range
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(dO, 16) || !aligned(dQ, 16) ||
         !aligned(dK, 16) || !aligned(dV, 16) || !aligned(L, 4) || !aligned(coords, 4) || !aligned(sigma, 4) ||
         !aligned(dsigma, 4) || !aligned(workspace, 16))
@@ -314,6 +319,7 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.beta = betas;
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
+    p.order = sample_order;
     p.Z = Z;
     p.H = H;
     p.N = N;

@@ -74,6 +74,7 @@ struct GaBwdParams {
     int form;              // logit form, as in the forward
     const float *beta;     // [H], form 1 only
     float min_rbf, max_rbf;
+    const int *order;      // [Z] permutation of the samples or nullptr (only with the full (batch, head) range)
 };
 
 // D[zh_local, i] = sum_d O * dO; one warp per row, 2 elements per lane.
@@ -217,7 +218,11 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
     const int qtr = (warp >> 2) & 3;              // which 32 key columns / which 16 output columns
     const int r = (warp & 3) * 32 + lane;         // row inside a tile = TMEM lane
-    const int zh_local = blockIdx.y;
+    int zh_local = blockIdx.y;
+    if (p.order) {  // samples in the given order (longest first): neighbouring CTAs get similar amounts of work
+        const int zp = zh_local / p.H;
+        zh_local = p.order[zp] * p.H + (zh_local - zp * p.H);
+    }
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
     const int j0 = blockIdx.x * GA_BN;

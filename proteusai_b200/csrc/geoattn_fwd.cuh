@@ -72,6 +72,7 @@ struct GaFwdParams {
     int form;
     const float *beta;     // [H], form 1 only
     float min_rbf, max_rbf;
+    const int *order;      // [Z] permutation of the samples or nullptr (only with the full (batch, head) range)
 };
 
 struct GaForm {  // per-head constants of logit form 1
@@ -179,7 +180,11 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const bool is_math = warp < GA_FWD_MATH_THREADS / 32;
     const int half = (warp >> 2) & 1;             // 0: key columns 0..63, 1: 64..127
     const int r = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
-    const int zh_local = blockIdx.y;              // index into the tensor maps (they start at zh_begin)
+    int zh_local = blockIdx.y;                    // index into the tensor maps (they start at zh_begin)
+    if (p.order) {  // samples in the given order (longest first): neighbouring CTAs get similar amounts of work
+        const int zp = zh_local / p.H;
+        zh_local = p.order[zp] * p.H + (zh_local - zp * p.H);
+    }
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
     const int i0 = blockIdx.x * GA_BM;

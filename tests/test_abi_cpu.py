@@ -90,7 +90,7 @@ def test_geoattn_argument_errors(lib):
     p = ctypes.c_void_p(0x1000)
     f = lib.pai_geoattn_fwd
     ok = dict(Z=2, H=2, N=64, d=64)
-    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), None, p, p, kw.get("Z", 2), kw.get("H", 2), kw.get("N", 64),
+    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), None, kw.get("order", None), p, p, kw.get("Z", 2), kw.get("H", 2), kw.get("N", 64),
                          kw.get("d", 64), 0.125, kw.get("lo", 0.0), kw.get("hi", 1.0), kw.get("form", 0), kw.get("zb", 0), kw.get("ze", 4), None]
     assert f(*args(Q=None)) == -1
     assert f(*args(Z=0)) == -2
@@ -101,17 +101,18 @@ def test_geoattn_argument_errors(lib):
     assert f(*args(zb=3, ze=2)) == -6
     assert f(*args(ze=5)) == -6
     assert f(*args(Q=ctypes.c_void_p(0x1008))) == -3
+    assert f(*args(order=p, zb=1)) == -4  # a sample permutation needs the full (batch, head) range
     g = lib.pai_geoattn_bwd
     need = lib.pai_geoattn_bwd_workspace_bytes(2, 2, 64, 64)
     assert need == 2 * 2 * 64 * 4
-    base = [p] * 8 + [p, None] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, None]
+    base = [p] * 8 + [p, None, None] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, None]
     bad = list(base)
-    bad[16] = need - 1
+    bad[17] = need - 1
     assert g(*bad) == -5
     bad = list(base)
     bad[0] = None
     assert g(*bad) == -1
     bad = list(base)
-    bad[24] = 1      # logit form 1 ...
-    bad[14] = None   # ... without a dbetas buffer
+    bad[25] = 1      # logit form 1 ...
+    bad[15] = None   # ... without a dbetas buffer
     assert g(*bad) == -1
