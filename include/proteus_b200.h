@@ -90,6 +90,34 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
                   int Z, int N, int K, int row_begin, int row_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Anisotropic Wavefunction Embedding with per-wavenumber C-beta scaling, forward.
+ * Replaces wf_embedding_kernel_forward() of the variant the reference's model calls by default
+ *   (utils/model_utils/wf_embedding/anisotropic/cb_scaling/learnable_wavenumbers/cuda/wf_embedding_kernel.cu,
+ *   pybind entry in .../cuda/wf_embedding_if.cpp; Python side .../cuda/wf_embedding.py:16-64).
+ *   Phase of wavenumber k for observer i, source j:  k * (r - s_k * (R/r . B_j)),  R = A_i - A_j, r = |R|.
+ *
+ *   coords_a_soa [Z,3,N] fp32   C-alpha coordinates, x/y/z planes
+ *   coords_b_soa [Z,3,N] fp32   C-beta directions (unit vectors), x/y/z planes
+ *   valid        [Z,N]   u8     1 = real token, 0 = padding; NULL = all valid
+ *   cb_magnitudes [K], wavenumbers [K] fp32
+ *   out          [Z,N,2K] fp32  interleaved sum_j cos(phase)/r, sum_j sin(phase)/r
+ *   d_cb, d_k    [Z,N,2K] fp32  derivative of every output element w.r.t. s_k and w.r.t. k (kept for the backward)
+ *   row_begin,row_end           as in pai_we_fwd
+ */
+int pai_we_aniso_fwd(const float *coords_a_soa, const float *coords_b_soa, const uint8_t *valid,
+                     const float *cb_magnitudes, const float *wavenumbers, float *out, float *d_cb, float *d_k,
+                     int Z, int N, int K, int row_begin, int row_end, void *stream);
+
+/* Anisotropic Wavefunction Embedding, backward.  Replaces the PyTorch expressions in _wf_embedding.backward
+ *   (.../learnable_wavenumbers/cuda/wf_embedding.py:66-79):
+ *   grad_cb[k] = sum_{z,n} dO[z,n,2k] d_cb[z,n,2k] + dO[z,n,2k+1] d_cb[z,n,2k+1], and the same with d_k.
+ *   workspace: at least pai_we_aniso_bwd_workspace_bytes(Z,N,K) bytes, 16-byte aligned; results are bit-reproducible. */
+size_t pai_we_aniso_bwd_workspace_bytes(int Z, int N, int K);
+int pai_we_aniso_bwd(const float *dO, const float *d_cb, const float *d_k, float *grad_cb, float *grad_wavenumbers,
+                     void *workspace, size_t workspace_bytes, int Z, int N, int K, int row_begin, int row_end,
+                     void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Wavefunction Embedding, backward w.r.t. the wavenumbers, without any caller-provided scratch.
  * No counterpart in the reference: this entry point exists for callers that cannot allocate device
  * memory at the time of the call, for example a serving process that handed the whole GPU to its own

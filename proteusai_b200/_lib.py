@@ -21,6 +21,9 @@ SIGNATURES = {
     "pai_we_bwd_dk_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pai_we_bwd_dk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "pai_we_aniso_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "pai_we_aniso_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "pai_we_aniso_bwd": (c_int, [c_void_p] * 6 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_we_bwd_dk_static_max_k": (c_int, []),
     "pai_we_bwd_dk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),

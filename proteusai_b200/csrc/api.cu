@@ -6,6 +6,7 @@
 #include "geoattn_fwd.cuh"
 #include "we_bwd.cuh"
 #include "we_fwd.cuh"
+#include "we_aniso_fwd.cuh"
 
 #include <cstdlib>
 #include <cstring>
@@ -328,6 +329,69 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
     pai::geoattn_bwd_kernel<<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();
+}
+
+int pai_we_aniso_fwd(const float *coords_a_soa, const float *coords_b_soa, const uint8_t *valid, const float *cb_magnitudes,
+                     const float *wavenumbers, float *out, float *d_cb, float *d_k, int Z, int N, int K, int row_begin,
+                     int row_end, void *stream) {
+    if (!coords_a_soa || !coords_b_soa || !cb_magnitudes || !wavenumbers || !out || !d_cb || !d_k) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || Z > 65535 || N < 1 || K < 1 || (long long)N * K > (1ll << 40)) return PAI_ERR_BAD_SHAPE;
+    if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(coords_a_soa, 4) || !aligned(coords_b_soa, 4) || !aligned(cb_magnitudes, 4) || !aligned(wavenumbers, 4) ||
+        !aligned(out, 4) || !aligned(d_cb, 4) || !aligned(d_k, 4))
+        return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    if (row_begin == row_end) return PAI_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t rows = (size_t)(row_end - row_begin), pitch = (size_t)N * 2 * K * sizeof(float), width = rows * 2 * K * sizeof(float);
+    float *bufs[3] = {out, d_cb, d_k};
+    for (float *b : bufs) {
+        cudaError_t ce = cudaMemset2DAsync(b + (size_t)row_begin * 2 * K, pitch, 0, width, (size_t)Z, st);
+        if (ce != cudaSuccess) return (int)ce;
+    }
+    int sms = 0;
+    if (int e = current_device_sms(&sms)) return e;
+    pai::WeAnisoParams p;
+    p.coords_a = coords_a_soa;
+    p.coords_b = coords_b_soa;
+    p.valid = valid;
+    p.cb = cb_magnitudes;
+    p.wn = wavenumbers;
+    p.out = out;
+    p.d_cb = d_cb;
+    p.d_k = d_k;
+    p.N = N;
+    p.K = K;
+    p.row_begin = row_begin;
+    p.row_end = row_end;
+    p.use_tma = (aligned(coords_a_soa, 16) && aligned(coords_b_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
+    return pai::we_aniso_fwd_launch(p, Z, sms, st);
+}
+
+size_t pai_we_aniso_bwd_workspace_bytes(int Z, int N, int K) {
+    (void)Z;
+    (void)N;
+    if (K < 1) return 0;
+    return (size_t)pai::WE_BWD_MAX_BLOCKS * 2 * (size_t)K * sizeof(float);
+}
+
+int pai_we_aniso_bwd(const float *dO, const float *d_cb, const float *d_k, float *grad_cb, float *grad_wavenumbers, void *workspace,
+                     size_t workspace_bytes, int Z, int N, int K, int row_begin, int row_end, void *stream) {
+    if (!dO || !d_cb || !d_k || !grad_cb || !grad_wavenumbers || !workspace) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || (long long)Z * N > (1ll << 30)) return PAI_ERR_BAD_SHAPE;
+    if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
+    if (!aligned(dO, 8) || !aligned(d_cb, 8) || !aligned(d_k, 8) || !aligned(grad_cb, 4) || !aligned(grad_wavenumbers, 4) ||
+        !aligned(workspace, 16))
+        return PAI_ERR_MISALIGNED;
+    if (workspace_bytes < pai_we_aniso_bwd_workspace_bytes(Z, N, K)) return PAI_ERR_WORKSPACE_TOO_SMALL;
+    if (int e = require_sm100()) return e;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (row_begin == row_end) {
+        cudaError_t ce = cudaMemsetAsync(grad_cb, 0, (size_t)K * sizeof(float), st);
+        if (ce != cudaSuccess) return (int)ce;
+        return (int)cudaMemsetAsync(grad_wavenumbers, 0, (size_t)K * sizeof(float), st);
+    }
+    return pai::we_aniso_bwd_launch(dO, d_cb, d_k, grad_cb, grad_wavenumbers, (float *)workspace, Z, N, K, row_begin, row_end, st);
 }
 
 // ---- allocation-free variant of the WE backward --------------------------------------------------

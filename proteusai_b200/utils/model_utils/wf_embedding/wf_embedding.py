@@ -4,12 +4,14 @@ Mirrors ``utils/model_utils/wf_embedding/wf_embedding.py:24-49`` of the referenc
 constructor arguments, same parameter names (``wavenumbers`` holds log-wavenumbers,
 ``aa_magnitudes``), same wavelength schedule (``logspace(0, 1, K, base)``, i.e. exponents
 ``i / (K - 1)``), same ``forward(coords_alpha, coords_beta, key_padding_mask)`` signature, so a
-reference checkpoint loads.  Only the isotropic kernel exists here: ``anisotropic=True`` (the
-reference's default) raises instead of silently computing something else.
+reference checkpoint loads.  Both branches of the reference are provided: the isotropic kernel and the
+anisotropic one with per-wavenumber C-beta scaling (``wf_embedding_learnCB``, the reference's default).
 """
 import torch
 import torch.nn as nn
 
+from proteusai_b200.utils.model_utils.wf_embedding.anisotropic.cb_scaling.learnable_wavenumbers.cuda.wf_embedding import (
+    wf_embedding as wf_embedding_learnCB)
 from proteusai_b200.utils.model_utils.wf_embedding.isotropic.cuda.wf_embedding import wf_embedding as wf_embedding_iso
 
 
@@ -28,6 +30,5 @@ class WaveFunctionEmbedding(nn.Module):
 
     def forward(self, coords_alpha, coords_beta=None, key_padding_mask=None):
         if self.aniso:
-            raise NotImplementedError(
-                "anisotropic wavefunction embedding is not part of the B200 hot path; construct with anisotropic=False")
+            return wf_embedding_learnCB(coords_alpha, coords_beta, self.aa_magnitudes, self.get_wavenumbers(), mask=key_padding_mask)
         return wf_embedding_iso(coords_alpha, self.get_wavenumbers(), magnitude_type=1, dropout_p=0.0, mask=key_padding_mask)

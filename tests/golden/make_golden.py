@@ -10,6 +10,7 @@ are cut out of their files by AST and executed as they stand:
 
 * ``wf_embedding_torch``  from ``tests/wf_embed/wf_embed.py``
 * ``torch_attn``          from ``tests/attn/geo_attn.py``
+* ``wf_embedding_torch``  (anisotropic, C-beta scaling) from ``tests/wf_embed/wf_embed_aniso_learnCB_learnK.py``
 
 Inputs are seeded; inputs and the reference's outputs (and gradients obtained by
 autograd through the reference functions, as the reference's tests do) are stored in
@@ -148,6 +149,31 @@ def main(ref_root):
         for nm, t in zip(("dq", "dk", "dv", "dspreads", "dbetas"), leaves):
             blob[f"{name}.{nm}"] = t.grad.numpy()
     np.savez_compressed(os.path.join(HERE, "geoattn_reference_d64.npz"), **blob)
+
+    # anisotropic WE with per-wavenumber C-beta scaling: outputs and autograd gradients of the reference function
+    aniso_torch = extract(os.path.join(ref_root, "tests/wf_embed/wf_embed_aniso_learnCB_learnK.py"), "wf_embedding_torch")
+    g = torch.Generator().manual_seed(20240605)
+    blob = {}
+    z, n, k = 2, 80, 12
+    cases = {}
+    # the reference test's own input style: A = max_wl * rand, B = normalised randn, cb = rand, wavenumbers = randn
+    a = 20 * torch.rand((z, n, 3), generator=g)
+    b = torch.randn((z, n, 3), generator=g)
+    b = b / torch.linalg.vector_norm(b, dim=2, keepdim=True)
+    a[1, 8] = a[1, 7]  # a coincident pair
+    cases["rand"] = (a, b, torch.rand((k,), generator=g), torch.randn((k,), generator=g), torch.zeros(z, n, dtype=torch.bool))
+    c, m = chains.chain_batch([80, 51], 80, seed=17)
+    cases["chain_padded"] = (torch.from_numpy(c), b, torch.rand((k,), generator=g) * 2, torch.from_numpy(chains.wavenumbers(2 * k)),
+                             torch.from_numpy(m))
+    for name, (ca, cbv, cbm, wn, mask) in cases.items():
+        cbm_g, wn_g = cbm.clone().requires_grad_(True), wn.clone().requires_grad_(True)
+        out = aniso_torch(ca, cbv, cbm_g, wn_g, mask)
+        d_out = torch.randn(out.shape, generator=g)
+        (out * d_out).sum().backward()
+        blob.update({f"{name}.coords_a": ca.numpy(), f"{name}.coords_b": cbv.numpy(), f"{name}.cb": cbm.numpy(), f"{name}.wn": wn.numpy(),
+                     f"{name}.mask": mask.numpy(), f"{name}.d_out": d_out.numpy(), f"{name}.out": out.detach().numpy(),
+                     f"{name}.d_cb": cbm_g.grad.numpy(), f"{name}.d_wn": wn_g.grad.numpy()})
+    np.savez_compressed(os.path.join(HERE, "we_aniso_reference.npz"), **blob)
     print("wrote", sorted(os.listdir(HERE)))
 
 
