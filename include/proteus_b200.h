@@ -183,7 +183,7 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
  *   Q, K, V, O, dO [Z,H,N,d] bf16 contiguous (d must be 64); L [Z,H,N] fp32 as written by the forward
  *   dQ, dK, dV     [Z,H,N,d] fp32, like the reference's gradients (:626-628); every row of the
  *                  (batch, head) range is written, rows of padded tokens as zeros; dQ is accumulated
- *                  across key tiles with reduce-add copies, so its summation order is not fixed
+ *                  across key tiles with fp32 reductions, so its summation order is not fixed
  *   dsigma         [H] fp32, overwritten: gradient w.r.t. the spreads summed over the (batch, head) range
  *   dbetas         [H] fp32, overwritten: gradient w.r.t. betas (logit_form 1; may be NULL for logit_form 0)
  *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned

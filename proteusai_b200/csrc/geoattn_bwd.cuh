@@ -21,8 +21,8 @@
 //     dP  = dO_i V_j^T    A K-major,  B K-major     -> TMEM [128 x 128]
 //     dV += P^T dO_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
 //     dK += dS^T Q_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
-//     dQ_i = dS K_j       A K-major,  B MN-major    -> TMEM [128 x 64], reduced into global fp32 dQ
-//                                                      with bulk reduce-add copies (one per 32 rows)
+//     dQ_i = dS K_j       A K-major,  B MN-major    -> TMEM [128 x 64], read back and added into the global
+//                                                      fp32 dQ with 16-byte vector reductions
 // P and dS are written by the math threads as bf16 into shared memory in the swizzled [i][j] layout,
 // which serves both as K-major (dQ) and MN-major (dV, dK) operand.  The element-wise stage runs in
 // packed fp32x2 arithmetic with |r_i - r_j|^2 from centred coordinates (three FMAs).  Query tiles
@@ -43,13 +43,12 @@ struct GaBwdSmem {
     alignas(1024) uint8_t dout[2][GA_TILE_BYTES];
     alignas(1024) uint8_t p[2 * GA_TILE_BYTES];
     alignas(1024) uint8_t ds[2 * GA_TILE_BYTES];
-    alignas(1024) float dq[GA_BM * GA_D];  // fp32 staging for the reduce-add, row-major
     // centred key coordinates, two keys per entry:
     float4 ka[GA_BN / 2];                  // {x_j, x_j+1, y_j, y_j+1}
     float4 kc[GA_BN / 2];                  // {z_j, z_j+1, |k_j|^2, |k_j+1|^2}
     alignas(16) float kb[GA_BN];           // additive mask: 0 for a valid key, -inf for a padded one
     uint16_t tiles[GA_MAX_TILES];          // query tiles that hold at least one valid query
-    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_g, bar_pds, bar_dqr;
+    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_g, bar_vk, bar_pds, bar_dqr;
     uint32_t tmem_base;
     int ntiles;
     int first_k;                           // first valid key of the tile (origin of the centring)
@@ -91,23 +90,8 @@ __global__ void __launch_bounds__(256) geoattn_bwd_dsum_kernel(const __nv_bfloat
     if (lane == 0) dsum[row] = s;
 }
 
-__device__ __forceinline__ void bulk_reduce_add_f32(float *dst_gmem, const float *src_smem, uint32_t bytes) {
-    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_gmem),
-                 "r"(smem_u32(src_smem)), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
-
-// barrier among the four math warps that share 32 query rows (immediate ids, see named_bar_sync)
-__device__ __forceinline__ void group_bar_sync(int quarter) {
-    switch (quarter) {
-        case 0: named_bar_sync<1>(128); break;
-        case 1: named_bar_sync<2>(128); break;
-        case 2: named_bar_sync<3>(128); break;
-        default: named_bar_sync<4>(128); break;
-    }
+__device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 struct GaBwdRow {  // per-thread constants of the current query row, packed for fp32x2 arithmetic
@@ -119,7 +103,8 @@ struct GaBwdRow {  // per-thread constants of the current query row, packed for 
 template <bool MASKED, int FORM>
 __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const float4 *ka, const float4 *kc, const float *kb,
                                              const GaBwdRow &rw, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
-                                             f2_t &dbeta2, uint8_t *p_tile, uint8_t *ds_tile, int r, int chunk0) {
+                                             f2_t &dbeta2, uint8_t *p_tile, uint8_t *ds_tile, int r, int chunk0, uint64_t *gate,
+                                             uint32_t gate_parity) {
     uint32_t sv[16], dpv[16];
     tmem_ld16(t_s, sv);
     tmem_ld16(t_dp, dpv);
@@ -202,6 +187,8 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const 
             pw[e] = pack_bf16x2(p0, p1);
             dw[e] = pack_bf16x2(d0, d1);
         }
+        // the previous tile's dV / dK MMAs read the P and dS tiles: no store before they have completed
+        if (gate != nullptr && g == 0) mbar_wait_timed(gate, gate_parity);
         const int chunk = chunk0 + g;
         const uint32_t off = (chunk >> 3) * GA_TILE_BYTES + sw128_offset(r, chunk & 7);
         *reinterpret_cast<uint4 *>(p_tile + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
@@ -297,6 +284,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&sm.bar_qdo[1], 1);
             mbar_init(&sm.bar_sp, 1);
             mbar_init(&sm.bar_g, 1);
+            mbar_init(&sm.bar_vk, 1);
             mbar_init(&sm.bar_pds, GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_dqr, GA_BWD_MATH_THREADS);
             mbar_fence_init();
@@ -338,20 +326,23 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                             IDESC_SP, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_sp);
             };
-            auto issue_grads = [&](int buf, bool first) {
-                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
+            auto issue_dq = [&]() {  // the math warps wait for this one; K = 16 keys per step
 #pragma unroll
-                for (int kk = 0; kk < GA_BN / 16; ++kk)  // dQ first: the math warps wait for it; K = 16 keys per step
+                for (int kk = 0; kk < GA_BN / 16; ++kk)
                     umma_ss(tm_dq, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
                             umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_DQ, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_g);
+            };
+            auto issue_dv_dk = [&](int buf, bool first) {  // K = 16 query rows per step: 2 KiB down the [i][j] tiles
+                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
 #pragma unroll
-                for (int kk = 0; kk < GA_BM / 16; ++kk) {  // K = 16 query rows per step: 2 KiB down the [i][j] tiles
+                for (int kk = 0; kk < GA_BM / 16; ++kk) {
                     umma_ss(tm_dv, umma_desc_sw128(p_addr + kk * 2048, GA_TILE_BYTES, 1024),
                             umma_desc_sw128(do_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
                     umma_ss(tm_dk, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024),
                             umma_desc_sw128(q_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
                 }
+                umma_commit(&sm.bar_vk);
             };
             mbar_expect_tx(&sm.bar_kv, 2 * GA_TILE_BYTES);
             tma_load_3d(sm.k, &map_k, 0, j0, zh_local, &sm.bar_kv);
@@ -368,16 +359,16 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 mbar_wait_timed(&sm.bar_pds, par);  // P, dS(t) written; S, dP(t) consumed
                 if (t > 0) mbar_wait_timed(&sm.bar_dqr, par ^ 1);  // dQ(t-1) has been read out of TMEM
                 tc_fence_after();
-                issue_grads(buf, t == 0);
+                // dQ(t) first (the math warps stage it next), then the next tile's S and dP so that its element-wise
+                // stage can start while dV / dK(t) are still running; P and dS(t) stay untouched until bar_vk(t)
+                issue_dq();
                 if (t + 1 < nt) {
                     mbar_wait_timed(&sm.bar_qdo[buf ^ 1], (uint32_t)(((t + 1) >> 1) & 1));
-                    issue_s_dp(buf ^ 1);  // the next tile's S / dP run behind the gradient MMAs
-                    // everything issued so far (grads(t) included) completes before bar_sp(t+1) fires
-                } else {
-                    umma_commit(&sm.bar_sp);  // final completion signal for the dV / dK accumulation
+                    issue_s_dp(buf ^ 1);
                 }
+                issue_dv_dk(buf, t == 0);
                 if (t + 2 < nt) {  // Q / dO buffer `buf` is free once S, dP(t) and the gradient MMAs(t) are done
-                    mbar_wait_timed(&sm.bar_sp, par ^ 1);
+                    mbar_wait_timed(&sm.bar_vk, par);
                     load_qdo(buf, sm.tiles[t + 2]);
                 }
             }
@@ -398,16 +389,14 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             fm.rmin = p.min_rbf;
             fm.rmax = p.max_rbf;
         }
-        float *stage = sm.dq + (warp & 3) * 32 * GA_D;  // the 32 rows this warp shares with three others
-        const bool copy_lane = qtr == 0 && lane == 0;   // issues the reduce-add copy of those 32 rows
 
-        for (int t = 0; t < nt; ++t) {
-            const uint32_t par = (uint32_t)(t & 1);
-            const int i0 = sm.tiles[t] * GA_BM;
-            const int row = i0 + r;
-            // per-row inputs of this query tile (overlaps the S / dP MMAs)
+        float qcx, qcy, qcz, l2, dsum;
+        auto load_row = [&](int tile) {
+            const int row = tile * GA_BM + r;
             const bool q_ok = row < N && (vz ? vz[row] != 0 : true);
-            float qcx = 0.f, qcy = 0.f, qcz = 0.f, l2 = INFINITY, dsum = 0.f;  // l2 = +inf: P = 0 for a padded query
+            qcx = qcy = qcz = 0.f;
+            l2 = INFINITY;  // +inf: P = 0 for a padded query
+            dsum = 0.f;
             if (q_ok) {
                 qcx = cz[row * 3] - orx;
                 qcy = cz[row * 3 + 1] - ory;
@@ -416,6 +405,12 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 l2 = lse == -INFINITY ? INFINITY : lse * 1.4426950408889634f;  // a row without any valid pair: P = 0
                 dsum = p.dsum[(size_t)zh_local * N + row];
             }
+        };
+        load_row(sm.tiles[0]);
+        for (int t = 0; t < nt; ++t) {
+            const uint32_t par = (uint32_t)(t & 1);
+            const int i0 = sm.tiles[t] * GA_BM;
+            // per-row inputs of this query tile (loaded during the previous tile, see the end of the loop body)
             GaBwdRow rw;
             rw.qx2 = f2_pack(-2.f * qcx, -2.f * qcx);
             rw.qy2 = f2_pack(-2.f * qcy, -2.f * qcy);
@@ -430,7 +425,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     _Pragma("unroll") for (int c = 0; c < 2; ++c) ga_bwd_chunk<MASKED, FORM>(                                                \
         tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16, &sm.ka[qtr * 16 + c * 8],               \
         &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2, scale2, fm, dsig2, dbeta2, sm.p, sm.ds, r,       \
-        qtr * 4 + c * 2)
+        qtr * 4 + c * 2, (t > 0 && c == 0) ? &sm.bar_vk : nullptr, par ^ 1)
             if (p.form == 0) {
                 if (has_hole) { PAI_GA_BWD(true, 0); } else { PAI_GA_BWD(false, 0); }
             } else {
@@ -440,35 +435,29 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             fence_proxy_async();
             tc_fence_before();
             mbar_arrive(&sm.bar_pds);
-            // dQ tile: TMEM -> fp32 staging -> bulk reduce-add into global dQ (one copy per 32 rows)
+            if (t + 1 < nt) load_row(sm.tiles[t + 1]);  // the loads fly while the MMAs run
+            // dQ tile: TMEM -> registers -> vector reductions into the global fp32 dQ
             mbar_wait_timed(&sm.bar_g, par);
             tc_fence_after();
-            if (copy_lane) bulk_wait_group_read0();  // the previous copy has finished reading the staging
-            group_bar_sync(warp & 3);
             {
                 uint32_t v[16];
                 tmem_ld16(tm_dq + lane_base + qtr * 16, v);
                 tmem_wait_ld();
                 tc_fence_before();
                 mbar_arrive(&sm.bar_dqr);
+                const int row = i0 + r;
+                if (row < N) {
+                    float *dst = p.dq + ((size_t)zh * N + row) * GA_D + qtr * 16;
 #pragma unroll
-                for (int e = 0; e < 16; e += 4)
-                    *reinterpret_cast<uint4 *>(stage + lane * GA_D + qtr * 16 + e) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
-            }
-            fence_proxy_async();
-            group_bar_sync(warp & 3);
-            if (copy_lane) {
-                const int r0 = i0 + (warp & 3) * 32;
-                const int nrows = min(32, N - r0);
-                if (nrows > 0) {
-                    bulk_reduce_add_f32(p.dq + ((size_t)zh * N + r0) * GA_D, stage, (uint32_t)nrows * GA_D * 4);
-                    bulk_commit_group();
+                    for (int e = 0; e < 16; e += 4)
+                        red_add_v4(dst + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                                   __uint_as_float(v[e + 3]));
                 }
             }
         }
 
         // ---- epilogue: dV, dK rows of this key tile; dsigma -------------------------------------------
-        mbar_wait_timed(&sm.bar_sp, (uint32_t)(nt & 1));  // the last commit: every accumulation has completed
+        mbar_wait_timed(&sm.bar_vk, (uint32_t)((nt - 1) & 1));  // the last dV / dK accumulation has completed
         tc_fence_after();
         {
             uint32_t a[16], b[16];
@@ -496,7 +485,6 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             sm.dsig[warp] = dsig_acc;
             sm.dbeta[warp] = dbeta_acc;
         }
-        if (copy_lane) bulk_wait_group0();  // the reduce-add copies issued by this lane have completed
     }
     tc_fence_before();
     __syncthreads();
