@@ -430,11 +430,14 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const float m_safe = m_run == -INFINITY ? 0.f : m_run;  // a row without any valid pair so far: P = 2^(-inf) = 0
             const f2_t mn2 = f2_pack(m_safe, m_safe);
             f2_t l2 = 0ull;
+            uint32_t va[16], vb[16];  // two chunks in flight: the TMEM load of the next overlaps the exponentials of this one
+            tmem_ld16(tmem_s + lane_base + half * 64, va);
+            tmem_wait_ld();
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t v[16];
-                tmem_ld16(tmem_s + lane_base + half * 64 + c * 16, v);
-                tmem_wait_ld();
+                uint32_t(&v)[16] = (c & 1) ? vb : va;
+                uint32_t(&vn)[16] = (c & 1) ? va : vb;
+                if (c + 1 < 4) tmem_ld16(tmem_s + lane_base + half * 64 + (c + 1) * 16, vn);
                 float ex[16];
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
@@ -453,6 +456,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     }
                     *reinterpret_cast<uint4 *>(sm.p + half * GA_TILE_BYTES + sw128_offset(r, c * 2 + g)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
+                if (c + 1 < 4) tmem_wait_ld();
             }
             float l0, l1;
             f2_unpack(l2, l0, l1);
