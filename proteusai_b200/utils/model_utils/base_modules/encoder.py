@@ -4,8 +4,9 @@ encoder-only model used as the end-to-end inference configuration.
 ``GeoAttention`` keeps the reference's constructor, parameter names and semantics
 (``old/old_scripts/encoder.py:43-121``): per-head projection weights ``q_proj/k_proj/v_proj [H, d_model, d_k]``
 with biases ``[H, d_k]``, ``spreads = min_spread + exp(spread_weights)``, ``betas = exp(beta_weights)``,
-heads concatenated d_k-major / head-minor before the bias-free ``out_proj``.  The three projections run as one
-batched GEMM each that writes ``[Z, H, N, d_k]`` directly, the layout the kernel's TMA maps read.
+heads concatenated d_k-major / head-minor before the bias-free ``out_proj``.  The projections run as one GEMM
+over all heads (and over Q, K, V together for self-attention) instead of the reference's per-head broadcast
+matmul, which copies the input once per head.
 
 ``Encoder`` is the reference's post-norm block (``old/old_scripts/encoder.py:8-41``): ``LN(x + drop(attn))``
 then ``LN(x + drop(ffn))``.  The reference's ``forward`` passes ``coords_beta`` positionally into a
@@ -41,16 +42,24 @@ class GeoAttention(nn.Module):
     def get_betas(self):
         return torch.exp(self.beta_weights)
 
-    def _project(self, x, w, b):
-        # [Z,N,D] x [H,D,dk] -> [Z,H,N,dk]
-        return torch.matmul(x.unsqueeze(1), w.to(x.dtype).unsqueeze(0)) + b.to(x.dtype)[None, :, None, :]
+    def _project(self, x, weights, biases):
+        """Per-head projections ``x W_h + b_h`` for one or several weight sets as ONE GEMM:
+        ``[Z*N, D] x [D, S*H*dk]`` (the reference's broadcast ``matmul(x.unsqueeze(1), W.unsqueeze(0))`` materialises
+        ``x`` once per head).  Returns a list of ``[Z, H, N, dk]`` views."""
+        z, n, d = x.shape
+        w2 = torch.cat([w.permute(1, 0, 2).reshape(d, self.heads * self.d_k) for w in weights], dim=1).to(x.dtype)
+        b2 = torch.cat([b.reshape(self.heads * self.d_k) for b in biases]).to(x.dtype)
+        y = torch.addmm(b2, x.reshape(z * n, d), w2).view(z, n, len(weights), self.heads, self.d_k)
+        return [y[:, :, i].permute(0, 2, 1, 3) for i in range(len(weights))]
 
     def forward(self, q, k, v, coords, mask=None, flash=True):
         assert q.shape == k.shape == v.shape and q.dim() == 3 and q.shape[2] == self.d_model
         batch, n, _ = q.shape
-        Q = self._project(q, self.q_proj, self.q_bias)
-        K = self._project(k, self.k_proj, self.k_bias)
-        V = self._project(v, self.v_proj, self.v_bias)
+        if q is k and k is v:  # self-attention: one fused GEMM for Q, K and V
+            Q, K, V = self._project(q, (self.q_proj, self.k_proj, self.v_proj), (self.q_bias, self.k_bias, self.v_bias))
+        else:
+            (Q,), (K,), (V,) = (self._project(x, (w,), (b,)) for x, w, b in
+                                ((q, self.q_proj, self.q_bias), (k, self.k_proj, self.k_bias), (v, self.v_proj, self.v_bias)))
         out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
                              min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
         out = out.permute(0, 2, 3, 1).reshape(batch, n, self.d_model)  # d_k-major, head-minor
