@@ -35,6 +35,27 @@ int current_device_cc(int *cc_out) {
     return 0;
 }
 
+// Run counters of the WE forward (one 4-byte slot per launch in flight, handed out round-robin): part of the
+// library image so that the entry point needs no workspace argument.
+static __device__ unsigned g_we_run_counters[256];
+
+int next_we_counter(unsigned **slot) {
+    static unsigned *base[64];
+    static unsigned next[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return (int)PAI_ERR_UNSUPPORTED;
+    if (!base[dev]) {
+        unsigned *p = nullptr;
+        e = cudaGetSymbolAddress((void **)&p, g_we_run_counters);
+        if (e != cudaSuccess) return (int)e;
+        base[dev] = p;
+    }
+    *slot = base[dev] + (__atomic_fetch_add(&next[dev], 1u, __ATOMIC_RELAXED) & 255u);
+    return 0;
+}
+
 int current_device_sms(int *sms_out) {
     static int cache[64];
     int dev = 0;
@@ -166,9 +187,11 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     if (ce != cudaSuccess) return (int)ce;
     int sms = 0;
     if (int e = current_device_sms(&sms)) return e;
+    unsigned *counter = nullptr;
+    if (int e = next_we_counter(&counter)) return e;
     return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_TJ", 0), env_int("PAI_WE_WAVES", 0),
                               env_int("PAI_WE_REPRODUCIBLE", 0) != 0, env_int("PAI_WE_RANGE_REDUCE", 0) != 0,
-                              env_int("PAI_WE_POLY_PAIRS", 1), sms, st);
+                              env_int("PAI_WE_POLY_PAIRS", 1), sms, counter, st);
 }
 
 size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {

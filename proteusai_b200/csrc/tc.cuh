@@ -8,13 +8,13 @@
 namespace pai {
 
 // ---- time-bounded mbarrier wait ---------------------------------------------------------------
-// Gives up after ~1 s of SM clock and records the failure in the device status word; the caller
+// Gives up after ~0.1 s of SM clock and records the failure in the device status word; the caller
 // carries on (results are then garbage, the host sees the status), so no wait can hang the GPU.
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t *bar, uint32_t parity) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 2000000000ll) {
+        if (clock64() - t0 > 200000000ll) {
             atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
             return false;
         }

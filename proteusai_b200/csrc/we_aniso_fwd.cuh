@@ -230,6 +230,7 @@ static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, cudaStream_t str
     const long long resident = (long long)sms * WE_CTAS_PER_SM;
     int tj = WE_TJ_MAX;
     while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
+    if (p.valid && tj > 64) tj = 64;  // with padding, short tiles waste less on the tile that straddles a sample's end
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
     p.units = items * p.tiles;

@@ -11,7 +11,8 @@
 //     block, group of 4 slices); it needs all source tiles of its batch element;
 //   * the (item, source tile) pairs form one linear sequence which is cut into equal runs, one
 //     per CTA of a grid of (SM count x 4 resident CTAs x a few waves).  Every SM therefore gets
-//     the same amount of work whatever the shape or the shard size, at the price of items that
+//     the same amount of work whatever the shape or the shard size (the CTAs draw runs from a global
+//     counter, so padded batches, whose runs are very unequal, balance too), at the price of items that
 //     straddle a cut: each run adds its partial sums into the zero-filled outputs with fp32
 //     reductions, so the last bit of a sum can differ from run to run.  A "reproducible" launch
 //     mode keeps every run at least one item long: then an output element receives at most two
@@ -49,12 +50,15 @@ struct WeFwdParams {
     int obs_blocks;        // 32-observer blocks per batch element
     int k_groups;          // groups of WE_WARPS * KS wavenumbers
     long long units;       // Z * obs_blocks * k_groups * tiles
+    int nruns;             // the unit sequence is cut into this many equal runs
+    unsigned *counter;     // zeroed before the launch: CTAs draw run indices from it (nullptr: run = blockIdx.x)
 };
 
 struct __align__(16) WeSmem {
     float stage[2][3][WE_TJ_MAX];  // x/y/z planes, two stages
     float4 tile[WE_TJ_MAX];        // repacked {x,y,z,valid}
     uint64_t bar[2];
+    unsigned run;
 };
 
 // KS: wavenumbers per lane (even).  MAG1: compile-time fast path for magnitude_type == 1.
@@ -73,11 +77,6 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = p.N, K = p.K;
     const bool tma = p.use_tma != 0;
-
-    // this CTA's run of (item, tile) units
-    const long long u0 = p.units * blockIdx.x / gridDim.x;
-    const long long u1 = p.units * (blockIdx.x + 1) / gridDim.x;
-    if (u0 >= u1) return;
 
     auto issue_tile = [&](long long u, int st) {  // thread 0: bulk-copy the three planes of unit u's tile
         const long long item = u / p.tiles;
@@ -99,7 +98,6 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
             fence_proxy_async();
         }
         __syncthreads();
-        if (tid == 0) issue_tile(u0, 0);
     }
 
     // state of the current item
@@ -139,11 +137,25 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
         }
     };
 
+    // Runs are drawn from a global counter (padded batches make runs very unequal, so a static assignment would
+    // leave SMs idle) or, for reproducible sums, assigned by block index.  n counts the units this CTA has staged
+    // so far: it selects the staging buffer and the mbarrier phase across runs.
     bool timed_out = false;
-    for (long long u = u0; u < u1; ++u) {
-        const int n = (int)(u - u0), st = n & 1;
+    int n = 0;
+    for (;;) {
+    unsigned run = blockIdx.x;
+    if (p.counter) {
+        if (tid == 0) sm.run = atomicAdd(p.counter, 1u);
+        __syncthreads();  // (the next write of sm.run comes after the barriers inside the run)
+        run = sm.run;
+    }
+    if (run >= (unsigned)p.nruns) break;
+    const long long u0 = p.units * run / p.nruns;
+    const long long u1 = p.units * (run + 1) / p.nruns;
+    if (tma && tid == 0 && u0 < u1) issue_tile(u0, n & 1);  // that buffer was drained two units ago
+    for (long long u = u0; u < u1; ++u, ++n) {
+        const int st = n & 1;
         if (tma && tid == 0 && u + 1 < u1) issue_tile(u + 1, st ^ 1);  // stage st^1 was drained by the previous repack
-
         const long long item = u / p.tiles;
         const int tile = (int)(u - item * p.tiles);
         if (item != cur_item) {
@@ -270,11 +282,13 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
             }
         }
     }
-    if (timed_out) {
-        if (tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
-        return;  // the one copy that may still be in flight targets this CTA's own shared memory
-    }
+    if (timed_out) break;
     flush();
+    cur_item = -1;
+    if (!p.counter) break;
+    }
+    if (timed_out && tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
+    // (after a time-out the one copy that may still be in flight targets this CTA's own shared memory)
 }
 
 template <int KS, int NP>
@@ -291,7 +305,7 @@ static void we_fwd_launch_np(const WeFwdParams &p, bool rr, unsigned grid, cudaS
 
 template <int KS>
 static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint, int waves, bool reproducible, int npoly,
-                            cudaStream_t stream) {
+                            unsigned *counter, cudaStream_t stream) {
     const int rows = p.row_end - p.row_begin;
     p.obs_blocks = (rows + 31) / 32;
     p.k_groups = (p.K + WE_WARPS * KS - 1) / (WE_WARPS * KS);
@@ -303,6 +317,9 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
         tj = tj_hint;
     } else {
         while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
+        // with padding, the tile that straddles the end of a sample is looped over in full: keep tiles short
+        // (measured on 64 chains of 64..1024 padded to 1024: 4.68 ms at 512, 3.97 ms at 64)
+        if (p.valid && tj > 64) tj = 64;
     }
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
@@ -317,7 +334,14 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
             while (waves > 1 && p.units / (resident * waves) < p.tiles) --waves;
     }
     const long long slots = resident * waves;
-    const unsigned grid = (unsigned)(p.units < slots ? p.units : slots);
+    p.nruns = (int)(p.units < slots ? p.units : slots);
+    p.counter = reproducible ? nullptr : counter;
+    unsigned grid = (unsigned)p.nruns;
+    if (p.counter) {  // persistent CTAs drawing runs from the counter
+        if (grid > (unsigned)resident) grid = (unsigned)resident;
+        cudaError_t ce = cudaMemsetAsync(p.counter, 0, sizeof(unsigned), stream);
+        if (ce != cudaSuccess) return (int)ce;
+    }
     // pairs evaluated on the FMA pipe (KS = 16 has 8 pairs per lane)
     if (KS == 16) {
         switch (npoly) {
@@ -335,14 +359,14 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
 // ks_hint: 0 = choose; otherwise 2, 8 or 16.  tj_hint: 0 = choose; otherwise a multiple of 4 in
 // [4, 512].  waves: 0 = choose; otherwise CTAs launched per resident CTA slot.  rr: explicit range reduction.  The three outputs must already be zero over the row range.
 static int we_fwd_launch(const WeFwdParams &p, int Z, int ks_hint, int tj_hint, int waves, bool reproducible, bool rr,
-                         int npoly, int sms, cudaStream_t stream) {
+                         int npoly, int sms, unsigned *counter, cudaStream_t stream) {
     int ks = ks_hint;
     if (ks == 0) ks = p.K >= 64 ? 16 : (p.K >= 32 ? 8 : 2);
     if (tj_hint < 0 || tj_hint > WE_TJ_MAX || (tj_hint & 3) || waves < 0 || waves > 64) return (int)PAI_ERR_UNSUPPORTED;
     switch (ks) {
-        case 16: return we_fwd_launch_ks<16>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, stream);
-        case 8: return we_fwd_launch_ks<8>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, stream);
-        case 2: return we_fwd_launch_ks<2>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, stream);
+        case 16: return we_fwd_launch_ks<16>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
+        case 8: return we_fwd_launch_ks<8>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
+        case 2: return we_fwd_launch_ks<2>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
         default: return (int)PAI_ERR_UNSUPPORTED;
     }
 }
