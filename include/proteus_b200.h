@@ -65,7 +65,12 @@ int pai_device_status(void *stream);
  *   row_begin,row_end          observer rows [row_begin,row_end) of every batch element are
  *                              computed and written; other rows are not touched (multi-GPU shard)
  *   magnitude_type             0: 1, 1: 1/r, 2: 1/log2(r), 3: 1/sqrt(r)
- *   dropout_p, seed            only dropout_p == 0 is supported (PAI_ERR_UNSUPPORTED otherwise)
+ *   dropout_p, seed            0 <= dropout_p < 1 (PAI_ERR_UNSUPPORTED otherwise).  With dropout_p > 0 single
+ *                              (observer, source, wavenumber) evaluations are dropped as the reference kernel
+ *                              does (wf_embedding_kernel.cu:27-46,227-232): a hash of (z, i, j, k, seed) mapped to
+ *                              [0,1] keeps the evaluation when >= dropout_p; kept terms, in `out` and in both
+ *                              stored sums, are scaled by 1/(1-dropout_p).  The same seed gives the same pattern
+ *                              for any row range, shard or launch configuration.
  * Pairs with j == i, coincident points (r == 0) and padded tokens contribute nothing.
  * Requires 1 <= N, 1 <= K, 1 <= Z <= 65535.
  */

@@ -10,8 +10,12 @@ chunked form does (sources stay on axis 1, observers move to axis 2).
 Pinned against the reference function itself: ``tests/golden/make_golden.py`` extracts
 ``wf_embedding_torch`` from the reference tree, runs it on seeded inputs and stores the
 outputs; ``tests/test_oracle_we.py`` checks this restatement reproduces them bit for bit.
-Dropout is not modelled (the reference function ignores ``dropout_p`` as well).
+The reference function ignores ``dropout_p``; the reference *kernel* does not.  Its index-hash dropout
+(``isotropic/cuda/wf_embedding_kernel.cu:27-46,227-232``) is restated in ``dropout_keep`` and applied when
+``dropout_p > 0``.  That part is parity unpinned: the reference holds no test or vector for it, and its kernel
+cannot run where this oracle is built.
 """
+import numpy as np
 import torch
 
 
@@ -31,8 +35,33 @@ def _magnitudes(dists, pair_mask, mag_type):
     raise ValueError(f"magnitude_type must be 0..3, not {mag_type}")
 
 
+def dropout_hash(z, i, j, k, seed):
+    """``hash5`` of the reference kernel (``wf_embedding_kernel.cu:27-40``) for index arrays ``z, i, j, k``
+    (broadcastable): the seed xor-ed with one multiply-add term per index, then a multiply/xor-shift finaliser,
+    all in wrapping 32-bit arithmetic."""
+    u = lambda a: np.asarray(a).astype(np.uint32)
+    c = np.uint32
+    with np.errstate(over="ignore"):
+        h = c(seed) ^ (u(z) * c(0x85ebca6b) + c(0x9e3779b9))
+        h = h ^ (u(i) * c(0xc2b2ae35) + c(0x165667b1))
+        h = h ^ (u(j) * c(0x27d4eb2f) + c(0xd6e8feb8))
+        h = h ^ (u(k) * c(0x85ebca6b) + c(0x1b873593))
+        h = (h ^ (h >> c(16))) * c(0x85ebca6b)
+        h = h ^ (h >> c(13))
+        h = (h ^ (h >> c(16))) * c(0xc2b2ae35)
+        h = h ^ (h >> c(16))
+    return h
+
+
+def dropout_keep(z, i, j, k, seed, dropout_p):
+    """Keep mask of the reference kernel's dropout (``wf_embedding_kernel.cu:42-46``): the hash is mapped to [0, 1]
+    with a float division by ``float(UINT32_MAX)`` (which is 2^32 in fp32) and values >= p are kept."""
+    normalized = dropout_hash(z, i, j, k, seed).astype(np.float32) / np.float32(4294967295.0)
+    return normalized >= np.float32(dropout_p)
+
+
 def wf_embedding_ref(coords, wavenumbers, mag_type=1, mask=None, rows=None, chunk=128,
-                     dtype=None, return_sums=False):
+                     dtype=None, return_sums=False, dropout_p=0.0, seed=0):
     """Features ``[Z, R, 2K]`` for observer rows ``rows = (begin, end)`` (default: all).
 
     coords ``[Z, N, 3]``, wavenumbers ``[K]``, mask ``[Z, N]`` bool with True = padded.
@@ -41,6 +70,8 @@ def wf_embedding_ref(coords, wavenumbers, mag_type=1, mask=None, rows=None, chun
     per-row sums the reference kernel stores for its backward,
     ``sum_j mag*r*cos(k r)`` and ``sum_j mag*r*sin(k r)``
     (``isotropic/cuda/wf_embedding_kernel.cu:237-238``), each ``[Z, R, K]``.
+    With ``dropout_p > 0`` single evaluations are dropped and the kept ones scaled by ``1/(1-p)``, in the
+    features and in the stored sums, as the reference kernel does (``:227-238``).
     """
     dtype = dtype or coords.dtype
     coords = coords.to(dtype)
@@ -60,6 +91,11 @@ def wf_embedding_ref(coords, wavenumbers, mag_type=1, mask=None, rows=None, chun
         pair_mask = mask[:, :, None] | mask[:, None, i0:i1] | (dists == 0)  # :106
         mags = _magnitudes(dists, pair_mask, mag_type)[:, :, :, None]
         cosp, sinp = torch.cos(phases), torch.sin(phases)
+        if dropout_p != 0.0:
+            keep = dropout_keep(np.arange(z)[:, None, None, None], np.arange(i0, i1)[None, None, :, None],
+                                np.arange(n)[None, :, None, None], np.arange(k)[None, None, None, :], seed, dropout_p)
+            keep = torch.from_numpy(keep).to(dtype) / (1 - dropout_p)
+            cosp, sinp = cosp * keep, sinp * keep
         real = mags * cosp  # :119
         imag = mags * sinp  # :120
         feats = torch.stack([real.sum(dim=1), imag.sum(dim=1)], dim=-1)  # :123-127
@@ -83,14 +119,15 @@ def dk_analytic(d_out, cos_sums, sin_sums):
     return ((d_out[:, :, 1::2] * cos_sums) - (d_out[:, :, 0::2] * sin_sums)).sum(dim=(0, 1))
 
 
-def dk_autograd(coords, wavenumbers, d_out, mag_type=1, mask=None, dtype=torch.float64, chunk=64):
+def dk_autograd(coords, wavenumbers, d_out, mag_type=1, mask=None, dtype=torch.float64, chunk=64, dropout_p=0.0, seed=0):
     """Wavenumber gradient by autograd through the dense formulation (the reference test's
     own check, ``tests/wf_embed/wf_embed.py:60-74``), accumulated over observer chunks."""
     wn = wavenumbers.detach().to(dtype).clone().requires_grad_(True)
     n = coords.shape[1]
     for i0 in range(0, n, chunk):
         i1 = min(i0 + chunk, n)
-        out = wf_embedding_ref(coords, wn, mag_type, mask, rows=(i0, i1), chunk=chunk, dtype=dtype)
+        out = wf_embedding_ref(coords, wn, mag_type, mask, rows=(i0, i1), chunk=chunk, dtype=dtype,
+                               dropout_p=dropout_p, seed=seed)
         (out * d_out[:, i0:i1].to(dtype)).sum().backward()
     return wn.grad
 

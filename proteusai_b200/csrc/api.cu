@@ -147,12 +147,11 @@ int pai_device_status(void *stream) {
 int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *wavenumbers, float *out, float *cos_sums,
                float *sin_sums, int Z, int N, int K, int row_begin, int row_end, int magnitude_type, float dropout_p,
                uint32_t seed, void *stream) {
-    (void)seed;
     if (!coords_soa || !wavenumbers || !out || !cos_sums || !sin_sums) return PAI_ERR_NULL_POINTER;
     if (Z < 1 || Z > 65535 || N < 1 || K < 1 || (long long)N * K > (1ll << 40)) return PAI_ERR_BAD_SHAPE;
     if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
     if (magnitude_type < 0 || magnitude_type > 3) return PAI_ERR_UNSUPPORTED;
-    if (dropout_p != 0.0f) return PAI_ERR_UNSUPPORTED;
+    if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) return PAI_ERR_UNSUPPORTED;
     if (!aligned(coords_soa, 4) || !aligned(wavenumbers, 4)) return PAI_ERR_MISALIGNED;
     if ((K & 1) == 0 ? (!aligned(out, 16) || !aligned(cos_sums, 8) || !aligned(sin_sums, 8))
                      : (!aligned(out, 4) || !aligned(cos_sums, 4) || !aligned(sin_sums, 4)))
@@ -171,6 +170,23 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.mag_type = magnitude_type;
+    p.seed = seed;
+    p.drop_thr = 0u;
+    p.drop_scale = 0.f;
+    if (dropout_p != 0.0f) {
+        // The reference keeps an evaluation when (float)h / (float)UINT32_MAX >= p, where (float)UINT32_MAX is 2^32
+        // and the conversion of h rounds to nearest.  That conversion is monotonic in h, so the test equals
+        // h >= (the smallest h that passes), found here by bisection with the same float arithmetic.
+        const float t = dropout_p * 4294967296.0f;  // exact (a power-of-two scaling)
+        uint32_t lo = 0u, hi = 0xffffffffu;          // invariant: hi passes (p < 1), everything below lo fails
+        while (lo < hi) {
+            const uint32_t mid = lo + (hi - lo) / 2u;
+            if ((float)mid >= t) hi = mid;
+            else lo = mid + 1u;
+        }
+        p.drop_thr = lo;
+        p.drop_scale = 1.0f / (1.0f - dropout_p);
+    }
     // bulk copies need 16-byte aligned plane segments: base aligned and N a multiple of 4
     p.use_tma = (aligned(coords_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
     // the kernel adds partial sums into the outputs: zero the rows of the shard first
@@ -388,7 +404,10 @@ int pai_we_aniso_fwd(const float *coords_a_soa, const float *coords_b_soa, const
     p.row_begin = row_begin;
     p.row_end = row_end;
     p.use_tma = (aligned(coords_a_soa, 16) && aligned(coords_b_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
-    return pai::we_aniso_fwd_launch(p, Z, sms, st);
+    unsigned *counter = nullptr;
+    if (valid)
+        if (int e = next_we_counter(&counter)) return e;
+    return pai::we_aniso_fwd_launch(p, Z, sms, counter, st);
 }
 
 size_t pai_we_aniso_bwd_workspace_bytes(int Z, int N, int K) {

@@ -30,6 +30,8 @@ struct WeAnisoParams {
     int N, K, row_begin, row_end, use_tma;
     int tj, tiles, obs_blocks, k_groups;
     long long units;
+    int nruns;          // the unit sequence is cut into this many equal runs
+    unsigned *counter;  // zeroed before the launch: CTAs draw run indices from it (nullptr: run = blockIdx.x)
 };
 
 struct __align__(16) WeAnisoSmem {
@@ -37,6 +39,8 @@ struct __align__(16) WeAnisoSmem {
     float4 ta[WE_TJ_MAX];          // {x, y, z, valid}
     float4 tb[WE_TJ_MAX];          // {bx, by, bz, 0}
     uint64_t bar[2];
+    int hi[2][WE_WARPS];
+    unsigned run;
 };
 
 __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kernel(const WeAnisoParams p) {
@@ -45,9 +49,6 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = p.N, K = p.K;
     const bool tma = p.use_tma != 0;
-    const long long u0 = p.units * blockIdx.x / gridDim.x;
-    const long long u1 = p.units * (blockIdx.x + 1) / gridDim.x;
-    if (u0 >= u1) return;
 
     auto issue_tile = [&](long long u, int st) {  // thread 0: bulk-copy the six planes of unit u's tile
         const long long item = u / p.tiles;
@@ -72,7 +73,6 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
             fence_proxy_async();
         }
         __syncthreads();
-        if (tid == 0) issue_tile(u0, 0);
     }
 
     long long cur_item = -1;
@@ -111,10 +111,24 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
         }
     };
 
+    // Runs are assigned by block index or, with a padding mask (very unequal runs), drawn from a global counter by
+    // persistent CTAs.  n counts the units this CTA has staged: it selects the buffer and the mbarrier phase.
     bool timed_out = false;
-    for (long long u = u0; u < u1; ++u) {
-        const int n = (int)(u - u0), st = n & 1;
-        if (tma && tid == 0 && u + 1 < u1) issue_tile(u + 1, st ^ 1);
+    int n = 0;
+    for (;;) {
+    unsigned run = blockIdx.x;
+    if (p.counter) {
+        if (tid == 0) sm.run = atomicAdd(p.counter, 1u);
+        __syncthreads();  // (the next write of sm.run comes after the barriers inside the run)
+        run = sm.run;
+    }
+    if (run >= (unsigned)p.nruns) break;
+    const long long u0 = p.units * run / p.nruns;
+    const long long u1 = p.units * (run + 1) / p.nruns;
+    if (tma && tid == 0 && u0 < u1) issue_tile(u0, n & 1);  // that buffer was drained two units ago
+    for (long long u = u0; u < u1; ++u, ++n) {
+        const int st = n & 1;
+        if (tma && tid == 0 && u + 1 < u1) issue_tile(u + 1, st ^ 1);  // stage st^1 was drained by the previous repack
         const long long item = u / p.tiles;
         const int tile = (int)(u - item * p.tiles);
         if (item != cur_item) {
@@ -177,15 +191,19 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
                 b = a;
             }
             a.w = v ? 1.f : 0.f;
-            mine |= v ? 1 : 0;
+            if (v) mine = j + 1;
             sm.ta[j] = a;
             sm.tb[j] = b;
         }
-        const bool any = __syncthreads_or(mine) != 0;
-        if (!any || !item_live) continue;
+        mine = __reduce_max_sync(0xffffffffu, mine);
+        if (lane == 0) sm.hi[st][warp] = mine;
+        __syncthreads();  // also publishes the tile
+        // sources past the last valid one of the tile (the padded tail of a sample) are not looped over
+        const int hi = max(max(sm.hi[st][0], sm.hi[st][1]), max(sm.hi[st][2], sm.hi[st][3]));
+        if (hi == 0 || !item_live) continue;
 
 #pragma unroll 2
-        for (int j = 0; j < cnt; ++j) {
+        for (int j = 0; j < hi; ++j) {
             const float4 s = sm.ta[j], bj = sm.tb[j];
             const float dx = ox - s.x, dy = oy - s.y, dz = oz - s.z;  // R = A_i - A_j
             const float d2 = (dx * dx + dy * dy + dz * dz) * s.w;
@@ -215,14 +233,15 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
             }
         }
     }
-    if (timed_out) {
-        if (tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
-        return;
-    }
+    if (timed_out) break;
     flush();
+    cur_item = -1;
+    if (!p.counter) break;
+    }
+    if (timed_out && tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
 }
 
-static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, cudaStream_t stream) {
+static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, unsigned *counter, cudaStream_t stream) {
     const int rows = p.row_end - p.row_begin;
     p.obs_blocks = (rows + 31) / 32;
     p.k_groups = (p.K + WE_WARPS * WEA_KS - 1) / (WE_WARPS * WEA_KS);
@@ -230,12 +249,19 @@ static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, cudaStream_t str
     const long long resident = (long long)sms * WE_CTAS_PER_SM;
     int tj = WE_TJ_MAX;
     while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
-    if (p.valid && tj > 64) tj = 64;  // with padding, short tiles waste less on the tile that straddles a sample's end
+    if (p.valid && tj > 256) tj = 256;  // with padding: fewer bulk copies of all-padding tiles
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
     p.units = items * p.tiles;
-    const long long slots = resident * WE_MAX_WAVES;
-    const unsigned grid = (unsigned)(p.units < slots ? p.units : slots);
+    const long long slots = resident * (p.valid ? 2 * WE_MAX_WAVES : WE_MAX_WAVES);  // unequal runs: more, shorter ones
+    p.nruns = (int)(p.units < slots ? p.units : slots);
+    p.counter = p.valid ? counter : nullptr;
+    unsigned grid = (unsigned)p.nruns;
+    if (p.counter) {
+        if (grid > (unsigned)resident) grid = (unsigned)resident;
+        cudaError_t ce = cudaMemsetAsync(p.counter, 0, sizeof(unsigned), stream);
+        if (ce != cudaSuccess) return (int)ce;
+    }
     we_aniso_fwd_kernel<<<grid, WE_THREADS, 0, stream>>>(p);
     return (int)cudaPeekAtLastError();
 }

@@ -51,6 +51,9 @@ struct WeFwdParams {
     int k_groups;          // groups of WE_WARPS * KS wavenumbers
     long long units;       // Z * obs_blocks * k_groups * tiles
     int nruns;             // the unit sequence is cut into this many equal runs
+    uint32_t seed;         // dropout: hash seed,
+    uint32_t drop_thr;     //   an evaluation is kept when its hash is >= this,
+    float drop_scale;      //   and kept evaluations are scaled by this (1 / (1 - p)); 0 = no dropout
     unsigned *counter;     // zeroed before the launch: CTAs draw run indices from it (nullptr: run = blockIdx.x)
 };
 
@@ -58,8 +61,19 @@ struct __align__(16) WeSmem {
     float stage[2][3][WE_TJ_MAX];  // x/y/z planes, two stages
     float4 tile[WE_TJ_MAX];        // repacked {x,y,z,valid}
     uint64_t bar[2];
+    int hi[2][WE_WARPS];
     unsigned run;
 };
+
+// Final mixing of the reference's dropout hash (hash5, wf_embedding_kernel.cu:27-40); the caller has already
+// xor-ed the seed with the four index terms.
+__device__ __forceinline__ uint32_t we_hash_mix(uint32_t h) {
+    h = (h ^ (h >> 16)) * 0x85ebca6bu;
+    h ^= h >> 13;
+    h = (h ^ (h >> 16)) * 0xc2b2ae35u;
+    h ^= h >> 16;
+    return h;
+}
 
 // KS: wavenumbers per lane (even).  MAG1: compile-time fast path for magnitude_type == 1.
 // RR: reduce the phase to [-pi, pi] explicitly (phase in revolutions, subtract the nearest
@@ -70,7 +84,12 @@ struct __align__(16) WeSmem {
 //     Measured at N = 16384: NP = 1 (one eighth of the evaluations) is 5.6 % faster than NP = 0, NP = 2
 //     3 %, NP = 3 slower: the long dependent Horner chains share the in-order issue of each warp with the
 //     SFU instructions, so the pipes overlap far less than their idle capacities suggest.
-template <int KS, bool MAG1, bool RR, int NP>
+//
+// DROP: dropout of single evaluations, as the reference kernel does it (wf_embedding_kernel.cu:27-46,227-232): a
+//     hash of (batch element, observer, source, wavenumber index, seed) is mapped to [0, 1] and the evaluation is
+//     kept when that is >= p; kept real and imaginary parts (and with them the stored sums) are scaled by 1/(1-p).
+//     The comparison (float)h / 2^32 >= p is done on the integer: the host passes the smallest h that passes.
+template <int KS, bool MAG1, bool RR, int NP, bool DROP = false>
 __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(const WeFwdParams p) {
     __shared__ WeSmem sm;
     constexpr int KP = KS / 2;
@@ -105,6 +124,7 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
     int z = 0, row = 0, k0 = 0;
     bool row_in = false, ov = false, item_live = false;
     float ox = 0.f, oy = 0.f, oz = 0.f;
+    uint32_t h_zi = 0u, h_k0 = 0u;  // dropout hash: the (seed, batch element, observer) part and the wavenumber term of k0
     f2_t kk[KP];
     f2_t acc_re[KP], acc_im[KP], acc_c[KP], acc_s[KP];
 #pragma unroll
@@ -180,6 +200,10 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
                 }
             }
             item_live = __any_sync(0xffffffffu, ov) && k0 < K;  // the same 32 observers in every warp of the CTA
+            if (DROP) {
+                h_zi = p.seed ^ ((uint32_t)z * 0x85ebca6bu + 0x9e3779b9u) ^ ((uint32_t)row * 0xc2b2ae35u + 0x165667b1u);
+                h_k0 = (uint32_t)k0 * 0x85ebca6bu + 0x1b873593u;
+            }
 #pragma unroll
             for (int q = 0; q < KP; ++q) {
                 float a = (k0 + 2 * q < K) ? p.wn[k0 + 2 * q] : 0.f;
@@ -206,7 +230,7 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
         } else {
             __syncthreads();  // everyone is done reading sm.tile
         }
-        // repack to {x,y,z,valid}; count valid sources of this tile
+        // repack to {x,y,z,valid}; find the end of the valid sources of this tile
         int mine = 0;
         for (int j = tid; j < cnt; j += WE_THREADS) {
             float4 s;
@@ -222,14 +246,18 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
             const bool v = vz ? (vz[j0 + j] != 0) : true;
             if (!v) s.x = s.y = s.z = 0.f;  // whatever the padding holds (even NaN) never enters the arithmetic
             s.w = v ? 1.f : 0.f;
-            mine |= v ? 1 : 0;
+            if (v) mine = j + 1;
             sm.tile[j] = s;
         }
-        const bool any = __syncthreads_or(mine) != 0;  // also publishes sm.tile
-        if (!any || !item_live) continue;
+        mine = __reduce_max_sync(0xffffffffu, mine);
+        if (lane == 0) sm.hi[st][warp] = mine;
+        __syncthreads();  // also publishes sm.tile (sm.hi[st] is next written two units later, after two more barriers)
+        // sources past the last valid one of the tile (the padded tail of a sample) are not looped over
+        const int hi = max(max(sm.hi[st][0], sm.hi[st][1]), max(sm.hi[st][2], sm.hi[st][3]));
+        if (hi == 0 || !item_live) continue;
 
 #pragma unroll 2
-        for (int j = 0; j < cnt; ++j) {
+        for (int j = 0; j < hi; ++j) {
             const float4 s = sm.tile[j];
             const float dx = ox - s.x, dy = oy - s.y, dz = oz - s.z;
             const float d2 = (dx * dx + dy * dy + dz * dz) * s.w;  // 0 for padded sources
@@ -251,6 +279,8 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
                 magr = mag * r;
             }
             const f2_t r2 = f2_pack(r, r), mag2 = f2_pack(mag, mag), magr2 = f2_pack(magr, magr);
+            uint32_t h_j = 0u;
+            if (DROP) h_j = h_zi ^ ((uint32_t)(j0 + j) * 0x27d4eb2fu + 0xd6e8feb8u);
 #pragma unroll
             for (int q = 0; q < KP; ++q) {
                 if (q < NP) {  // FMA-pipe evaluation
@@ -274,7 +304,14 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
                 }
                 sfu_sincos(pa, sa, ca);
                 sfu_sincos(pb, sb, cb);
-                const f2_t c2 = f2_pack(ca, cb), s2 = f2_pack(sa, sb);
+                f2_t c2 = f2_pack(ca, cb), s2 = f2_pack(sa, sb);
+                if (DROP) {
+                    const uint32_t ha = we_hash_mix(h_j ^ (h_k0 + (uint32_t)(2 * q) * 0x85ebca6bu));
+                    const uint32_t hb = we_hash_mix(h_j ^ (h_k0 + (uint32_t)(2 * q + 1) * 0x85ebca6bu));
+                    const f2_t keep2 = f2_pack(ha >= p.drop_thr ? p.drop_scale : 0.f, hb >= p.drop_thr ? p.drop_scale : 0.f);
+                    c2 = f2_mul(c2, keep2);
+                    s2 = f2_mul(s2, keep2);
+                }
                 acc_re[q] = f2_fma(c2, mag2, acc_re[q]);
                 acc_im[q] = f2_fma(s2, mag2, acc_im[q]);
                 acc_c[q] = f2_fma(c2, magr2, acc_c[q]);
@@ -294,6 +331,11 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
 template <int KS, int NP>
 static void we_fwd_launch_np(const WeFwdParams &p, bool rr, unsigned grid, cudaStream_t stream) {
     dim3 block(WE_THREADS);
+    if (p.drop_scale != 0.f) {  // dropout: all evaluations on the SFU, no explicit range reduction
+        if (p.mag_type == 1) we_fwd_kernel<KS, true, false, 0, true><<<grid, block, 0, stream>>>(p);
+        else we_fwd_kernel<KS, false, false, 0, true><<<grid, block, 0, stream>>>(p);
+        return;
+    }
     if (p.mag_type == 1) {
         if (rr) we_fwd_kernel<KS, true, true, NP><<<grid, block, 0, stream>>>(p);
         else we_fwd_kernel<KS, true, false, NP><<<grid, block, 0, stream>>>(p);
@@ -317,9 +359,9 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
         tj = tj_hint;
     } else {
         while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
-        // with padding, the tile that straddles the end of a sample is looped over in full: keep tiles short
-        // (measured on 64 chains of 64..1024 padded to 1024: 4.68 ms at 512, 3.97 ms at 64)
-        if (p.valid && tj > 64) tj = 64;
+        // with padding, shorter tiles mean fewer bulk copies of all-padding tiles (the loop over a tile already
+        // stops at its last valid source)
+        if (p.valid && tj > 256) tj = 256;
     }
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
@@ -329,7 +371,9 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
     // With `reproducible` the wave count is limited so that a run stays at least one item long: then at
     // most two runs add into any output element and the result is identical from run to run.
     if (waves <= 0) {
-        waves = WE_MAX_WAVES;
+        // (with a padding mask the runs are very unequal: twice as many, shorter ones shorten the tail; measured on
+        // 64 chains of 64..1024 padded to 1024: 3.72 ms at 8 runs per slot, 3.52 ms at 16)
+        waves = (p.valid && !reproducible) ? 2 * WE_MAX_WAVES : WE_MAX_WAVES;
         if (reproducible)
             while (waves > 1 && p.units / (resident * waves) < p.tiles) --waves;
     }

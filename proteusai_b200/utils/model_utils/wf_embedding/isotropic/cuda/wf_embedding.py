@@ -7,7 +7,9 @@ Same names, argument order and return values as
 Differences, all supersets: ``mask=None`` means "no padding" (the reference crashes on it);
 padding travels as an explicit validity array instead of the x == 12345 sentinel; the backward
 reduction is one fused kernel instead of three elementwise PyTorch kernels and a sum.
+Dropout (``dropout_p > 0``) follows the reference kernel's index hash.
 """
+import numpy as np
 import torch
 
 from proteusai_b200 import _lib
@@ -18,12 +20,14 @@ def wf_embedding(coords, wavenumbers, magnitude_type=1, dropout_p=0.0, mask=None
 
 
 def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=0, row_end=None,
-                    out=None, cos_sums=None, sin_sums=None):
+                    out=None, cos_sums=None, sin_sums=None, dropout_p=0.0, seed=0):
     """Run the forward kernel on observer rows ``[row_begin, row_end)`` of every batch element.
 
     Returns ``(out [Z,N,2K], cos_sums [Z,N,K], sin_sums [Z,N,K])``; only the rows of the range are
     written (the other rows of freshly allocated buffers are left uninitialised).  This is the
     multi-GPU building block: every rank holds all coordinates and computes its own rows.
+    With ``dropout_p > 0`` evaluations are dropped by the reference kernel's index hash under ``seed``
+    (the pattern does not depend on the row range, so all ranks of a sharded call pass the same seed).
     """
     assert magnitude_type in [0, 1, 2, 3]  # mag=1, 1/|R|, 1/log2(|R|), 1/sqrt(|R|)
     if not coords.is_cuda:
@@ -46,7 +50,8 @@ def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().pai_we_fwd(
             _lib.ptr(planes), _lib.ptr(valid), _lib.ptr(wn), _lib.ptr(out), _lib.ptr(cos_sums), _lib.ptr(sin_sums),
-            batch, n, k, row_begin, row_end, magnitude_type, 0.0, 0, _lib.current_stream()), "pai_we_fwd")
+            batch, n, k, row_begin, row_end, magnitude_type, float(dropout_p), int(seed) & 0xFFFFFFFF,
+            _lib.current_stream()), "pai_we_fwd")
     return out, cos_sums, sin_sums
 
 
@@ -71,9 +76,9 @@ class _wf_embedding(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, coords, wavenumbers, magnitude_type, dropout_p, mask):
-        if dropout_p != 0.0:
-            raise RuntimeError("wf_embedding: dropout_p != 0 is not supported by the B200 kernel")
-        out, cos_sums, sin_sums = we_forward_rows(coords, wavenumbers, magnitude_type, mask)
+        # a fresh 32-bit seed per call, drawn as the reference draws it (wf_embedding.py:48-49)
+        seed = int(np.random.default_rng().integers(0, 2**32, dtype=np.uint32)) if dropout_p != 0.0 else 0
+        out, cos_sums, sin_sums = we_forward_rows(coords, wavenumbers, magnitude_type, mask, dropout_p=dropout_p, seed=seed)
         ctx.save_for_backward(cos_sums, sin_sums)
         ctx.wn_dtype = wavenumbers.dtype
         return out

@@ -54,7 +54,9 @@ def test_we_fwd_argument_errors(lib):
     assert f(p, null, p, p, p, p, 1, 8, 4, 5, 4, 1, 0.0, 0, None) == -6
     assert f(p, null, p, p, p, p, 1, 8, 4, 0, 9, 1, 0.0, 0, None) == -6
     assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 7, 0.0, 0, None) == -4
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.1, 0, None) == -4
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 1.0, 0, None) == -4   # dropout_p must be in [0, 1)
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, -0.1, 0, None) == -4
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, float("nan"), 0, None) == -4
     assert f(p, null, p, ctypes.c_void_p(0x1004), p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, None) == -3
 
 

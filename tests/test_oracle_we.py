@@ -88,3 +88,38 @@ def test_chain_geometry():
     assert d2.min() > 5.3 and d2.max() < 6.6
     wn = chains.wavenumbers(512)
     assert wn.shape == (256,) and abs(wn[0] - 2 * np.pi / 3.7) < 1e-6 and wn[-1] > 2 * np.pi / 20.0
+
+
+def test_dropout_hash_restatement():
+    """The keep count and an order-dependent checksum of the hashes were produced by compiling the same 32-bit
+    arithmetic as a C program (gcc) over the same index grid: z < 2, i < 50, j < 60, k < 16, seed 1234, p = 0.3."""
+    from oracle.we_ref import dropout_hash, dropout_keep
+    idx = (np.arange(2)[:, None, None, None], np.arange(50)[None, :, None, None],
+           np.arange(60)[None, None, :, None], np.arange(16)[None, None, None, :])
+    h = dropout_hash(*idx, 1234)
+    assert h.dtype == np.uint32 and h.shape == (2, 50, 60, 16)
+    x = 0
+    for v in h.ravel().tolist():
+        x = (x * 31 + v) & 0xFFFFFFFF
+    assert x == 4207743621
+    keep = dropout_keep(*idx, 1234, 0.3)
+    assert int(keep.sum()) == 67135
+    assert abs(keep.mean() - 0.7) < 5e-3
+    assert dropout_keep(*idx, 1234, 0.0).all()
+
+
+def test_dropout_forward_and_gradient_are_consistent():
+    c, m = chains.chain_batch([48, 31], 48, seed=8)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    wn = torch.from_numpy(chains.wavenumbers(16))
+    base = wf_embedding_ref(c, wn, 1, m)
+    o, cs, sn = wf_embedding_ref(c, wn, 1, m, return_sums=True, dropout_p=0.2, seed=99)
+    assert rel_l2(base, o) > 1e-2                       # something was dropped
+    assert torch.all(o[1, 31:] == 0)                    # padded rows stay zero
+    assert torch.equal(o, wf_embedding_ref(c, wn, 1, m, dropout_p=0.2, seed=99, chunk=16))  # index hash: chunking-free
+    assert not torch.equal(o, wf_embedding_ref(c, wn, 1, m, dropout_p=0.2, seed=100))
+    # averaged over seeds the scaled output is unbiased
+    mean = sum(wf_embedding_ref(c, wn, 1, m, dropout_p=0.2, seed=s).double() for s in range(200)) / 200
+    assert rel_l2(base, mean) < 5e-2
+    d_out = torch.randn(o.shape, generator=torch.Generator().manual_seed(1))
+    assert rel_l2(dk_autograd(c, wn, d_out, 1, m, dropout_p=0.2, seed=99), dk_analytic(d_out, cs, sn)) < 1e-5

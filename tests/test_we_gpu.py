@@ -200,3 +200,38 @@ def test_module_matches_reference_schedule(we):
     assert rel_l2(ref, out.detach().cpu()) < OUT_TOL
     out.square().sum().backward()
     assert mod.wavenumbers.grad is not None and torch.isfinite(mod.wavenumbers.grad).all()
+
+
+@pytest.mark.parametrize("mag", [1, 3])
+def test_dropout_matches_the_index_hash(we, mag):
+    """Dropout follows the reference kernel's hash of (z, i, j, k, seed): the same evaluations are dropped as in the
+    oracle's restatement, for the features, the stored sums and therefore the analytic gradient; the pattern does
+    not depend on the row range or on the launch configuration."""
+    lengths = [200, 137, 64]
+    c, m = chains.chain_batch(lengths, 200, seed=21)
+    c_t, m_t, wn_t = torch.from_numpy(c), torch.from_numpy(m), torch.from_numpy(chains.wavenumbers(64))
+    p, seed = 0.15, 0xC0FFEE11
+    ref, cs_ref, sn_ref = wf_embedding_ref(c_t, wn_t, mag, m_t, dtype=torch.float64, return_sums=True, dropout_p=p, seed=seed)
+    out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), mag, m_t.cuda(), dropout_p=p, seed=seed)
+    assert rel_l2(ref, out.cpu()) < OUT_TOL
+    assert rel_l2(cs_ref, cs.cpu()) < OUT_TOL and rel_l2(sn_ref, sn.cpu()) < OUT_TOL
+    assert rel_l2(wf_embedding_ref(c_t, wn_t, mag, m_t, dtype=torch.float64), out.cpu()) > 1e-2
+    part, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), mag, m_t.cuda(), 40, 120, dropout_p=p, seed=seed)
+    assert rel_l2(ref[:, 40:120], part[:, 40:120].cpu()) < OUT_TOL
+    d_out = torch.randn(out.shape, generator=torch.Generator().manual_seed(3))
+    dk = we.we_backward_dk(d_out.cuda(), cs, sn)
+    assert rel_l2(dk_analytic(d_out.double(), cs_ref, sn_ref), dk.cpu()) < DK_TOL
+    other, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), mag, m_t.cuda(), dropout_p=p, seed=seed + 1)
+    assert rel_l2(ref, other.cpu()) > 1e-2
+
+
+def test_dropout_through_the_autograd_function(we):
+    c, m = chains.chain_batch([96], 96, seed=22)
+    wn = torch.from_numpy(chains.wavenumbers(32)).cuda().requires_grad_(True)
+    a = we.wf_embedding(torch.from_numpy(c).cuda(), wn, 1, 0.3, torch.from_numpy(m).cuda())
+    b = we.wf_embedding(torch.from_numpy(c).cuda(), wn, 1, 0.3, torch.from_numpy(m).cuda())
+    assert not torch.equal(a, b)  # a fresh seed per call
+    a.sum().backward()
+    assert torch.isfinite(wn.grad).all()
+    with pytest.raises(RuntimeError):
+        we.we_forward_rows(torch.from_numpy(c).cuda(), wn.detach(), 1, None, dropout_p=1.0)
