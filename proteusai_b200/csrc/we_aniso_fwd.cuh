@@ -249,7 +249,6 @@ static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, unsigned *counte
     const long long resident = (long long)sms * WE_CTAS_PER_SM;
     int tj = WE_TJ_MAX;
     while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
-    if (p.valid && tj > 256) tj = 256;  // with padding: fewer bulk copies of all-padding tiles
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
     p.units = items * p.tiles;

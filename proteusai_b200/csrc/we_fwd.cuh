@@ -359,9 +359,6 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
         tj = tj_hint;
     } else {
         while (tj > 64 && items * ((p.N + tj - 1) / tj) < 8 * resident) tj /= 2;
-        // with padding, shorter tiles mean fewer bulk copies of all-padding tiles (the loop over a tile already
-        // stops at its last valid source)
-        if (p.valid && tj > 256) tj = 256;
     }
     p.tj = tj;
     p.tiles = (p.N + tj - 1) / tj;
@@ -372,7 +369,7 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
     // most two runs add into any output element and the result is identical from run to run.
     if (waves <= 0) {
         // (with a padding mask the runs are very unequal: twice as many, shorter ones shorten the tail; measured on
-        // 64 chains of 64..1024 padded to 1024: 3.72 ms at 8 runs per slot, 3.52 ms at 16)
+        // 64 chains of 64..1024 padded to 1024: 3.71 ms at 8 runs per slot, 3.51 ms at 16, 3.50 ms at 32)
         waves = (p.valid && !reproducible) ? 2 * WE_MAX_WAVES : WE_MAX_WAVES;
         if (reproducible)
             while (waves > 1 && p.units / (resident * waves) < p.tiles) --waves;
