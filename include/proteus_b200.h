@@ -180,6 +180,26 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
                     int zh_begin, int zh_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Geometric attention, forward, on strided tensors.
+ * The reference kernel takes a stride for every axis of Q, K, V and O (`_attn_fwd` arguments stride_Q_Z ... stride_O_D,
+ *   old/old_scripts/attn/geometric_attn.py:58-62, passed from tensor.stride() at :588-591), so a caller can hand it
+ *   views such as the [Z,H,N,d] permutation of a fused projection output [Z,N,3,H,d] without a copy.  Same here:
+ *
+ *   q_strides, k_strides, v_strides, o_strides   int64[3] on the host: element strides of the z, h and n axes; the d
+ *                                                axis must be contiguous (stride 1).  Strides of axes longer than 1
+ *                                                must be multiples of 8 elements (rows move 16 bytes at a time) and
+ *                                                at least d.
+ *   Everything else as in pai_geoattn_fwd, which is this call with the strides of a contiguous [Z,H,N,d] tensor.
+ *   L is always contiguous [Z,H,N].
+ */
+int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides,
+                            const void *V, const int64_t *v_strides, const float *coords, const float *sigma,
+                            const float *betas, const uint8_t *valid, const int32_t *sample_order,
+                            void *O, const int64_t *o_strides, float *L,
+                            int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
+                            int zh_begin, int zh_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Geometric attention, backward.
  * Replaces _geometric_attn.backward (old/old_scripts/attn/geometric_attn.py:610-660): the PyTorch row-sum
  *   D = sum(O * dO) (:616) and the Triton launch `_attn_bwd[grid](...)` (:640-657; kernel :265-543), for the
@@ -202,6 +222,23 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
                     void *workspace, size_t workspace_bytes,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
                     int zh_begin, int zh_end, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Row operations of the encoder block on either side of the attention kernel (bf16 in and out, fp32 arithmetic).
+ * The reference runs them as PyTorch operators, so there is no reference FFI to replace:
+ *   pai_add_layernorm_bf16   out[r,:] = LayerNorm(x[r,:] + y[r,:]) * gamma + beta, the post-norm steps
+ *                            `norm(q + dropout(attn))` and `norm(q + dropout(ffn))` of Encoder.forward
+ *                            (old/old_scripts/encoder.py:30-39) with dropout inactive, as one pass over the rows.
+ *                            x, y, out [rows, D] bf16 (y may be NULL: plain LayerNorm; out may alias x or y);
+ *                            gamma, beta [D] bf16, or fp32 when params_fp32 != 0; D a multiple of 8, at most 4096;
+ *                            biased variance, eps inside the square root, as nn.LayerNorm.
+ *   pai_gelu_bf16            out[i] = x[i] * Phi(x[i]), the erf form of GELU used by the reference MLP
+ *                            (utils/model_utils/base_modules/base_modules.py:46-52, F.gelu); n a multiple of 8;
+ *                            out may alias x.  Phi is evaluated to ~1e-7 absolute, below bf16 resolution.
+ */
+int pai_add_layernorm_bf16(const void *x, const void *y, const void *gamma, const void *beta, int params_fp32,
+                           void *out, long long rows, int D, float eps, void *stream);
+int pai_gelu_bf16(const void *x, void *out, long long n, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and

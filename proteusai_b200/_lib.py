@@ -6,10 +6,12 @@ raises.  Pointers are raw device addresses (``tensor.data_ptr()``), the stream i
 """
 import ctypes
 import os
-from ctypes import c_char_p, c_double, c_float, c_int, c_size_t, c_uint32, c_void_p
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("PROTEUS_B200_LIB", os.path.join(_PKG, "libproteus_b200.so"))
+
+_I64P = ctypes.POINTER(c_int64)  # host array of three element strides (z, h, n)
 
 # name -> (restype, argtypes); mirrors include/proteus_b200.h
 SIGNATURES = {
@@ -27,9 +29,13 @@ SIGNATURES = {
     "pai_we_bwd_dk_static_max_k": (c_int, []),
     "pai_we_bwd_dk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+    "pai_geoattn_fwd_strided": (c_int, [c_void_p, _I64P, c_void_p, _I64P, c_void_p, _I64P] + [c_void_p] * 6 + [_I64P, c_void_p] +
+                                [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "pai_geoattn_bwd": (c_int, [c_void_p] * 16 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
                                 c_int, c_int, c_void_p]),
+    "pai_add_layernorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p]),
+    "pai_gelu_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_void_p]),
     "pai_measure_sfu_peak": (c_int, [ctypes.POINTER(c_double), ctypes.POINTER(c_double)]),
 }
 

@@ -3,6 +3,7 @@
 #include "common.cuh"
 
 #include "geoattn_bwd.cuh"
+#include "encoder_ops.cuh"
 #include "geoattn_fwd.cuh"
 #include "we_bwd.cuh"
 #include "we_fwd.cuh"
@@ -234,11 +235,13 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
                               (cudaStream_t)stream);
 }
 
-int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L, int Z, int H,
-                    int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
-                    void *stream) {
-    if (!Q || !K || !V || !coords || !sigma || !O || !L) return PAI_ERR_NULL_POINTER;
+int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides, const void *V,
+                            const int64_t *v_strides, const float *coords, const float *sigma, const float *betas,
+                            const uint8_t *valid, const int32_t *sample_order, void *O, const int64_t *o_strides, float *L, int Z,
+                            int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin,
+                            int zh_end, void *stream) {
+    if (!Q || !K || !V || !coords || !sigma || !O || !L || !q_strides || !k_strides || !v_strides || !o_strides)
+        return PAI_ERR_NULL_POINTER;
     if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
     if (logit_form == 1 && !betas) return PAI_ERR_NULL_POINTER;
     if (logit_form == 1 && !(max_rbf > min_rbf)) return PAI_ERR_BAD_SHAPE;
@@ -249,14 +252,28 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(coords, 4) ||
         !aligned(sigma, 4) || !aligned(L, 4))
         return PAI_ERR_MISALIGNED;
+    for (const int64_t *st : {q_strides, k_strides, v_strides, o_strides})
+        for (int a = 0; a < 3; ++a) {
+            // rows are moved 16 bytes at a time; an axis of extent 1 may carry any stride (it is never stepped)
+            const int extent = a == 0 ? Z : a == 1 ? H : N;
+            if (st[a] < 0 || st[a] >= (1ll << 38)) return PAI_ERR_BAD_SHAPE;
+            if ((st[a] & 7) != 0 && extent > 1) return PAI_ERR_MISALIGNED;
+            if (st[a] < d && extent > 1) return PAI_ERR_BAD_SHAPE;  // rows of d elements must not overlap
+        }
     if (int e = require_sm100()) return e;
     if (zh_begin == zh_end) return PAI_OK;
     const int nzh = zh_end - zh_begin;
-    const size_t off = (size_t)zh_begin * N * d * 2;
+    auto stride_of = [&](const int64_t *st, int a, int extent) { return extent > 1 ? (long long)st[a] : (long long)d; };
     CUtensorMap mq, mk, mv;
-    if (int e = pai::make_map_bf16_rows(&mq, (const char *)Q + off, nzh, N, d, pai::GA_BM)) return e;
-    if (int e = pai::make_map_bf16_rows(&mk, (const char *)K + off, nzh, N, d, pai::GA_BN)) return e;
-    if (int e = pai::make_map_bf16_rows(&mv, (const char *)V + off, nzh, N, d, pai::GA_BN)) return e;
+    if (int e = pai::make_map_bf16_zhnd(&mq, Q, Z, H, N, d, stride_of(q_strides, 0, Z), stride_of(q_strides, 1, H),
+                                        stride_of(q_strides, 2, N), pai::GA_BM))
+        return e;
+    if (int e = pai::make_map_bf16_zhnd(&mk, K, Z, H, N, d, stride_of(k_strides, 0, Z), stride_of(k_strides, 1, H),
+                                        stride_of(k_strides, 2, N), pai::GA_BN))
+        return e;
+    if (int e = pai::make_map_bf16_zhnd(&mv, V, Z, H, N, d, stride_of(v_strides, 0, Z), stride_of(v_strides, 1, H),
+                                        stride_of(v_strides, 2, N), pai::GA_BN))
+        return e;
     const int smem = (int)sizeof(pai::GaFwdSmem) + 1024;
     static bool attr_done[64];
     int dev = 0;
@@ -271,6 +288,9 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     p.valid = valid;
     p.sigma = sigma;
     p.out = (__nv_bfloat16 *)O;
+    p.so_z = stride_of(o_strides, 0, Z);
+    p.so_h = stride_of(o_strides, 1, H);
+    p.so_n = stride_of(o_strides, 2, N);
     p.lse = L;
     p.Z = Z;
     p.H = H;
@@ -285,6 +305,15 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
     dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
     pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
+}
+
+int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
+                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L, int Z, int H,
+                    int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
+                    void *stream) {
+    const int64_t st[3] = {(int64_t)H * N * d, (int64_t)N * d, (int64_t)d};  // contiguous [Z,H,N,d]
+    return pai_geoattn_fwd_strided(Q, st, K, st, V, st, coords, sigma, betas, valid, sample_order, O, st, L, Z, H, N, d, scale,
+                                   min_rbf, max_rbf, logit_form, zh_begin, zh_end, stream);
 }
 
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
@@ -474,6 +503,29 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
     }
     // Pass 1 overwrites every partial row that pass 2 reads, so nothing in the array has to start at zero.
     return pai::we_bwd_launch(dO, cos_sums, sin_sums, dk, scratch, Z, N, K, row_begin, row_end, (cudaStream_t)stream);
+}
+
+int pai_add_layernorm_bf16(const void *x, const void *y, const void *gamma, const void *beta, int params_fp32, void *out,
+                           long long rows, int D, float eps, void *stream) {
+    if (!x || !gamma || !beta || !out) return PAI_ERR_NULL_POINTER;
+    if (rows < 0 || D < 8 || (D & 7) != 0 || D > 4096 || !(eps >= 0.f)) return PAI_ERR_BAD_SHAPE;
+    if (!aligned(x, 16) || (y && !aligned(y, 16)) || !aligned(out, 16) || !aligned(gamma, 16) || !aligned(beta, 16))
+        return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    if (rows == 0) return PAI_OK;
+    if ((rows + 7) / 8 > 0x7fffffffll) return PAI_ERR_BAD_SHAPE;
+    return pai::add_layernorm_bf16_launch(x, y, gamma, beta, out, rows, D, eps, params_fp32 ? 1 : 0, (cudaStream_t)stream);
+}
+
+int pai_gelu_bf16(const void *x, void *out, long long n, void *stream) {
+    if (!x || !out) return PAI_ERR_NULL_POINTER;
+    if (n < 0 || (n & 7) != 0) return PAI_ERR_BAD_SHAPE;
+    if (!aligned(x, 16) || !aligned(out, 16)) return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    if (n == 0) return PAI_OK;
+    int sms = 0;
+    if (int e = current_device_sms(&sms)) return e;
+    return pai::gelu_bf16_launch(x, out, n, sms, (cudaStream_t)stream);
 }
 
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {

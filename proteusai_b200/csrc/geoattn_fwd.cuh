@@ -63,7 +63,8 @@ struct GaFwdParams {
     const float *coords;   // [Z,N,3]
     const uint8_t *valid;  // [Z,N] or nullptr
     const float *sigma;    // [H]
-    __nv_bfloat16 *out;    // [Z,H,N,64]
+    __nv_bfloat16 *out;    // element (z,h,n,:) at out + z*so_z + h*so_h + n*so_n, 64 contiguous values
+    long long so_z, so_h, so_n;
     float *lse;            // [Z,H,N]  log-sum-exp of SR (natural log), -inf for padded queries
     int Z, H, N, zh_begin;
     float scale;
@@ -180,7 +181,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const bool is_math = warp < GA_FWD_MATH_THREADS / 32;
     const int half = (warp >> 2) & 1;             // 0: key columns 0..63, 1: 64..127
     const int r = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
-    int zh_local = blockIdx.y;                    // index into the tensor maps (they start at zh_begin)
+    int zh_local = blockIdx.y;                    // index into the shard of (batch, head) pairs
     if (p.order) {  // samples in the given order (longest first): neighbouring CTAs get similar amounts of work
         const int zp = zh_local / p.H;
         zh_local = p.order[zp] * p.H + (zh_local - zp * p.H);
@@ -220,7 +221,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();
     const int nt = sm.ntiles;
 
-    __nv_bfloat16 *orow = p.out + ((size_t)zh * N + row) * GA_D + half * 32;
+    __nv_bfloat16 *orow = p.out + (long long)z * p.so_z + (long long)h * p.so_h + (long long)row * p.so_n + half * 32;
     if (!cta_has_query || nt == 0) {  // nothing to attend from / to: zeros and -inf
         if (is_math && row < N) {
 #pragma unroll
@@ -296,11 +297,11 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             };
             auto tile_row = [&](int t) { return (int)(sm.tiles[t] & 0x7fff) * GA_BN; };
             mbar_expect_tx(&sm.bar_q, GA_TILE_BYTES);
-            tma_load_3d(sm.q, &map_q, 0, i0, zh_local, &sm.bar_q);
+            tma_load_4d(sm.q, &map_q, 0, i0, h, z, &sm.bar_q);
             mbar_expect_tx(&sm.bar_k, GA_TILE_BYTES);
-            tma_load_3d(sm.k, &map_k, 0, tile_row(0), zh_local, &sm.bar_k);
+            tma_load_4d(sm.k, &map_k, 0, tile_row(0), h, z, &sm.bar_k);
             mbar_expect_tx(&sm.bar_v, GA_TILE_BYTES);
-            tma_load_3d(sm.v, &map_v, 0, tile_row(0), zh_local, &sm.bar_v);
+            tma_load_4d(sm.v, &map_v, 0, tile_row(0), h, z, &sm.bar_v);
             mbar_wait_timed(&sm.bar_q, 0);
             mbar_wait_timed(&sm.bar_k, 0);
             tc_fence_after();
@@ -308,7 +309,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (nt > 1) {  // the K buffer is free once S(0) has completed
                 mbar_wait_timed(&sm.bar_s, 0);
                 mbar_expect_tx(&sm.bar_k, GA_TILE_BYTES);
-                tma_load_3d(sm.k, &map_k, 0, tile_row(1), zh_local, &sm.bar_k);
+                tma_load_4d(sm.k, &map_k, 0, tile_row(1), h, z, &sm.bar_k);
             }
             for (int t = 0; t < nt; ++t) {
                 const uint32_t par = (uint32_t)(t & 1);
@@ -323,12 +324,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 if (t + 2 < nt) {  // K buffer free once S(t+1) has completed
                     mbar_wait_timed(&sm.bar_s, par ^ 1);
                     mbar_expect_tx(&sm.bar_k, GA_TILE_BYTES);
-                    tma_load_3d(sm.k, &map_k, 0, tile_row(t + 2), zh_local, &sm.bar_k);
+                    tma_load_4d(sm.k, &map_k, 0, tile_row(t + 2), h, z, &sm.bar_k);
                 }
                 if (t + 1 < nt) {  // V buffer free once P V(t) has completed
                     mbar_wait_timed(&sm.bar_o, par);
                     mbar_expect_tx(&sm.bar_v, GA_TILE_BYTES);
-                    tma_load_3d(sm.v, &map_v, 0, tile_row(t + 1), zh_local, &sm.bar_v);
+                    tma_load_4d(sm.v, &map_v, 0, tile_row(t + 1), h, z, &sm.bar_v);
                 }
             }
         }

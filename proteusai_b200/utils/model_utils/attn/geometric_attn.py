@@ -18,6 +18,7 @@ Two logit forms are available (``set_logit_form``):
 Products are bf16 x bf16 with fp32 accumulation (the reference casts to fp16); outputs and gradients come
 back in the dtype of ``Q``.
 """
+import ctypes
 import os
 
 import torch
@@ -55,13 +56,26 @@ def longest_first(mask):
     return torch.argsort((~mask).sum(dim=1), descending=True, stable=True).to(torch.int32)
 
 
+def _strided_ok(t):
+    """True when the kernel can read/write ``t`` ``[Z,H,N,d]`` in place: d contiguous, rows on 16-byte boundaries."""
+    return t.stride(3) == 1 and all(t.size(a) == 1 or (t.stride(a) % 8 == 0 and t.stride(a) >= t.size(3)) for a in range(3))
+
+
+def _strides3(t):
+    return (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+
 def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None,
-                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None):
-    """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V must be bf16 contiguous.
-    Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``; only the pairs of the range are written."""
+                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, out_layout="zhnd"):
+    """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V are bf16 ``[Z,H,N,d]``, read in place through
+    their strides when ``d`` is contiguous and the other strides are multiples of 8 elements (for instance the permuted
+    views of a fused projection output ``[Z,N,3,H,d]``), copied otherwise.  Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``;
+    only the pairs of the range are written.  ``out_layout="znhd"`` allocates O as ``[Z,N,H,d]`` in memory and returns
+    its ``[Z,H,N,d]`` view, so that ``O.permute(0, 2, 1, 3).reshape(Z, N, H*d)`` is free."""
     if not Q.is_cuda:
         raise RuntimeError("geometric_attn needs CUDA tensors: there is no CPU path")
     batch, nheads, n, d_k = Q.shape
+    Q, K, V = (t if _strided_ok(t) else t.contiguous() for t in (Q, K, V))
     zh_end = batch * nheads if zh_end is None else zh_end
     dev = Q.device
     coords = coords.to(torch.float32).contiguous()
@@ -69,14 +83,20 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
     if out is None:
-        out = torch.empty(batch, nheads, n, d_k, dtype=torch.bfloat16, device=dev)
+        if out_layout == "znhd":
+            out = torch.empty(batch, n, nheads, d_k, dtype=torch.bfloat16, device=dev).permute(0, 2, 1, 3)
+        else:
+            out = torch.empty(batch, nheads, n, d_k, dtype=torch.bfloat16, device=dev)
+    elif not _strided_ok(out):
+        raise ValueError("out must have a contiguous last axis and strides that are multiples of 8 elements")
     if lse is None:
         lse = torch.empty(batch, nheads, n, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().pai_geoattn_fwd(
-            _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(coords), _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(valid),
-            _lib.ptr(order), _lib.ptr(out), _lib.ptr(lse), batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf),
-            _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_fwd")
+        _lib.check(_lib.lib().pai_geoattn_fwd_strided(
+            _lib.ptr(Q), _strides3(Q), _lib.ptr(K), _strides3(K), _lib.ptr(V), _strides3(V), _lib.ptr(coords), _lib.ptr(sigma),
+            _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(order), _lib.ptr(out), _strides3(out), _lib.ptr(lse), batch, nheads, n, d_k,
+            1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()),
+            "pai_geoattn_fwd_strided")
     return out, lse
 
 
@@ -118,13 +138,20 @@ class _geometric_attn(torch.autograd.Function):
         assert coords.dim() == 3 and coords.size(2) == 3, f"coordinates must be of shape (batch, N, 3), not {coords.shape}"
         assert spreads.size(0) == nheads, f"number of spreads per batch must be equal to nheads, not {spreads.size(0)=} and {nheads=}"
         assert torch.all(spreads > 0), f"spreads must be a tensor of positive, non-zero floats, not {spreads}"
-        qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
+        # Without a backward to prepare for, Q, K, V are read through their strides (no copies) and O is laid out
+        # [Z,N,H,d] in memory, which is what the head concatenation that follows wants; the backward kernels read
+        # contiguous [Z,H,N,d] tensors, so with gradients everything is made contiguous here once.
+        needs_bwd = any(ctx.needs_input_grad)
+        if needs_bwd:
+            qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
+        else:
+            qb, kb, vb = (t.to(torch.bfloat16) for t in (Q, K, V))
         form = _logit_form
         if form == "beta_abs" and betas is None:
             raise ValueError("the beta_abs logit form needs betas")
         order = None
         out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask, betas=betas, min_rbf=min_rbf, max_rbf=max_rbf, form=form,
-                                   order=order)
+                                   order=order, out_layout="zhnd" if needs_bwd else "znhd")
         ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0),
                               betas if betas is not None else torch.empty(0), order if order is not None else torch.empty(0))
         ctx.has_order = order is not None

@@ -9,13 +9,15 @@ over all heads (and over Q, K, V together for self-attention) instead of the ref
 matmul, which copies the input once per head.
 
 ``Encoder`` is the reference's post-norm block (``old/old_scripts/encoder.py:8-41``): ``LN(x + drop(attn))``
-then ``LN(x + drop(ffn))``.  The reference's ``forward`` passes ``coords_beta`` positionally into a
+then ``LN(x + drop(ffn))``, each one fused kernel in bf16 inference.  The reference's ``forward`` passes ``coords_beta`` positionally into a
 ``GeoAttention.forward`` that has no such parameter (a TypeError there); here it is accepted and unused.
 """
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from proteusai_b200.utils.model_utils.attn.geometric_attn import geometric_attn
+from proteusai_b200.utils.model_utils.base_modules import fused_ops
 from proteusai_b200.utils.model_utils.base_modules.base_modules import MLP
 from proteusai_b200.utils.model_utils.wf_embedding.wf_embedding import WaveFunctionEmbedding
 
@@ -62,8 +64,11 @@ class GeoAttention(nn.Module):
                                 ((q, self.q_proj, self.q_bias), (k, self.k_proj, self.k_bias), (v, self.v_proj, self.v_bias)))
         out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
                              min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
-        out = out.permute(0, 2, 3, 1).reshape(batch, n, self.d_model)  # d_k-major, head-minor
-        return self.out_proj(out)
+        # The reference concatenates the heads d_k-major / head-minor (feature dd*H + h) before out_proj.  The same
+        # product with the heads kept whole (feature h*d_k + dd) and the columns of the weight reordered to match:
+        # the activation view below is free when the kernel wrote O as [Z,N,H,d_k] (inference), the weight is small.
+        w = self.out_proj.weight.view(self.d_model, self.d_k, self.heads).transpose(1, 2).reshape(self.d_model, self.d_model)
+        return F.linear(out.permute(0, 2, 1, 3).reshape(batch, n, self.d_model), w.to(out.dtype))
 
 
 class Encoder(nn.Module):
@@ -77,9 +82,16 @@ class Encoder(nn.Module):
         self.ffn_norm = nn.LayerNorm(d_model)
         self.dropout = nn.Dropout(dropout)
 
+    def _add_norm(self, x, y, norm):
+        """``norm(x + dropout(y))``: one fused pass for bf16 inference, the PyTorch operators otherwise."""
+        drop_off = not self.training or self.dropout.p == 0.0
+        if drop_off and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096 and fused_ops.usable(x, y, norm.weight, norm.bias):
+            return fused_ops.add_layernorm(x, y, norm.weight, norm.bias, norm.eps)
+        return norm(x + self.dropout(y))
+
     def forward(self, q, k, v, coords, coords_beta=None, mask=None):
-        q = self.attn_norm(q + self.dropout(self.attn(q, k, v, coords, mask=mask)))
-        return self.ffn_norm(q + self.dropout(self.ffn(q)))
+        q = self._add_norm(q, self.attn(q, k, v, coords, mask=mask), self.attn_norm)
+        return self._add_norm(q, self.ffn(q), self.ffn_norm)
 
 
 class ProteusEncoderModel(nn.Module):

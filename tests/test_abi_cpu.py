@@ -118,3 +118,27 @@ def test_geoattn_argument_errors(lib):
     bad[25] = 1      # logit form 1 ...
     bad[15] = None   # ... without a dbetas buffer
     assert g(*bad) == -1
+
+
+def test_strided_attention_and_row_op_argument_errors(lib):
+    p = ctypes.c_void_p(0x1000)
+    i64 = lambda *v: (ctypes.c_int64 * 3)(*v)
+    ok = i64(2 * 64 * 64, 64 * 64, 64)
+    f = lib.pai_geoattn_fwd_strided
+    call = lambda **kw: f(p, kw.get("qs", ok), p, ok, p, ok, p, p, None, None, None, p, kw.get("os", ok), p, 2, 2, 64,
+                          kw.get("d", 64), 0.125, 0.0, 1.0, 0, 0, kw.get("ze", 4), None)
+    assert call(qs=None) == -1
+    assert call(d=32) == -4
+    assert call(ze=5) == -6
+    assert call(qs=i64(2 * 64 * 64, 64 * 64, 68)) == -3     # rows off the 16-byte grid
+    assert call(os=i64(2 * 64 * 64, 64 * 64, 32)) == -2     # overlapping rows
+    assert call(qs=i64(-8, 64 * 64, 64)) == -2
+    g = lib.pai_add_layernorm_bf16
+    assert g(None, p, p, p, 0, p, 4, 512, 1e-5, None) == -1
+    assert g(p, p, p, p, 0, p, 4, 516, 1e-5, None) == -2      # D must be a multiple of 8
+    assert g(p, p, p, p, 0, p, 4, 8192, 1e-5, None) == -2     # ... and at most 4096
+    assert g(p, ctypes.c_void_p(0x1008), p, p, 0, p, 4, 512, 1e-5, None) == -3
+    h = lib.pai_gelu_bf16
+    assert h(p, None, 64, None) == -1
+    assert h(p, p, 60, None) == -2
+    assert h(ctypes.c_void_p(0x1004), p, 64, None) == -3

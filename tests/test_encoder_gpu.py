@@ -69,3 +69,54 @@ def test_encoder_model_inference_matches_oracle_composition():
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         lb = model(tokens.cuda(), c.cuda(), m.cuda()).float().cpu()
     assert (lb[valid].argmax(-1) == ref[valid].argmax(-1)).float().mean().item() >= 0.9
+
+
+def test_encoder_model_bf16_inference_uses_fused_ops_and_matches_oracle_composition():
+    """The bf16 inference configuration: strided Q/K/V straight from the fused projection, O written head-major,
+    LayerNorm(x + y) and GELU as fused kernels.  Compared with the fp32 oracle composition of the same weights."""
+    from proteusai_b200.utils.model_utils.base_modules.encoder import ProteusEncoderModel
+    torch.manual_seed(5)
+    model = ProteusEncoderModel(d_model=128, heads=2, layers=2, d_hidden=256).cuda().eval()
+    lengths = [200, 64, 131]
+    c, m = chains.chain_batch(lengths, 200, seed=6)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    tokens = torch.randint(0, 33, (3, 200), generator=torch.Generator().manual_seed(7))
+    with torch.no_grad():
+        ref = _reference_forward(model, tokens, c, m)
+        model.to_compute_dtype_(torch.bfloat16)
+        logits = model(tokens.cuda(), c.cuda(), m.cuda()).float().cpu()
+    valid = ~m
+    err = (logits[valid] - ref[valid]).abs().max().item()
+    agree = (logits[valid].argmax(-1) == ref[valid].argmax(-1)).float().mean().item()
+    assert err < 1e-1 and agree >= 0.95, (err, agree)
+
+
+@pytest.mark.parametrize("d", [8, 128, 512, 520, 1024, 4096])
+def test_add_layernorm_kernel(d):
+    from proteusai_b200.utils.model_utils.base_modules import fused_ops
+    g = torch.Generator().manual_seed(d)
+    rows = 37
+    x = torch.randn(rows, d, generator=g).to(torch.bfloat16)
+    y = (3 * torch.randn(rows, d, generator=g) + 1).to(torch.bfloat16)
+    w = torch.randn(d, generator=g)
+    b = torch.randn(d, generator=g)
+    ref = torch.nn.functional.layer_norm(x.float() + y.float(), (d,), w, b, 1e-5)
+    out = fused_ops.add_layernorm(x.cuda(), y.cuda(), w.cuda(), b.cuda(), 1e-5)
+    assert out.dtype == torch.bfloat16
+    assert (out.float().cpu() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    wb, bb = w.to(torch.bfloat16), b.to(torch.bfloat16)
+    ref = torch.nn.functional.layer_norm(x.float(), (d,), wb.float(), bb.float(), 1e-5)
+    out = fused_ops.add_layernorm(x.cuda(), None, wb.cuda(), bb.cuda(), 1e-5)
+    assert (out.float().cpu() - ref).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+
+
+def test_gelu_kernel():
+    from proteusai_b200.utils.model_utils.base_modules import fused_ops
+    x = torch.cat([torch.linspace(-12, 12, 4001), torch.randn(4096 - 4001 + 8 * 100, generator=torch.Generator().manual_seed(0))])
+    x = x[: (x.numel() // 8) * 8].to(torch.bfloat16)
+    ref = torch.nn.functional.gelu(x.double())
+    out = fused_ops.gelu(x.cuda()).float().cpu().double()
+    assert ((out - ref).abs() <= 2 ** -8 * ref.abs() + 1e-7).all()
+    y = x.cuda().clone()
+    assert fused_ops.gelu(y, inplace=True).data_ptr() == y.data_ptr()
+    assert torch.equal(y.float().cpu().double(), out)

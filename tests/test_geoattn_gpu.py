@@ -130,3 +130,34 @@ def test_in_tree_form_matches_reference_golden(ga, golden_dir):
         ga.set_logit_form(prev)
     from proteusai_b200 import _lib
     _lib.device_status()
+
+
+def test_strided_inputs_and_head_major_output(ga):
+    """Q, K, V read in place as the [Z,H,N,d] views of a fused projection output [Z,N,3,H,d], O written as [Z,N,H,d]:
+    the same kernel on the same values, so the results equal those of the contiguous call bit for bit."""
+    z, h, n, d = 2, 3, 200, 64
+    g = torch.Generator().manual_seed(31)
+    y = (torch.randn(z, n, 3, h, d, generator=g) / 8).to(torch.bfloat16).cuda()
+    q, k, v = (y[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    assert not q.is_contiguous()
+    c, m = chains.chain_batch([200, 77], n, seed=32)
+    c, m = torch.from_numpy(c).cuda(), torch.from_numpy(m).cuda()
+    sig = torch.from_numpy(chains.sigmas(h)).cuda()
+    o_ref, l_ref = ga.geoattn_forward(q.contiguous(), k.contiguous(), v.contiguous(), c, sig, m)
+    o, l = ga.geoattn_forward(q, k, v, c, sig, m, out_layout="znhd")
+    assert o.shape == (z, h, n, d) and o.permute(0, 2, 1, 3).is_contiguous()
+    assert torch.equal(o, o_ref) and torch.equal(l, l_ref)
+    # a shard of the (batch, head) pairs through the strided path
+    o2 = torch.zeros_like(o)
+    ga.geoattn_forward(q, k, v, c, sig, m, 2, 5, out=o2)
+    assert torch.equal(o2.reshape(z * h, n, d)[2:5], o_ref.reshape(z * h, n, d)[2:5])
+    assert torch.all(o2.reshape(z * h, n, d)[:2] == 0) and torch.all(o2.reshape(z * h, n, d)[5:] == 0)
+    # the public call without gradients takes the strided path and returns the head-major layout
+    with torch.no_grad():
+        pub = ga.geometric_attn(q, k, v, c, sig, None, mask=m)
+    assert torch.equal(pub, o_ref) and pub.permute(0, 2, 1, 3).is_contiguous()
+    # rows that are not on 16-byte boundaries are copied, not rejected
+    odd = torch.zeros(z, h, n, d + 4, dtype=torch.bfloat16, device="cuda")[..., 2:d + 2]
+    odd.copy_(q)
+    o3, _ = ga.geoattn_forward(odd, k, v, c, sig, m)
+    assert torch.equal(o3, o_ref)
