@@ -268,7 +268,7 @@ def run_reference(args):
     evals = rows * (N_SEQ - 1) * K_WN
     value = evals * len(times) / sum(times)
     line = {
-        "impl": "reference", "metric": "WE pair*wavenumber evals/s @N=16384,d=512", "value": value, "unit": "evals/s",
+        "impl": "reference", "metric": f"WE pair*wavenumber evals/s @N={N_SEQ},d=512", "value": value, "unit": "evals/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * EVALS_PER_STEP / value, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -395,7 +395,7 @@ def main():
         achieved = evals_per_launch / (kern_ms * 1e-3)
         nominal = SFU_NOMINAL_PAIRS_PER_CLK_SM * sms * (clocks["sm_max_mhz"] or 1965) * 1e6
         line = {
-            "metric": "WE pair*wavenumber evals/s @N=16384,d=512", "value": value, "unit": "evals/s",
+            "metric": f"WE pair*wavenumber evals/s @N={N_SEQ},d=512", "value": value, "unit": "evals/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": total_ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": value / H100_PUBLISHED_EVALS_PER_S if N_SEQ == 16384 else None,
             "dtype": "f32", "data": "synthetic",

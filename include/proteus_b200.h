@@ -159,7 +159,8 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
  *   with S_ij = q_i.k_j * scale, R_ij = exp(-|r_i-r_j|^2 / (2 sigma_h^2)), softmax over the keys j, a pair (i,j) valid
  *   iff both tokens are unpadded.
  *
- *   Q, K, V  [Z,H,N,d] bf16, contiguous     (d must be 64)
+ *   Q, K, V  [Z,H,N,d] bf16, contiguous     (d must be 64; a caller with narrower heads zero-pads Q, K, V to 64 and
+ *                                            passes the scale of the true width, as the Python wrapper does)
  *   coords   [Z,N,3]   fp32                 C-alpha coordinates
  *   sigma    [H]       fp32                 per-head RBF spread
  *   betas    [H]       fp32                 per-head RBF weight (logit_form 1)

@@ -16,7 +16,7 @@ Two logit forms are available (``set_logit_form``):
                               is returned.
 
 Products are bf16 x bf16 with fp32 accumulation (the reference casts to fp16); outputs and gradients come
-back in the dtype of ``Q``.
+back in the dtype of ``Q``.  Heads of up to 64 dimensions are supported (narrower ones run zero-padded to 64).
 """
 import ctypes
 import os
@@ -26,6 +26,7 @@ import torch
 from proteusai_b200 import _lib
 
 _FORMS = {"one_plus_rbf": 0, "beta_abs": 1}
+_KERNEL_D = 64  # head dimension the kernels are built for; narrower heads are zero-padded by geometric_attn
 _logit_form = os.environ.get("PROTEUS_GEOATTN_FORM", "one_plus_rbf")
 
 
@@ -40,6 +41,23 @@ def set_logit_form(name):
 
 def get_logit_form():
     return _logit_form
+
+
+_check_spreads = True
+
+
+class spreads_known_positive:
+    """Context in which ``geometric_attn`` skips its ``spreads > 0`` assertion.  The assertion copies a flag from the
+    device and so stalls the host once per call; a caller whose spreads are positive by construction (``GeoAttention``:
+    ``min_spread + exp(w)``) wraps its call in this to keep the launch queue running ahead of the GPU."""
+
+    def __enter__(self):
+        global _check_spreads
+        self.prev, _check_spreads = _check_spreads, False
+
+    def __exit__(self, *exc):
+        global _check_spreads
+        _check_spreads = self.prev
 
 
 def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00, max_rbf=1.00):
@@ -66,12 +84,13 @@ def _strides3(t):
 
 
 def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None,
-                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, out_layout="zhnd"):
+                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, out_layout="zhnd", scale=None):
     """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V are bf16 ``[Z,H,N,d]``, read in place through
     their strides when ``d`` is contiguous and the other strides are multiples of 8 elements (for instance the permuted
     views of a fused projection output ``[Z,N,3,H,d]``), copied otherwise.  Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``;
     only the pairs of the range are written.  ``out_layout="znhd"`` allocates O as ``[Z,N,H,d]`` in memory and returns
-    its ``[Z,H,N,d]`` view, so that ``O.permute(0, 2, 1, 3).reshape(Z, N, H*d)`` is free."""
+    its ``[Z,H,N,d]`` view, so that ``O.permute(0, 2, 1, 3).reshape(Z, N, H*d)`` is free.  ``scale`` is the softmax scale
+    (default ``1/sqrt(d)``)."""
     if not Q.is_cuda:
         raise RuntimeError("geometric_attn needs CUDA tensors: there is no CPU path")
     batch, nheads, n, d_k = Q.shape
@@ -80,7 +99,7 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     dev = Q.device
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
-    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
     if out is None:
         if out_layout == "znhd":
@@ -95,13 +114,13 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
         _lib.check(_lib.lib().pai_geoattn_fwd_strided(
             _lib.ptr(Q), _strides3(Q), _lib.ptr(K), _strides3(K), _lib.ptr(V), _strides3(V), _lib.ptr(coords), _lib.ptr(sigma),
             _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(order), _lib.ptr(out), _strides3(out), _lib.ptr(lse), batch, nheads, n, d_k,
-            1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()),
-            "pai_geoattn_fwd_strided")
+            float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin,
+            zh_end, _lib.current_stream()), "pai_geoattn_fwd_strided")
     return out, lse
 
 
 def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0, zh_end=None,
-                     betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None):
+                     betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, scale=None):
     """Gradients on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V, O, dO bf16 contiguous.
     Returns fp32 ``(dQ, dK, dV [Z,H,N,d], d_spreads [H])`` and, for the ``beta_abs`` form, ``d_betas [H]`` as a fifth
     element; only the pairs of the range are written."""
@@ -110,7 +129,7 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
     dev = Q.device
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
-    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
     dq, dk, dv = (torch.empty(batch, nheads, n, d_k, dtype=torch.float32, device=dev) for _ in range(3))
     dsig = torch.empty(nheads, dtype=torch.float32, device=dev)
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
@@ -122,8 +141,8 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
         _lib.check(lib.pai_geoattn_bwd(
             _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(dO), _lib.ptr(lse), _lib.ptr(coords),
             _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(order), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig),
-            _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, 1.0 / (d_k ** 0.5), float(min_rbf),
-            float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_bwd")
+            _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, float(scale) if scale is not None else 1.0 / (d_k ** 0.5),
+            float(min_rbf), float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_bwd")
     if form == "beta_abs":
         return dq, dk, dv, dsig, dbeta
     return dq, dk, dv, dsig
@@ -137,12 +156,22 @@ class _geometric_attn(torch.autograd.Function):
         batch, nheads, N, d_k = Q.shape
         assert coords.dim() == 3 and coords.size(2) == 3, f"coordinates must be of shape (batch, N, 3), not {coords.shape}"
         assert spreads.size(0) == nheads, f"number of spreads per batch must be equal to nheads, not {spreads.size(0)=} and {nheads=}"
-        assert torch.all(spreads > 0), f"spreads must be a tensor of positive, non-zero floats, not {spreads}"
+        if _check_spreads:  # reads the device back (a host synchronisation), as the reference's assert does
+            assert torch.all(spreads > 0), f"spreads must be a tensor of positive, non-zero floats, not {spreads}"
         # Without a backward to prepare for, Q, K, V are read through their strides (no copies) and O is laid out
         # [Z,N,H,d] in memory, which is what the head concatenation that follows wants; the backward kernels read
         # contiguous [Z,H,N,d] tensors, so with gradients everything is made contiguous here once.
         needs_bwd = any(ctx.needs_input_grad)
-        if needs_bwd:
+        if d_k > _KERNEL_D:
+            raise RuntimeError(f"geometric_attn: head dimension {d_k} is not supported by the B200 kernel (at most {_KERNEL_D})")
+        scale = 1.0 / (d_k ** 0.5)
+        if d_k < _KERNEL_D:
+            # The kernel is built for heads of 64.  Narrower heads (the reference's own test uses 32) run zero-padded:
+            # zeros add nothing to Q K^T, the extra columns of V give zero columns of O, and the softmax scale stays
+            # that of the true width.  The padded columns are cut off again below (and from the gradients).
+            pad = lambda t: torch.nn.functional.pad(t.to(torch.bfloat16), (0, _KERNEL_D - d_k))
+            qb, kb, vb = pad(Q), pad(K), pad(V)
+        elif needs_bwd:
             qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
         else:
             qb, kb, vb = (t.to(torch.bfloat16) for t in (Q, K, V))
@@ -151,7 +180,7 @@ class _geometric_attn(torch.autograd.Function):
             raise ValueError("the beta_abs logit form needs betas")
         order = None
         out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask, betas=betas, min_rbf=min_rbf, max_rbf=max_rbf, form=form,
-                                   order=order, out_layout="zhnd" if needs_bwd else "znhd")
+                                   order=order, out_layout="zhnd" if needs_bwd else "znhd", scale=scale)
         ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0),
                               betas if betas is not None else torch.empty(0), order if order is not None else torch.empty(0))
         ctx.has_order = order is not None
@@ -159,7 +188,8 @@ class _geometric_attn(torch.autograd.Function):
         ctx.form, ctx.min_rbf, ctx.max_rbf = form, min_rbf, max_rbf
         ctx.in_dtype = Q.dtype
         ctx.spread_dtype = spreads.dtype
-        return out.to(Q.dtype)
+        ctx.d_k, ctx.scale = d_k, scale
+        return out[..., :d_k].to(Q.dtype)
 
     @staticmethod
     def backward(ctx, dO):
@@ -167,11 +197,15 @@ class _geometric_attn(torch.autograd.Function):
         mask = mask if ctx.has_mask else None
         order = order if ctx.has_order else None
         dt = ctx.in_dtype
+        d_k = ctx.d_k
+        if d_k < _KERNEL_D:
+            dO = torch.nn.functional.pad(dO, (0, _KERNEL_D - d_k))
         if ctx.form == "beta_abs":
             dq, dk, dv, dsig, dbeta = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads,
                                                        mask, betas=betas, min_rbf=ctx.min_rbf, max_rbf=ctx.max_rbf, form=ctx.form,
-                                                       order=order)
-            return dq.to(dt), dk.to(dt), dv.to(dt), None, dsig.to(ctx.spread_dtype), dbeta.to(betas.dtype), None, None, None
+                                                       order=order, scale=ctx.scale)
+            return (dq[..., :d_k].to(dt), dk[..., :d_k].to(dt), dv[..., :d_k].to(dt), None, dsig.to(ctx.spread_dtype),
+                    dbeta.to(betas.dtype), None, None, None)
         dq, dk, dv, dsig = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads, mask,
-                                            order=order)
-        return dq.to(dt), dk.to(dt), dv.to(dt), None, dsig.to(ctx.spread_dtype), None, None, None, None
+                                            order=order, scale=ctx.scale)
+        return dq[..., :d_k].to(dt), dk[..., :d_k].to(dt), dv[..., :d_k].to(dt), None, dsig.to(ctx.spread_dtype), None, None, None, None

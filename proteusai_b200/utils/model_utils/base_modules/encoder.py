@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from proteusai_b200.utils.model_utils.attn.geometric_attn import geometric_attn
+from proteusai_b200.utils.model_utils.attn.geometric_attn import geometric_attn, spreads_known_positive
 from proteusai_b200.utils.model_utils.base_modules import fused_ops
 from proteusai_b200.utils.model_utils.base_modules.base_modules import MLP
 from proteusai_b200.utils.model_utils.wf_embedding.wf_embedding import WaveFunctionEmbedding
@@ -62,8 +62,9 @@ class GeoAttention(nn.Module):
         else:
             (Q,), (K,), (V,) = (self._project(x, (w,), (b,)) for x, w, b in
                                 ((q, self.q_proj, self.q_bias), (k, self.k_proj, self.k_bias), (v, self.v_proj, self.v_bias)))
-        out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
-                             min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
+        with spreads_known_positive():  # min_spread + exp(w) > 0: no need to read it back from the device
+            out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
+                                 min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
         # The reference concatenates the heads d_k-major / head-minor (feature dd*H + h) before out_proj.  The same
         # product with the heads kept whole (feature h*d_k + dd) and the columns of the weight reordered to match:
         # the activation view below is free when the kernel wrote O as [Z,N,H,d_k] (inference), the weight is small.

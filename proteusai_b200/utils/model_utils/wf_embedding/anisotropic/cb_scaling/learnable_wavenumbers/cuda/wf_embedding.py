@@ -31,7 +31,7 @@ def we_aniso_forward_rows(coordsA, coordsB, cb_magnitudes, wavenumbers, mask=Non
     wn = wavenumbers.detach().to(torch.float32).contiguous()
     k = wn.shape[0]
     assert cb.shape[0] == k
-    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
     dev = coordsA.device
     out, d_cb, d_k = (torch.empty(batch, n, 2 * k, dtype=torch.float32, device=dev) for _ in range(3))
     with torch.cuda.device(dev):

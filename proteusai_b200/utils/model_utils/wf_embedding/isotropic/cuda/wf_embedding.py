@@ -39,7 +39,7 @@ def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=
     planes = coords.transpose(1, 2).to(torch.float32).contiguous()
     wn = wavenumbers.detach().to(torch.float32).contiguous()
     k = wn.shape[0]
-    valid = None if mask is None else (~mask).to(torch.uint8).contiguous()
+    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
     dev = coords.device
     if out is None:
         out = torch.empty(batch, n, 2 * k, dtype=torch.float32, device=dev)

@@ -161,3 +161,44 @@ def test_strided_inputs_and_head_major_output(ga):
     odd.copy_(q)
     o3, _ = ga.geoattn_forward(odd, k, v, c, sig, m)
     assert torch.equal(o3, o_ref)
+
+
+@pytest.mark.parametrize("form", ["beta_abs", "one_plus_rbf"])
+def test_reference_test_configuration_with_heads_of_32(ga, form):
+    """The reference test's own setup (tests/attn/geo_attn.py:14-31): batch 1, 4 heads, N 128, d_model 128, i.e. heads
+    of 32, fp32 N(0,1) inputs, collinear coordinates 50 N(0,1), spreads 3, betas 1, window [0, 1], at its tolerance
+    (atol 1e-2, :39) against the oracle on the bf16-rounded inputs.  Heads narrower than 64 run zero-padded."""
+    from oracle.geoattn_ref import geoattn_grads_autograd
+    g = torch.Generator().manual_seed(41)
+    z, h, n, dk = 1, 4, 128, 32
+    q, k, v = (torch.randn(z, h, n, dk, generator=g) for _ in range(3))
+    coords = (50 * torch.randn(z, n, 1, generator=g)).expand(z, n, 3).contiguous()
+    spreads, betas = torch.full((h,), 3.0), torch.full((h,), 1.0)
+    mask = torch.zeros(z, n, dtype=torch.bool)
+    d_out = torch.randn(z, h, n, dk, generator=g)
+    rnd = lambda t: t.to(torch.bfloat16).float()
+    o_ref, grads = geoattn_grads_autograd(rnd(q), rnd(k), rnd(v), coords, spreads, rnd(d_out), mask, variant=form, betas=betas,
+                                          min_rbf=0.0, max_rbf=1.0)
+    prev = ga.set_logit_form(form)
+    try:
+        leaves = [t.cuda().requires_grad_(True) for t in (q, k, v, spreads, betas)]
+        out = ga.geometric_attn(leaves[0], leaves[1], leaves[2], coords.cuda(), leaves[3], leaves[4], mask.cuda(), 0.0, 1.0)
+        assert out.shape == (z, h, n, dk) and out.dtype == torch.float32
+        out.backward(rnd(d_out).cuda())
+    finally:
+        ga.set_logit_form(prev)
+    assert (out.detach().cpu() - o_ref.detach()).abs().max().item() < 1e-2
+    for got, ref, nm in zip(leaves[:3], grads[:3], ("dq", "dk", "dv")):
+        assert got.grad.shape == (z, h, n, dk)
+        assert (got.grad.cpu() - ref).abs().max().item() < 1e-2 + ref.abs().max().item() * 2 ** -8, nm
+    assert torch.all((leaves[3].grad.cpu() - grads[3]).abs() <= 2e-2 * grads[3].abs() + 5e-3)
+    if form == "beta_abs":
+        assert torch.all((leaves[4].grad.cpu() - grads[4]).abs() <= 2e-2 * grads[4].abs() + 5e-3)
+    with torch.no_grad():  # the copy-free inference path pads and slices too
+        o2 = ga.geometric_attn(q.cuda(), k.cuda(), v.cuda(), coords.cuda(), spreads.cuda(), betas.cuda(), mask.cuda(), 0.0, 1.0) \
+            if form == "one_plus_rbf" else None
+    if o2 is not None:
+        assert (o2.cpu() - o_ref.detach()).abs().max().item() < 1e-2
+    with pytest.raises(RuntimeError):
+        ga.geometric_attn(torch.zeros(1, 1, 8, 128).cuda(), torch.zeros(1, 1, 8, 128).cuda(), torch.zeros(1, 1, 8, 128).cuda(),
+                          torch.zeros(1, 8, 3).cuda(), torch.ones(1).cuda(), None)
