@@ -242,6 +242,32 @@ int pai_add_layernorm_bf16(const void *x, const void *y, const void *gamma, cons
 int pai_gelu_bf16(const void *x, void *out, long long n, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Nearest-neighbour graph and radial-basis edge features: FeaturizeProtein.get_neighbors and the tensor part of
+ * FeaturizeProtein.get_edges (utils/model_utils/gnn/gnn.py:97-117 and :119-131), which the reference evaluates in
+ * PyTorch through an N x N distance matrix, torch.topk and a [Z,N,K,4,4,R] broadcast (no reference FFI to replace).
+ *
+ * pai_knn_neighbors
+ *   ca        [Z,N,3] fp32   C-alpha coordinates
+ *   valid     [Z,N]   u8     1 = real node, 0 = masked (the inverse of the reference's node_mask); NULL = all real
+ *   idx       [Z,N,K] i64    the K nearest nodes of each node in ascending order of distance (ties: lower index first);
+ *                            an edge that is dropped points back at its own node, as in the reference
+ *   edge_mask [Z,N,K] u8     1 = edge kept: both nodes real and distance < max_dist (12 in the reference)
+ *   Candidates of a real node are all nodes at non-zero distance, masked ones included (their padding coordinates take
+ *   part in the selection exactly as in the reference, and such edges are then dropped); a masked node gets itself K
+ *   times and no edge.  Distances are rounded as PyTorch rounds them (fp32 differences, squares, sum in x, y, z order,
+ *   IEEE square root).  Requires K <= N (the reference asserts it) and K <= 64.
+ * pai_edge_rbf
+ *   atoms     [Z,N,A,3] fp32  backbone atoms per node (A = 4 in the reference: N, C-alpha, C, C-beta)
+ *   idx       [Z,N,K]   i64   neighbour indices (within the batch element), e.g. from pai_knn_neighbors
+ *   centers   [R]       fp32  RBF centres; spread as the reference's Python float
+ *   out       [Z,N,K,A*A*R] fp32  out[..., (a*A + b)*R + r] = exp(-(|atoms[z,i,a] - atoms[z,idx,b]| - centers[r])^2 / spread^2)
+ */
+int pai_knn_neighbors(const float *ca, const uint8_t *valid, int64_t *idx, uint8_t *edge_mask,
+                      int Z, int N, int K, float max_dist, void *stream);
+int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread, float *out,
+                 int Z, int N, int K, int A, int R, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Measured SFU (MUFU) throughput of the current device: runs a register-only sin+cos loop and
  * returns results per second through *sincos_pairs_per_s (one pair = one sin and one cos, which is
  * what one WE evaluation needs) and the elapsed device time.  Synchronous.  Used as the

@@ -4,6 +4,7 @@
 
 #include "geoattn_bwd.cuh"
 #include "encoder_ops.cuh"
+#include "neighbors.cuh"
 #include "geoattn_fwd.cuh"
 #include "we_bwd.cuh"
 #include "we_fwd.cuh"
@@ -526,6 +527,28 @@ int pai_gelu_bf16(const void *x, void *out, long long n, void *stream) {
     int sms = 0;
     if (int e = current_device_sms(&sms)) return e;
     return pai::gelu_bf16_launch(x, out, n, sms, (cudaStream_t)stream);
+}
+
+int pai_knn_neighbors(const float *ca, const uint8_t *valid, int64_t *idx, uint8_t *edge_mask, int Z, int N, int K, float max_dist,
+                      void *stream) {
+    if (!ca || !idx || !edge_mask) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || K > N || (long long)Z * N > (1ll << 31)) return PAI_ERR_BAD_SHAPE;
+    if (K > pai::KNN_MAX_K) return PAI_ERR_UNSUPPORTED;
+    if (!aligned(ca, 4) || !aligned(idx, 8)) return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    static_assert(sizeof(long long) == sizeof(int64_t), "index type");
+    return pai::knn_launch(ca, valid, (long long *)idx, edge_mask, Z, N, K, max_dist, (cudaStream_t)stream);
+}
+
+int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread, float *out, int Z, int N, int K, int A,
+                 int R, void *stream) {
+    if (!atoms || !idx || !centers || !out) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || A < 1 || R < 1 || A > 64 || R > 4096 || !(spread > 0.0)) return PAI_ERR_BAD_SHAPE;
+    if (!aligned(atoms, 4) || !aligned(idx, 8) || !aligned(centers, 4) || !aligned(out, 16)) return PAI_ERR_MISALIGNED;
+    if (int e = require_sm100()) return e;
+    int sms = 0;
+    if (int e = current_device_sms(&sms)) return e;
+    return pai::edge_rbf_launch(atoms, (const long long *)idx, centers, spread, out, Z, N, K, A, R, sms, (cudaStream_t)stream);
 }
 
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {

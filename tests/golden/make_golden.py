@@ -11,6 +11,8 @@ are cut out of their files by AST and executed as they stand:
 * ``wf_embedding_torch``  from ``tests/wf_embed/wf_embed.py``
 * ``torch_attn``          from ``tests/attn/geo_attn.py``
 * ``wf_embedding_torch``  (anisotropic, C-beta scaling) from ``tests/wf_embed/wf_embed_aniso_learnCB_learnK.py``
+* ``FeaturizeProtein.get_neighbors`` / ``get_edges`` from ``utils/model_utils/gnn/gnn.py`` (a second argument ``gnn``
+  regenerates only their file)
 
 Inputs are seeded; inputs and the reference's outputs (and gradients obtained by
 autograd through the reference functions, as the reference's tests do) are stored in
@@ -38,6 +40,58 @@ def extract(path, name):
             exec(compile(ast.Module(body=[node], type_ignores=[]), path, "exec"), ns)
             return ns[name]
     raise KeyError(name)
+
+
+def extract_method(path, cls, name):
+    """A method of a class in the reference file, as a plain function taking ``self`` first."""
+    tree = ast.parse(open(path).read())
+    for node in tree.body:
+        if isinstance(node, ast.ClassDef) and node.name == cls:
+            for item in node.body:
+                if isinstance(item, ast.FunctionDef) and item.name == name:
+                    ns = {"torch": torch}
+                    exec(compile(ast.Module(body=[item], type_ignores=[]), path, "exec"), ns)
+                    return ns[name]
+    raise KeyError(f"{cls}.{name}")
+
+
+def backbone_atoms(ca, rng):
+    """Four atoms per node (N, C-alpha, C, C-beta) at bonded distances around the C-alpha trace."""
+    z, n, _ = ca.shape
+    off = rng.normal(size=(z, n, 4, 3))
+    off /= np.linalg.norm(off, axis=3, keepdims=True)
+    off *= np.array([1.46, 0.0, 1.52, 1.53])[None, None, :, None]
+    return (ca[:, :, None, :] + off).astype(np.float32)
+
+
+def gnn_golden(ref_root):
+    """Neighbour graph and edge features from the reference's own FeaturizeProtein methods (gnn.py:97-131)."""
+    from types import SimpleNamespace
+    path = os.path.join(ref_root, "utils/model_utils/gnn/gnn.py")
+    get_neighbors = extract_method(path, "FeaturizeProtein", "get_neighbors")
+    get_edges = extract_method(path, "FeaturizeProtein", "get_edges")
+    min_rbf, max_rbf, num_rbfs = 2.0, 22.0, 16          # the reference's defaults (gnn.py:24)
+    blob = {}
+    rng = np.random.default_rng(20240606)
+    for name, lengths, n, k in (("padded_k30", [48, 20], 48, 30), ("short_k8", [40, 9], 40, 8), ("k40", [90], 90, 40)):
+        c, m = chains.chain_batch(lengths, n, seed=23)
+        # Chains start at the origin, which is also where padding sits: move the real nodes away, otherwise the first node
+        # of a chain ties exactly with every padded node and torch.topk's unspecified tie order decides the outputs.
+        c[~m] += np.array([7.25, -4.5, 2.75], dtype=np.float32)
+        if name == "short_k8":
+            c[0, 5] = c[0, 4]  # a coincident pair
+        atoms = backbone_atoms(c, rng)
+        me = SimpleNamespace(K=k, rbf_centers=torch.linspace(min_rbf, max_rbf, num_rbfs), spread=(max_rbf - min_rbf) / num_rbfs,
+                             edge_norm=lambda t: t, edge_proj=lambda t: t)  # the two modules after the features: identity here
+        ca, mask = torch.from_numpy(atoms[:, :, 1].copy()), torch.from_numpy(m)
+        idx, edge_mask = get_neighbors(me, ca, node_mask=mask)
+        feats = get_edges(me, torch.from_numpy(atoms), idx)
+        blob.update({f"{name}.atoms": atoms, f"{name}.mask": m, f"{name}.k": np.int64(k), f"{name}.idx": idx.numpy(),
+                     f"{name}.edge_mask": edge_mask.numpy(), f"{name}.centers": me.rbf_centers.numpy(),
+                     f"{name}.spread": np.float64(me.spread)})
+        if name != "k40":  # (the feature tensor is large: kept for two cases)
+            blob[f"{name}.feats"] = feats.numpy()
+    np.savez_compressed(os.path.join(HERE, "gnn_reference.npz"), **blob)
 
 
 def we_cases():
@@ -97,7 +151,12 @@ def attn_d64_cases():
     return cases
 
 
-def main(ref_root):
+def main(ref_root, only=None):
+    torch.set_num_threads(1)
+    if only == "gnn":
+        gnn_golden(ref_root)
+        print("wrote gnn_reference.npz")
+        return
     wf_embedding_torch = extract(os.path.join(ref_root, "tests/wf_embed/wf_embed.py"), "wf_embedding_torch")
     torch_attn = extract(os.path.join(ref_root, "tests/attn/geo_attn.py"), "torch_attn")
     torch.set_num_threads(1)  # reductions stay in one fixed order
@@ -174,8 +233,9 @@ def main(ref_root):
                      f"{name}.mask": mask.numpy(), f"{name}.d_out": d_out.numpy(), f"{name}.out": out.detach().numpy(),
                      f"{name}.d_cb": cbm_g.grad.numpy(), f"{name}.d_wn": wn_g.grad.numpy()})
     np.savez_compressed(os.path.join(HERE, "we_aniso_reference.npz"), **blob)
+    gnn_golden(ref_root)
     print("wrote", sorted(os.listdir(HERE)))
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", sys.argv[2] if len(sys.argv) > 2 else None)

