@@ -227,6 +227,67 @@ def bench_encoder(dev, world, rank, steps, dist):
                        "sharding": f"batch over {world} rank(s), no collective"}}
 
 
+def bench_graph(dev, steps, cpu_baseline):
+    """Neighbour graph (K = 30) and radial-basis edge features (4 x 4 atom pairs x 16 centres) of one chain of
+    N = 16384 nodes, the step after the WE in the reference's featuriser.  One GPU (rank 0): the reference
+    runs this per sample; nothing to shard inside one chain.  The edge-feature kernel is HBM-write bound (1 kB per edge)."""
+    from oracle import chains
+    from proteusai_b200.utils.model_utils.gnn.gnn import edge_rbf, knn_neighbors
+    n, k = 16384, 30
+    c, _ = chains.chain_batch([n], n, seed=SEED)
+    rng = np.random.default_rng(SEED)
+    off = rng.normal(size=(1, n, 4, 3))
+    off /= np.linalg.norm(off, axis=3, keepdims=True)
+    off *= np.array([1.46, 0.0, 1.52, 1.53])[None, None, :, None]
+    atoms_h = torch.from_numpy((c[:, :, None, :] + off).astype(np.float32))
+    atoms = atoms_h.to(dev)
+    ca = atoms[:, :, 1].contiguous()
+    centers = torch.linspace(2.0, 22.0, 16, device=dev)
+    spread = 20.0 / 16
+
+    def timed_ms(fn):
+        for _ in range(3):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / steps
+
+    idx, _ = knn_neighbors(ca, None, k)
+    knn_ms = timed_ms(lambda: knn_neighbors(ca, None, k))
+    rbf_ms = timed_ms(lambda: edge_rbf(atoms, idx, centers, spread))  # 503 MB written per call: larger than L2
+    edges = n * k
+    out_bytes = edges * 256 * 4
+    hbm = None
+    try:
+        hbm = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        pass
+    peak, src = (hbm, "measured (MEASURED_PEAKS.json, copy bandwidth)") if hbm else (6650.0, "fallback")
+    res = {"metric": "graph featurisation nodes/s (K nearest + edge RBFs)", "value": n / ((knn_ms + rbf_ms) * 1e-3), "unit": "nodes/s",
+           "knn_ms": knn_ms, "edge_rbf_ms": rbf_ms, "dtype": "f32",
+           "config": {"workload": f"one chain, N={n}, K={k}, 4 atoms per node, 16 RBF centres, seed {SEED}", "sharding": "rank 0 only"},
+           "roofline": {"bound": "hbm", "kernel": "edge_rbf_4x4x16_kernel", "achieved": out_bytes / (rbf_ms * 1e-3) / 1e9, "peak": peak,
+                        "unit": "GB/s", "frac": out_bytes / (rbf_ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None},
+           "gpu_launches": 2 * steps}
+    if cpu_baseline:
+        from oracle.gnn_ref import edge_rbf_ref, get_neighbors_ref
+        torch.set_num_threads(os.cpu_count() or 1)
+        ns = 2048  # the dense formulation needs N^2 memory: a bounded sample of the same chain
+        a_s = atoms_h[:, :ns]
+        t0 = time.perf_counter()
+        i_s, _ = get_neighbors_ref(a_s[:, :, 1], torch.zeros(1, ns, dtype=torch.bool), k)
+        edge_rbf_ref(a_s, i_s, centers.cpu(), spread)
+        dt = time.perf_counter() - t0
+        res["cpu_baseline"] = {"value": ns / dt, "unit": "nodes/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"first {ns} nodes of the chain as a chain of their own (dense N x N formulation), {dt:.2f} s"}
+    return res
+
+
 def cpu_port_rate(coords, wn, target_s=12.0, chunk=32):
     """Times the oracle (the reference's dense PyTorch formulation, observer-chunked) on the host
     cores on a bounded run of observer rows.  Returns (evals/s, rows used, seconds)."""
@@ -428,6 +489,7 @@ def main():
     if rank == 0:
         line["geoattn"] = ga
         line["encoder"] = enc
+        line["graph"] = bench_graph(dev, args.steps, world == 1 and not args.no_cpu_baseline) if (N_SEQ == 16384 or args.geoattn) else None
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

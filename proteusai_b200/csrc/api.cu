@@ -532,7 +532,7 @@ int pai_gelu_bf16(const void *x, void *out, long long n, void *stream) {
 int pai_knn_neighbors(const float *ca, const uint8_t *valid, int64_t *idx, uint8_t *edge_mask, int Z, int N, int K, float max_dist,
                       void *stream) {
     if (!ca || !idx || !edge_mask) return PAI_ERR_NULL_POINTER;
-    if (Z < 1 || N < 1 || K < 1 || K > N || (long long)Z * N > (1ll << 31)) return PAI_ERR_BAD_SHAPE;
+    if (Z < 1 || Z > 65535 || N < 1 || K < 1 || K > N || (long long)Z * N > (1ll << 31)) return PAI_ERR_BAD_SHAPE;
     if (K > pai::KNN_MAX_K) return PAI_ERR_UNSUPPORTED;
     if (!aligned(ca, 4) || !aligned(idx, 8)) return PAI_ERR_MISALIGNED;
     if (int e = require_sm100()) return e;
