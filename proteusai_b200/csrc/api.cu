@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
 
 extern "C" {
 
-int pai_abi_version(void) { return 3; }
+int pai_abi_version(void) { return 4; }  // 4: dropout in pai_we_fwd; strided attention forward; encoder row kernels; neighbour graph and edge features
 
 const char *pai_status_str(int status) {
     switch (status) {

@@ -202,3 +202,40 @@ def test_reference_test_configuration_with_heads_of_32(ga, form):
     with pytest.raises(RuntimeError):
         ga.geometric_attn(torch.zeros(1, 1, 8, 128).cuda(), torch.zeros(1, 1, 8, 128).cuda(), torch.zeros(1, 1, 8, 128).cuda(),
                           torch.zeros(1, 8, 3).cuda(), torch.ones(1).cuda(), None)
+
+
+@pytest.mark.parametrize("n", [1, 5, 127, 129])
+def test_tiny_and_odd_lengths_forward_backward(ga, n):
+    q, k, v, d_out, c, m, sig = _inputs(2, 2, n, [n, max(1, n // 2)], seed=900 + n, std=1.0)
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = ga.geometric_attn(qd, kd, vd, c.cuda(), sig.cuda(), None, m.cuda())
+    out.backward(d_out.cuda())
+    o_r, _, dq, dk, dv, _ = geoattn_grads_closed_form(q.float(), k.float(), v.float(), c, sig, d_out.float(), m, dtype=torch.float64)
+    assert (out.detach().float().cpu().double() - o_r).abs().max().item() < ABS_TOL
+    for got, ref in ((qd.grad, dq), (kd.grad, dk), (vd.grad, dv)):
+        assert (got.float().cpu().double() - ref).abs().max().item() < ABS_TOL + ref.abs().max().item() * 2 ** -8
+
+
+def test_masks_with_holes_and_an_empty_sample(ga):
+    """Padding masks need not be prefixes: holes inside a chain, and a sample with no valid token at all (zeros out, zero
+    gradients, no NaN anywhere)."""
+    z, h, n = 3, 2, 300
+    q, k, v, d_out, c, m, sig = _inputs(z, h, n, [300, 300, 300], seed=77, std=1.0)
+    g = torch.Generator().manual_seed(78)
+    m = torch.zeros(z, n, dtype=torch.bool)
+    m[0] = torch.rand(n, generator=g) < 0.3          # holes
+    m[1, 100:260] = True                             # a gap that swallows a whole key tile
+    m[2] = True                                      # nothing valid
+    qd, kd, vd = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    sd = sig.cuda().requires_grad_(True)
+    out = ga.geometric_attn(qd, kd, vd, c.cuda(), sd, None, m.cuda())
+    out.backward(d_out.cuda())
+    o_r, _, dq, dk, dv, dsig = geoattn_grads_closed_form(q.float(), k.float(), v.float(), c, sig, d_out.float(), m, dtype=torch.float64)
+    assert (out.detach().float().cpu().double() - o_r).abs().max().item() < ABS_TOL
+    for got, ref in ((qd.grad, dq), (kd.grad, dk), (vd.grad, dv)):
+        assert torch.isfinite(got).all()
+        assert (got.float().cpu().double() - ref).abs().max().item() < ABS_TOL + ref.abs().max().item() * 2 ** -8
+    assert torch.all(out[2] == 0) and torch.all(qd.grad[2] == 0) and torch.all(kd.grad[2] == 0) and torch.all(vd.grad[2] == 0)
+    assert torch.all((sd.grad.cpu().double() - dsig).abs() <= 2e-2 * dsig.abs() + 5e-3)
+    from proteusai_b200 import _lib
+    _lib.device_status()
