@@ -150,25 +150,42 @@ __device__ __forceinline__ float gelu_erf(float x) {
     return x * phi;
 }
 
-__global__ void __launch_bounds__(ENC_THREADS) gelu_bf16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ out, long long n8) {
-    const long long stride = (long long)gridDim.x * ENC_THREADS;
-    for (long long i = (long long)blockIdx.x * ENC_THREADS + threadIdx.x; i < n8; i += stride) {
-        float f[8];
-        bf16x8_to_float(x[i], f);
+__device__ __forceinline__ uint4 gelu_bf16x8(const uint4 &u) {
+    float f[8];
+    bf16x8_to_float(u, f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k]);
-        uint4 pk;
-        pk.x = float2_to_bf16x2(f[0], f[1]);
-        pk.y = float2_to_bf16x2(f[2], f[3]);
-        pk.z = float2_to_bf16x2(f[4], f[5]);
-        pk.w = float2_to_bf16x2(f[6], f[7]);
-        out[i] = pk;
+    for (int k = 0; k < 8; ++k) f[k] = gelu_erf(f[k]);
+    uint4 pk;
+    pk.x = float2_to_bf16x2(f[0], f[1]);
+    pk.y = float2_to_bf16x2(f[2], f[3]);
+    pk.z = float2_to_bf16x2(f[4], f[5]);
+    pk.w = float2_to_bf16x2(f[6], f[7]);
+    return pk;
+}
+
+// Four independent 16-byte loads per thread and step: a B200 needs several MB of loads in flight to cover the HBM
+// latency at full bandwidth, more than one load per resident thread provides.
+__global__ void __launch_bounds__(ENC_THREADS) gelu_bf16_kernel(const uint4 *__restrict__ x, uint4 *__restrict__ out, long long n8) {
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * ENC_THREADS * U;
+    for (long long i0 = (long long)blockIdx.x * ENC_THREADS * U + threadIdx.x; i0 < n8; i0 += stride) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = i0 + (long long)u * ENC_THREADS;
+            if (i < n8) v[u] = x[i];
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const long long i = i0 + (long long)u * ENC_THREADS;
+            if (i < n8) out[i] = gelu_bf16x8(v[u]);
+        }
     }
 }
 
 static int gelu_bf16_launch(const void *x, void *out, long long n, int sms, cudaStream_t stream) {
     const long long n8 = n / 8;
-    long long blocks = (n8 + ENC_THREADS - 1) / ENC_THREADS;
+    long long blocks = (n8 + ENC_THREADS * 4 - 1) / (ENC_THREADS * 4);  // four 16-byte words per thread and step
     const long long cap = (long long)sms * 8 * 4;  // 8 resident CTAs per SM, a few waves
     if (blocks > cap) blocks = cap;
     gelu_bf16_kernel<<<(unsigned)blocks, ENC_THREADS, 0, stream>>>((const uint4 *)x, (uint4 *)out, n8);
