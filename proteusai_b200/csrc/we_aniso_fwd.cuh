@@ -80,7 +80,11 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
     bool row_in = false, ov = false, item_live = false;
     float ox = 0.f, oy = 0.f, oz = 0.f;
     f2_t kk[KP], ss[KP];                                            // wavenumbers, negated C-beta magnitudes
-    f2_t a_re[KP], a_im[KP], a_sr[KP], a_si[KP], a_kr[KP], a_ki[KP];  // out, d/ds, d/dk (real, imaginary)
+    // Sums over the sources of cos / r, sin / r (the output), sin b / r, cos b / r and plain sin, cos, with b = R/r . B_j.
+    // The two derivative rows follow from them at the flush, because the factors that depend on the wavenumber slot
+    // leave the sums: sum k b sin / r = k sum b sin / r, and (r - s b) / r = 1 - s b / r.  That keeps the inner loop at
+    // six accumulations with per-pair scalars only.
+    f2_t a_re[KP], a_im[KP], a_sr[KP], a_si[KP], a_kr[KP], a_ki[KP];
 #pragma unroll
     for (int q = 0; q < KP; ++q) kk[q] = ss[q] = a_re[q] = a_im[q] = a_sr[q] = a_si[q] = a_kr[q] = a_ki[q] = 0ull;
 
@@ -94,10 +98,11 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
             float v[6][2];
             f2_unpack(a_re[q], v[0][0], v[0][1]);
             f2_unpack(a_im[q], v[1][0], v[1][1]);
-            f2_unpack(a_sr[q], v[2][0], v[2][1]);
-            f2_unpack(a_si[q], v[3][0], v[3][1]);
-            f2_unpack(a_kr[q], v[4][0], v[4][1]);
-            f2_unpack(a_ki[q], v[5][0], v[5][1]);
+            // sum k b sin / r, sum k b cos / r;  sum (1 - s b / r) sin, sum (1 - s b / r) cos   (ss holds -s)
+            f2_unpack(f2_mul(kk[q], a_sr[q]), v[2][0], v[2][1]);
+            f2_unpack(f2_mul(kk[q], a_si[q]), v[3][0], v[3][1]);
+            f2_unpack(f2_fma(ss[q], a_sr[q], a_kr[q]), v[4][0], v[4][1]);
+            f2_unpack(f2_fma(ss[q], a_si[q], a_ki[q]), v[5][0], v[5][1]);
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 if (k + e >= K) break;
@@ -213,7 +218,9 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
             r = fmaf(0.5f * inv, fmaf(-r, r, d2), r);
             const float binv = (dx * bj.x + dy * bj.y + dz * bj.z) * inv * inv;  // (R/r . B_j) / r
             const float b = binv * r;                                              // R/r . B_j
-            const f2_t r2 = f2_pack(r, r), b2 = f2_pack(b, b), inv2 = f2_pack(inv, inv), binv2 = f2_pack(binv, binv);
+            const float one = m ? 1.f : 0.f;
+            const f2_t r2 = f2_pack(r, r), b2 = f2_pack(b, b), inv2 = f2_pack(inv, inv), binv2 = f2_pack(binv, binv),
+                       one2 = f2_pack(one, one);
 #pragma unroll
             for (int q = 0; q < KP; ++q) {
                 const f2_t w2 = f2_fma(ss[q], b2, r2);  // r - s_k b
@@ -222,14 +229,12 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
                 sfu_sincos(pa, sa, ca2);
                 sfu_sincos(pb, sb, cb2);
                 const f2_t c2 = f2_pack(ca2, cb2), s2 = f2_pack(sa, sb);
-                const f2_t kb2 = f2_mul(kk[q], binv2);  // k b / r
-                const f2_t wr2 = f2_mul(w2, inv2);      // (r - s_k b) / r
                 a_re[q] = f2_fma(c2, inv2, a_re[q]);
                 a_im[q] = f2_fma(s2, inv2, a_im[q]);
-                a_sr[q] = f2_fma(s2, kb2, a_sr[q]);
-                a_si[q] = f2_fma(c2, kb2, a_si[q]);
-                a_kr[q] = f2_fma(s2, wr2, a_kr[q]);
-                a_ki[q] = f2_fma(c2, wr2, a_ki[q]);
+                a_sr[q] = f2_fma(s2, binv2, a_sr[q]);
+                a_si[q] = f2_fma(c2, binv2, a_si[q]);
+                a_kr[q] = f2_fma(s2, one2, a_kr[q]);
+                a_ki[q] = f2_fma(c2, one2, a_ki[q]);
             }
         }
     }
