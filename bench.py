@@ -179,7 +179,7 @@ def bench_geoattn(dev, world, rank, steps, dist):
 EN_Z, EN_N, EN_SEED = 64, 1024, 1005
 
 
-def bench_encoder(dev, world, rank, steps, dist):
+def bench_encoder(dev, world, rank, steps, dist, graphed=False):
     """Encoder inference (bf16, random weights): token embedding (vocabulary 33 -> 512) + wavefunction embedding, 4 post-norm
     layers of geometric attention (H=8, sigma 3..15 A) and a 2048-wide GELU FFN, linear head to 20 logits.  64 chains with
     lengths uniform in 64..1024 padded to 1024, data-parallel: each rank takes a contiguous slice of the batch.  Returns
@@ -221,10 +221,45 @@ def bench_encoder(dev, world, rank, steps, dist):
         total = float(t.item())
     ms = total / steps
     valid_tokens = int(lengths.sum())
-    return {"metric": "encoder inference tokens/s (valid tokens, host inputs and outputs included)", "value": valid_tokens / (ms * 1e-3),
-            "unit": "tokens/s", "padded_tokens_per_s": EN_Z * EN_N / (ms * 1e-3), "ms_per_step": ms, "dtype": "bf16",
-            "config": {"workload": "4-layer geometric-attention encoder, d_model 512, H 8, FFN 2048, 64 chains of 64..1024 padded to 1024, seed 1005",
-                       "sharding": f"batch over {world} rank(s), no collective"}}
+    res = {"metric": "encoder inference tokens/s (valid tokens, host inputs and outputs included)", "value": valid_tokens / (ms * 1e-3),
+           "unit": "tokens/s", "padded_tokens_per_s": EN_Z * EN_N / (ms * 1e-3), "ms_per_step": ms, "dtype": "bf16",
+           "config": {"workload": "4-layer geometric-attention encoder, d_model 512, H 8, FFN 2048, 64 chains of 64..1024 padded to 1024, seed 1005",
+                      "sharding": f"batch over {world} rank(s), no collective"}}
+    if graphed:
+        # The same forward captured once into a CUDA graph and replayed: inputs are copied into static device buffers,
+        # the graph runs, the logits are copied out.  Removes the host's per-kernel launch work from the step.
+        c_s, m_s, t_s = (x.to(dev) for x in (coords_p, mask_p, tokens_p))
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(3):
+                model(t_s, c_s, m_s)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph), torch.no_grad():
+            logits_s = model(t_s, c_s, m_s)
+
+        def step_graph():
+            c_s.copy_(coords_p, non_blocking=True)
+            m_s.copy_(mask_p, non_blocking=True)
+            t_s.copy_(tokens_p, non_blocking=True)
+            graph.replay()
+            out_host.copy_(logits_s, non_blocking=True)
+
+        ref_logits = out_host.clone()
+        for _ in range(3):
+            step_graph()
+        torch.cuda.synchronize()
+        same = bool(torch.equal(ref_logits, out_host))
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step_graph()
+        b.record()
+        torch.cuda.synchronize()
+        res["cuda_graph"] = {"ms_per_step": a.elapsed_time(b) / steps, "logits_equal_eager": same}
+    return res
 
 
 def bench_graph(dev, steps, cpu_baseline):
@@ -351,6 +386,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--geoattn", action="store_true", help="also run the attention leg when --n-seq is not the default")
+    ap.add_argument("--graph-encoder", action="store_true",
+                    help="also time the encoder leg with its forward captured in a CUDA graph (off by default)")
     ap.add_argument("--n-seq", type=int, default=N_SEQ, help="sequence length (default: the headline 16384)")
     args = ap.parse_args()
     if args.n_seq != N_SEQ:
@@ -485,7 +522,7 @@ def main():
         ga = bench_geoattn(dev, world, rank, args.steps, dist)
     enc = None
     if N_SEQ == 16384 or args.geoattn:
-        enc = bench_encoder(dev, world, rank, args.steps, dist)
+        enc = bench_encoder(dev, world, rank, args.steps, dist, graphed=args.graph_encoder)
     if rank == 0:
         line["geoattn"] = ga
         line["encoder"] = enc

@@ -100,3 +100,16 @@ def test_long_chain_properties(gnn):
     # first sample of a dense oracle at N = 2048 cover the same code path (test_against_oracle)
     from proteusai_b200 import _lib
     _lib.device_status()
+
+
+def test_randomised_point_clouds(gnn):
+    """Thirty seeded random clouds (no chain structure, random masks with holes, K up to 64): indices and masks exact."""
+    rng = np.random.default_rng(777)
+    for case in range(30):
+        z, n = int(rng.integers(1, 4)), int(rng.integers(2, 400))
+        k = int(rng.integers(1, min(n, 64) + 1))
+        ca = torch.from_numpy((rng.normal(size=(z, n, 3)) * rng.uniform(3, 25)).astype(np.float32))
+        mask = torch.from_numpy(rng.random((z, n)) < rng.uniform(0, 0.5))
+        idx_ref, em_ref = get_neighbors_ref(ca, mask, k)
+        idx, em = gnn.knn_neighbors(ca.cuda(), mask.cuda(), k)
+        _same_graph(ca, idx.cpu(), em.cpu(), idx_ref, em_ref)

@@ -235,3 +235,28 @@ def test_dropout_through_the_autograd_function(we):
     assert torch.isfinite(wn.grad).all()
     with pytest.raises(RuntimeError):
         we.we_forward_rows(torch.from_numpy(c).cuda(), wn.detach(), 1, None, dropout_p=1.0)
+
+
+def test_randomised_shapes_masks_and_row_ranges(we):
+    """Forty seeded random cases: batch, length, wavenumber count, magnitude type, masks with holes, observer row range."""
+    rng = np.random.default_rng(424242)
+    for case in range(40):
+        z, n, k = int(rng.integers(1, 4)), int(rng.integers(1, 260)), int(rng.integers(1, 41))
+        mag = int(rng.integers(0, 4))
+        coords = torch.from_numpy((rng.normal(size=(z, n, 3)) * rng.uniform(2, 30)).astype(np.float32))
+        wn = torch.from_numpy(rng.uniform(0.05, 2.0, size=k).astype(np.float32))
+        mask = torch.from_numpy(rng.random((z, n)) < rng.uniform(0, 0.6))
+        r0 = int(rng.integers(0, n))
+        r1 = int(rng.integers(r0, n + 1))
+        out, cs, sn = we.we_forward_rows(coords.cuda(), wn.cuda(), mag, mask.cuda(), r0, r1)
+        if r1 == r0:
+            continue
+        ref, cs_r, sn_r = wf_embedding_ref(coords, wn, mag, mask, rows=(r0, r1), dtype=torch.float64, return_sums=True)
+        got = out[:, r0:r1].cpu().double()
+        scale = max(ref.abs().max().item(), 1e-30)
+        assert (got - ref).abs().max().item() <= 1e-4 * scale + 1e-6, (case, z, n, k, mag, r0, r1)
+        assert (cs[:, r0:r1].cpu().double() - cs_r).abs().max().item() <= 1e-4 * max(cs_r.abs().max().item(), 1e-30) + 1e-6, case
+        assert (sn[:, r0:r1].cpu().double() - sn_r).abs().max().item() <= 1e-4 * max(sn_r.abs().max().item(), 1e-30) + 1e-6, case
+        assert torch.all(out[:, r0:r1][mask[:, r0:r1].cuda()] == 0), case
+    from proteusai_b200 import _lib
+    _lib.device_status()
