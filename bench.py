@@ -295,6 +295,8 @@ def bench_graph(dev, steps, cpu_baseline):
     idx, _ = knn_neighbors(ca, None, k)
     knn_ms = timed_ms(lambda: knn_neighbors(ca, None, k))
     rbf_ms = timed_ms(lambda: edge_rbf(atoms, idx, centers, spread))  # 503 MB written per call: larger than L2
+    ln = torch.nn.LayerNorm(256).to(dev)
+    rbf_ln_ms = timed_ms(lambda: edge_rbf(atoms, idx, centers, spread, norm=ln))  # with the edge LayerNorm fused in
     edges = n * k
     out_bytes = edges * 256 * 4
     hbm = None
@@ -304,7 +306,7 @@ def bench_graph(dev, steps, cpu_baseline):
         pass
     peak, src = (hbm, "measured (MEASURED_PEAKS.json, copy bandwidth)") if hbm else (6650.0, "fallback")
     res = {"metric": "graph featurisation nodes/s (K nearest + edge RBFs)", "value": n / ((knn_ms + rbf_ms) * 1e-3), "unit": "nodes/s",
-           "knn_ms": knn_ms, "edge_rbf_ms": rbf_ms, "dtype": "f32",
+           "knn_ms": knn_ms, "edge_rbf_ms": rbf_ms, "edge_rbf_layernorm_ms": rbf_ln_ms, "dtype": "f32",
            "config": {"workload": f"one chain, N={n}, K={k}, 4 atoms per node, 16 RBF centres, seed {SEED}", "sharding": "rank 0 only"},
            "roofline": {"bound": "hbm", "kernel": "edge_rbf_4x4x16_kernel", "achieved": out_bytes / (rbf_ms * 1e-3) / 1e9, "peak": peak,
                         "unit": "GB/s", "frac": out_bytes / (rbf_ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None},

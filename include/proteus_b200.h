@@ -261,10 +261,14 @@ int pai_gelu_bf16(const void *x, void *out, long long n, void *stream);
  *   idx       [Z,N,K]   i64   neighbour indices (within the batch element), e.g. from pai_knn_neighbors
  *   centers   [R]       fp32  RBF centres; spread as the reference's Python float
  *   out       [Z,N,K,A*A*R] fp32  out[..., (a*A + b)*R + r] = exp(-(|atoms[z,i,a] - atoms[z,idx,b]| - centers[r])^2 / spread^2)
+ *   ln_gamma, ln_beta [A*A*R] fp32, ln_eps   optional (both NULL = off): the LayerNorm over the features of each edge that
+ *                             follows in the reference (`edge_norm`, gnn.py:134) applied before the store, so the features
+ *                             cross HBM once; available for A = 4, R = 16 (PAI_ERR_UNSUPPORTED otherwise).
  */
 int pai_knn_neighbors(const float *ca, const uint8_t *valid, int64_t *idx, uint8_t *edge_mask,
                       int Z, int N, int K, float max_dist, void *stream);
-int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread, float *out,
+int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread,
+                 const float *ln_gamma, const float *ln_beta, float ln_eps, float *out,
                  int Z, int N, int K, int A, int R, void *stream);
 
 /* ---------------------------------------------------------------------------------------

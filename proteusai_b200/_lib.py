@@ -37,7 +37,8 @@ SIGNATURES = {
     "pai_add_layernorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p]),
     "pai_gelu_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_void_p]),
     "pai_knn_neighbors": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
-    "pai_edge_rbf": (c_int, [c_void_p, c_void_p, c_void_p, c_double, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "pai_edge_rbf": (c_int, [c_void_p, c_void_p, c_void_p, c_double, c_void_p, c_void_p, c_float, c_void_p,
+                             c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_measure_sfu_peak": (c_int, [ctypes.POINTER(c_double), ctypes.POINTER(c_double)]),
 }
 

@@ -540,15 +540,19 @@ int pai_knn_neighbors(const float *ca, const uint8_t *valid, int64_t *idx, uint8
     return pai::knn_launch(ca, valid, (long long *)idx, edge_mask, Z, N, K, max_dist, (cudaStream_t)stream);
 }
 
-int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread, float *out, int Z, int N, int K, int A,
-                 int R, void *stream) {
+int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, double spread, const float *ln_gamma,
+                 const float *ln_beta, float ln_eps, float *out, int Z, int N, int K, int A, int R, void *stream) {
     if (!atoms || !idx || !centers || !out) return PAI_ERR_NULL_POINTER;
-    if (Z < 1 || N < 1 || K < 1 || A < 1 || R < 1 || A > 64 || R > 4096 || !(spread > 0.0)) return PAI_ERR_BAD_SHAPE;
+    if ((ln_gamma == nullptr) != (ln_beta == nullptr)) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || N < 1 || K < 1 || A < 1 || R < 1 || A > 64 || R > 4096 || !(spread > 0.0) || !(ln_eps >= 0.f)) return PAI_ERR_BAD_SHAPE;
+    if (ln_gamma && !(A == 4 && R == 16)) return PAI_ERR_UNSUPPORTED;
     if (!aligned(atoms, 4) || !aligned(idx, 8) || !aligned(centers, 4) || !aligned(out, 16)) return PAI_ERR_MISALIGNED;
+    if (ln_gamma && (!aligned(ln_gamma, 16) || !aligned(ln_beta, 16))) return PAI_ERR_MISALIGNED;
     if (int e = require_sm100()) return e;
     int sms = 0;
     if (int e = current_device_sms(&sms)) return e;
-    return pai::edge_rbf_launch(atoms, (const long long *)idx, centers, spread, out, Z, N, K, A, R, sms, (cudaStream_t)stream);
+    return pai::edge_rbf_launch(atoms, (const long long *)idx, centers, spread, ln_gamma, ln_beta, ln_eps, out, Z, N, K, A, R, sms,
+                                (cudaStream_t)stream);
 }
 
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {

@@ -218,10 +218,15 @@ __device__ __forceinline__ float ex2_fast(float x) {
 
 // out[z,i,k,a,b,r] = exp(-(|atoms[z,i,a] - atoms[z,idx[z,i,k],b]| - centers[r])^2 / spread^2), A = 4 atoms per node and
 // R = 16 centres (gnn.py:119-131): 256 values per edge, one warp per edge.
+// LN: the LayerNorm over the 256 features of an edge that follows in the reference (edge_norm, gnn.py:134) is applied
+// before the store -- the warp holds the whole feature row, so mean and variance are two shuffle reductions and the
+// features cross HBM once instead of three times (written, read and written again by a separate LayerNorm).
+template <bool LN>
 __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const float *__restrict__ atoms, const long long *__restrict__ idx,
                                                                      const float *__restrict__ centers,
-                                                                     float neg_log2e_over_spread2, float *__restrict__ out, int N,
-                                                                     int K, long long edges) {
+                                                                     float neg_log2e_over_spread2, const float *__restrict__ gamma,
+                                                                     const float *__restrict__ beta, float eps,
+                                                                     float *__restrict__ out, int N, int K, long long edges) {
     const int lane = threadIdx.x & 31;
     // Lane l computes the distance of atom pair l / 2 (a = l / 8, b = (l / 2) % 4; the two lanes of a pair compute the
     // same value).  It writes features 4 l .. 4 l + 3 (pair l / 4, centres 4 (l % 4) ..) and 128 + 4 l .. (pair 8 + l / 4),
@@ -231,6 +236,13 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const floa
     float c[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) c[q] = centers[r0 + q];
+    float4 g_lo = make_float4(1.f, 1.f, 1.f, 1.f), g_hi = g_lo, b_lo = make_float4(0.f, 0.f, 0.f, 0.f), b_hi = b_lo;
+    if (LN) {
+        g_lo = reinterpret_cast<const float4 *>(gamma)[lane];
+        g_hi = reinterpret_cast<const float4 *>(gamma)[32 + lane];
+        b_lo = reinterpret_cast<const float4 *>(beta)[lane];
+        b_hi = reinterpret_cast<const float4 *>(beta)[32 + lane];
+    }
     const long long warps = (long long)gridDim.x * (KNN_THREADS / 32);
     for (long long e = (long long)blockIdx.x * (KNN_THREADS / 32) + (threadIdx.x >> 5); e < edges; e += warps) {
         const long long node = e / K;          // z * N + i
@@ -246,6 +258,29 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const floa
             const float t0 = d_lo - c[q], t1 = d_hi - c[q];
             v[q] = ex2_fast(t0 * t0 * neg_log2e_over_spread2);
             v[4 + q] = ex2_fast(t1 * t1 * neg_log2e_over_spread2);
+        }
+        if (LN) {  // biased variance of the centred values, eps inside the square root, as nn.LayerNorm
+            float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float mean = sum * (1.f / 256.f);
+            float sq = 0.f;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                v[q] -= mean;
+                sq = fmaf(v[q], v[q], sq);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            const float rstd = rsqrtf(sq * (1.f / 256.f) + eps);
+            v[0] = fmaf(v[0] * rstd, g_lo.x, b_lo.x);
+            v[1] = fmaf(v[1] * rstd, g_lo.y, b_lo.y);
+            v[2] = fmaf(v[2] * rstd, g_lo.z, b_lo.z);
+            v[3] = fmaf(v[3] * rstd, g_lo.w, b_lo.w);
+            v[4] = fmaf(v[4] * rstd, g_hi.x, b_hi.x);
+            v[5] = fmaf(v[5] * rstd, g_hi.y, b_hi.y);
+            v[6] = fmaf(v[6] * rstd, g_hi.z, b_hi.z);
+            v[7] = fmaf(v[7] * rstd, g_hi.w, b_hi.w);
         }
         float4 *o = reinterpret_cast<float4 *>(out + e * 256);
         o[lane] = make_float4(v[0], v[1], v[2], v[3]);
@@ -274,8 +309,9 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_generic_kernel(const flo
     }
 }
 
-static int edge_rbf_launch(const float *atoms, const long long *idx, const float *centers, double spread, float *out, int Z, int N,
-                           int K, int A, int R, int sms, cudaStream_t stream) {
+static int edge_rbf_launch(const float *atoms, const long long *idx, const float *centers, double spread, const float *gamma,
+                           const float *beta, float eps, float *out, int Z, int N, int K, int A, int R, int sms,
+                           cudaStream_t stream) {
     const long long edges = (long long)Z * N * K;
     // exp(-t^2 / spread^2) = 2^(t^2 * (-log2 e / spread^2)): one multiply and one SFU operation per value.  Against the
     // reference's fp32 division and exp this moves a value by at most ~1e-7 absolute (argument error <= 2 ulp, times
@@ -285,8 +321,14 @@ static int edge_rbf_launch(const float *atoms, const long long *idx, const float
     if (A == 4 && R == 16) {
         long long blocks = (edges + KNN_THREADS / 32 - 1) / (KNN_THREADS / 32);
         if (blocks > cap) blocks = cap;
-        edge_rbf_4x4x16_kernel<<<(unsigned)blocks, KNN_THREADS, 0, stream>>>(atoms, idx, centers, spread2, out, N, K, edges);
+        if (gamma)
+            edge_rbf_4x4x16_kernel<true><<<(unsigned)blocks, KNN_THREADS, 0, stream>>>(atoms, idx, centers, spread2, gamma, beta, eps,
+                                                                                        out, N, K, edges);
+        else
+            edge_rbf_4x4x16_kernel<false><<<(unsigned)blocks, KNN_THREADS, 0, stream>>>(atoms, idx, centers, spread2, nullptr, nullptr,
+                                                                                         0.f, out, N, K, edges);
     } else {
+        if (gamma) return (int)PAI_ERR_UNSUPPORTED;  // the fused LayerNorm exists for the 4 x 4 x 16 layout only
         const long long total = edges * A * A * R;
         long long blocks = (total + KNN_THREADS - 1) / KNN_THREADS;
         if (blocks > cap) blocks = cap;

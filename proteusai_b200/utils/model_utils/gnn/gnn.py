@@ -31,9 +31,10 @@ def knn_neighbors(Ca, node_mask, k, max_dist=12.0):
     return idx, edge_mask
 
 
-def edge_rbf(C, K, rbf_centers, spread):
+def edge_rbf(C, K, rbf_centers, spread, norm=None):
     """``[Z,N,K,A*A*R]`` radial-basis features of the distances between the ``A`` atoms of every node ``C [Z,N,A,3]``
-    and the atoms of its neighbours ``K [Z,N,K]``."""
+    and the atoms of its neighbours ``K [Z,N,K]``.  ``norm`` (an ``nn.LayerNorm`` over the features, fp32, A = 4 and
+    R = 16) is applied inside the kernel, before the features are written."""
     if not C.is_cuda:
         raise RuntimeError("edge_rbf needs CUDA tensors: there is no CPU path")
     z, n, a, s = C.shape
@@ -44,9 +45,16 @@ def edge_rbf(C, K, rbf_centers, spread):
     centers = rbf_centers.detach().to(torch.float32).contiguous()
     r = centers.numel()
     out = torch.empty(z, n, k, a * a * r, dtype=torch.float32, device=C.device)
+    gamma = beta = None
+    eps = 0.0
+    if norm is not None:
+        gamma = norm.weight.detach().to(torch.float32).contiguous()
+        beta = norm.bias.detach().to(torch.float32).contiguous()
+        eps = norm.eps
     with torch.cuda.device(C.device):
-        _lib.check(_lib.lib().pai_edge_rbf(_lib.ptr(atoms), _lib.ptr(idx), _lib.ptr(centers), float(spread), _lib.ptr(out), z, n, k,
-                                           a, r, _lib.current_stream()), "pai_edge_rbf")
+        _lib.check(_lib.lib().pai_edge_rbf(_lib.ptr(atoms), _lib.ptr(idx), _lib.ptr(centers), float(spread), _lib.ptr(gamma),
+                                           _lib.ptr(beta), float(eps), _lib.ptr(out), z, n, k, a, r, _lib.current_stream()),
+                   "pai_edge_rbf")
     return out
 
 
@@ -66,6 +74,11 @@ class EdgeFeaturizer(nn.Module):
         return knn_neighbors(Ca, node_mask, self.K)
 
     def get_edges(self, C, K):
+        # without gradients to record, the LayerNorm runs inside the feature kernel (4 x 4 x 16 features, fp32 parameters)
+        fused = (not (torch.is_grad_enabled() and any(p.requires_grad for p in self.edge_norm.parameters()))
+                 and C.shape[2] == 4 and self.rbf_centers.numel() == 16 and self.edge_norm.weight.dtype == torch.float32)
+        if fused:
+            return self.edge_proj(edge_rbf(C, K, self.rbf_centers, self.spread, norm=self.edge_norm))
         E = edge_rbf(C, K, self.rbf_centers, self.spread)  # Z x N x K x (4*4*num_rbfs)
         return self.edge_proj(self.edge_norm(E))           # Z x N x K x De
 

@@ -152,6 +152,8 @@ def test_neighbour_and_edge_argument_errors(lib):
     assert f(p, None, p, p, 1, 128, 65, 12.0, None) == -4    # at most 64 neighbours
     assert f(p, None, ctypes.c_void_p(0x1004), p, 1, 64, 30, 12.0, None) == -3
     g = lib.pai_edge_rbf
-    assert g(p, p, None, 1.25, p, 1, 64, 30, 4, 16, None) == -1
-    assert g(p, p, p, 0.0, p, 1, 64, 30, 4, 16, None) == -2
-    assert g(p, p, p, 1.25, ctypes.c_void_p(0x1008), 1, 64, 30, 4, 16, None) == -3
+    assert g(p, p, None, 1.25, None, None, 0.0, p, 1, 64, 30, 4, 16, None) == -1
+    assert g(p, p, p, 0.0, None, None, 0.0, p, 1, 64, 30, 4, 16, None) == -2
+    assert g(p, p, p, 1.25, None, None, 0.0, ctypes.c_void_p(0x1008), 1, 64, 30, 4, 16, None) == -3
+    assert g(p, p, p, 1.25, p, None, 1e-5, p, 1, 64, 30, 4, 16, None) == -1      # gamma without beta
+    assert g(p, p, p, 1.25, p, p, 1e-5, p, 1, 64, 30, 3, 16, None) == -4         # fused LayerNorm: 4 x 4 x 16 only

@@ -80,6 +80,18 @@ def test_edge_features_generic_shapes_and_module(gnn):
     e_ref = torch.nn.functional.linear(torch.nn.functional.layer_norm(feats, (256,), mod.edge_norm.weight.cpu(), mod.edge_norm.bias.cpu()),
                                        mod.edge_proj.weight.cpu(), mod.edge_proj.bias.cpu())
     assert E.shape == (2, 80, 16, 32) and (E.detach().cpu() - e_ref.detach()).abs().max().item() < 1e-3
+    # the same with the LayerNorm inside the feature kernel (no gradients recorded), and the normalised features themselves
+    with torch.no_grad():
+        torch.nn.init.normal_(mod.edge_norm.weight)
+        torch.nn.init.normal_(mod.edge_norm.bias)
+        E2 = mod.get_edges(a4.cuda(), k_ref.cuda())
+        normed = gnn.edge_rbf(a4.cuda(), k_ref.cuda(), mod.rbf_centers, mod.spread, norm=mod.edge_norm)
+    n_ref = torch.nn.functional.layer_norm(feats, (256,), mod.edge_norm.weight.detach().cpu(), mod.edge_norm.bias.detach().cpu(), mod.edge_norm.eps)
+    assert (normed.cpu() - n_ref).abs().max().item() < 2e-5 * max(1.0, n_ref.abs().max().item())
+    e2_ref = torch.nn.functional.linear(n_ref, mod.edge_proj.weight.detach().cpu(), mod.edge_proj.bias.detach().cpu())
+    assert (E2.cpu() - e2_ref).abs().max().item() < 2e-3
+    with pytest.raises(RuntimeError):  # the fused LayerNorm exists for 4 atoms x 16 centres only
+        gnn.edge_rbf(atoms.cuda(), idx.cuda(), centers.cuda(), 0.7, norm=torch.nn.LayerNorm(45).cuda())
 
 
 def test_long_chain_properties(gnn):
