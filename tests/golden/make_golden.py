@@ -238,4 +238,6 @@ def main(ref_root, only=None):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", sys.argv[2] if len(sys.argv) > 2 else None)
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference [gnn]")
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) > 2 else None)
