@@ -376,6 +376,13 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
     }
     const long long slots = resident * waves;
     p.nruns = (int)(p.units < slots ? p.units : slots);
+    // Runs of equal length: with, say, 1.7 units per run half the runs would be twice as long as the others and the
+    // last wave of CTAs ragged; rounding the length up to a whole number of units keeps them alike (a row shard of
+    // 2048 of 16384 observers, 1.73 units per run before: 4.03 -> 3.91 ms).
+    if (!p.valid && p.nruns > 0) {
+        const long long len = (p.units + p.nruns - 1) / p.nruns;
+        p.nruns = (int)((p.units + len - 1) / len);
+    }
     // Without a mask every run costs the same and one CTA per run, placed by the hardware, is the faster
     // form (30.3 against 30.7 ms at N = 16384); with a mask the runs are very unequal and resident CTAs
     // draw them from the counter instead.
