@@ -259,6 +259,10 @@ static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, unsigned *counte
     p.units = items * p.tiles;
     const long long slots = resident * (p.valid ? 2 * WE_MAX_WAVES : WE_MAX_WAVES);  // unequal runs: more, shorter ones
     p.nruns = (int)(p.units < slots ? p.units : slots);
+    if (!p.valid && p.nruns > 0) {  // runs of equal length (a whole number of units), as in the isotropic launcher
+        const long long len = (p.units + p.nruns - 1) / p.nruns;
+        p.nruns = (int)((p.units + len - 1) / len);
+    }
     p.counter = p.valid ? counter : nullptr;
     unsigned grid = (unsigned)p.nruns;
     if (p.counter) {
