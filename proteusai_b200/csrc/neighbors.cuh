@@ -222,7 +222,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
 // before the store -- the warp holds the whole feature row, so mean and variance are two shuffle reductions and the
 // features cross HBM once instead of three times (written, read and written again by a separate LayerNorm).
 template <bool LN>
-__global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const float *__restrict__ atoms, const long long *__restrict__ idx,
+__global__ void __launch_bounds__(KNN_THREADS, 8) edge_rbf_4x4x16_kernel(const float *__restrict__ atoms, const long long *__restrict__ idx,
                                                                      const float *__restrict__ centers,
                                                                      float neg_log2e_over_spread2, const float *__restrict__ gamma,
                                                                      const float *__restrict__ beta, float eps,
@@ -236,20 +236,24 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const floa
     float c[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) c[q] = centers[r0 + q];
-    float4 g_lo = make_float4(1.f, 1.f, 1.f, 1.f), g_hi = g_lo, b_lo = make_float4(0.f, 0.f, 0.f, 0.f), b_hi = b_lo;
+    // LayerNorm parameters in shared memory (kept out of the registers: 8 CTAs per SM need 32 registers per thread)
+    __shared__ float4 s_gamma[64], s_beta[64];
     if (LN) {
-        g_lo = reinterpret_cast<const float4 *>(gamma)[lane];
-        g_hi = reinterpret_cast<const float4 *>(gamma)[32 + lane];
-        b_lo = reinterpret_cast<const float4 *>(beta)[lane];
-        b_hi = reinterpret_cast<const float4 *>(beta)[32 + lane];
+        if (threadIdx.x < 64) {
+            s_gamma[threadIdx.x] = reinterpret_cast<const float4 *>(gamma)[threadIdx.x];
+            s_beta[threadIdx.x] = reinterpret_cast<const float4 *>(beta)[threadIdx.x];
+        }
+        __syncthreads();
     }
-    const long long warps = (long long)gridDim.x * (KNN_THREADS / 32);
-    for (long long e = (long long)blockIdx.x * (KNN_THREADS / 32) + (threadIdx.x >> 5); e < edges; e += warps) {
-        const long long node = e / K;          // z * N + i
-        const long long zbase = (node / N) * N;  // z * N
-        const long long nb = zbase + idx[e];
-        const float *pi = atoms + (node * 4 + a) * 3;
-        const float *pj = atoms + (nb * 4 + b) * 3;
+    // 32-bit index arithmetic (the launcher guarantees edges < 2^31): 64-bit divisions cost dozens of instructions each
+    const unsigned warps = gridDim.x * (KNN_THREADS / 32);
+    const unsigned n_edges = (unsigned)edges, uK = (unsigned)K, uN = (unsigned)N;
+    for (unsigned e = blockIdx.x * (KNN_THREADS / 32) + (threadIdx.x >> 5); e < n_edges; e += warps) {
+        const unsigned node = e / uK;            // z * N + i
+        const unsigned zbase = (node / uN) * uN;  // z * N
+        const long long nb = (long long)zbase + idx[e];
+        const float *pi = atoms + ((size_t)node * 4 + a) * 3;
+        const float *pj = atoms + ((size_t)nb * 4 + b) * 3;
         const float d = ref_distance(pi[0], pi[1], pi[2], pj[0], pj[1], pj[2]);
         const float d_lo = __shfl_sync(0xffffffffu, d, src_lo), d_hi = __shfl_sync(0xffffffffu, d, src_hi);
         float v[8];
@@ -273,6 +277,7 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const floa
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
             const float rstd = rsqrtf(sq * (1.f / 256.f) + eps);
+            const float4 g_lo = s_gamma[lane], g_hi = s_gamma[32 + lane], b_lo = s_beta[lane], b_hi = s_beta[32 + lane];
             v[0] = fmaf(v[0] * rstd, g_lo.x, b_lo.x);
             v[1] = fmaf(v[1] * rstd, g_lo.y, b_lo.y);
             v[2] = fmaf(v[2] * rstd, g_lo.z, b_lo.z);
@@ -282,7 +287,7 @@ __global__ void __launch_bounds__(KNN_THREADS) edge_rbf_4x4x16_kernel(const floa
             v[6] = fmaf(v[6] * rstd, g_hi.z, b_hi.z);
             v[7] = fmaf(v[7] * rstd, g_hi.w, b_hi.w);
         }
-        float4 *o = reinterpret_cast<float4 *>(out + e * 256);
+        float4 *o = reinterpret_cast<float4 *>(out + (size_t)e * 256);
         o[lane] = make_float4(v[0], v[1], v[2], v[3]);
         o[32 + lane] = make_float4(v[4], v[5], v[6], v[7]);
     }
@@ -318,7 +323,7 @@ static int edge_rbf_launch(const float *atoms, const long long *idx, const float
     // arg * exp(-arg) <= 0.37), far inside the 1e-6 the features are compared at.
     const float spread2 = (float)(-1.4426950408889634 / (spread * spread));
     const long long cap = (long long)sms * 8 * 8;
-    if (A == 4 && R == 16) {
+    if (A == 4 && R == 16 && edges < (1ll << 31)) {  // (32-bit edge counter with room for the grid stride)
         long long blocks = (edges + KNN_THREADS / 32 - 1) / (KNN_THREADS / 32);
         if (blocks > cap) blocks = cap;
         if (gamma)
