@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(KNN_THREADS) knn_kernel(const float *__restric
     // the exact square root is taken only for candidates that can pass.
     float thr_v = max_dist;
     int thr_i = -1;
-    float thr2 = max_dist * max_dist * 1.000001f;
+    float thr2 = max_dist * max_dist * 1.000002f;
     const int ks = (K - 1) >> 5, kl = (K - 1) & 31;  // register and lane of entry K-1
 
     // Tiles are visited outwards from the CTA's own tile.  The result does not depend on the order (entries are ordered
@@ -90,11 +90,14 @@ __global__ void __launch_bounds__(KNN_THREADS) knn_kernel(const float *__restric
     };
     float px = 0.f, py = 0.f, pz = 0.f;  // this thread's candidate of the next tile, fetched while the current one is scanned
     auto fetch = [&](int tile) {
+        // slots past the end of the batch element hold NaN: their squared distance compares false with every
+        // threshold, so the scan needs no bounds test
         const int j = tile * KNN_THREADS + threadIdx.x;
         const bool ok = j < N;
-        px = ok ? cz[j * 3] : 0.f;
-        py = ok ? cz[j * 3 + 1] : 0.f;
-        pz = ok ? cz[j * 3 + 2] : 0.f;
+        const float nan = __int_as_float(0x7fc00000);
+        px = ok ? cz[j * 3] : nan;
+        py = ok ? cz[j * 3 + 1] : nan;
+        pz = ok ? cz[j * 3 + 2] : nan;
     };
     int t = 0;
     fetch(t_own);
@@ -110,26 +113,30 @@ __global__ void __launch_bounds__(KNN_THREADS) knn_kernel(const float *__restric
         if (t < 2 * ntile) fetch(tile_at(t));
         if (!active) continue;
         const int cnt = min(KNN_THREADS, N - base);
-        // 128 candidates per step, four consecutive ones per lane: one vote of the warp tells whether any of them can
-        // enter the list (almost never once the threshold is tight), and only then are they looked at one by one.
+        // 128 candidates per step, four consecutive ones per lane.  The common case costs eight flops and one compare
+        // per candidate: squared distances against the squared threshold, one vote of the warp; only when some candidate
+        // may enter the list (almost never once the threshold is tight) are square roots taken and candidates looked at
+        // one by one.
         for (int b = 0; b < cnt; b += 128) {
             const int l0 = b + 4 * lane;
             const float4 cx = *reinterpret_cast<const float4 *>(&tx[l0]);
             const float4 cy = *reinterpret_cast<const float4 *>(&ty[l0]);
             const float4 cz4 = *reinterpret_cast<const float4 *>(&tz[l0]);
             const float xs[4] = {cx.x, cx.y, cx.z, cx.w}, ys[4] = {cy.x, cy.y, cy.z, cy.w}, zs[4] = {cz4.x, cz4.y, cz4.z, cz4.w};
-            float d[4];
-            bool any = false;
+            bool maybe = false;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
+            for (int q = 0; q < 4; ++q) {  // fused arithmetic is enough for the filter: thr2 carries a margin of 16 ulp
+                const float dx = xs[q] - ix, dy = ys[q] - iy, dz = zs[q] - iz;
+                maybe |= fmaf(dz, dz, fmaf(dy, dy, dx * dx)) <= thr2;
+            }
+            if (__ballot_sync(0xffffffffu, maybe) == 0u) continue;
+            float d[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {  // now exactly as the reference rounds
                 const float s2 = ref_distance2(xs[q], ys[q], zs[q], ix, iy, iz);
                 d[q] = INFINITY;
-                if (l0 + q < cnt && s2 <= thr2 && s2 != 0.f) {  // s2 == 0: the node itself and coincident points
-                    d[q] = __fsqrt_rn(s2);
-                    any |= knn_less(d[q], base + l0 + q, thr_v, thr_i);
-                }
+                if (s2 <= thr2 && s2 != 0.f) d[q] = __fsqrt_rn(s2);  // s2 == 0: the node itself and coincident points
             }
-            if (__ballot_sync(0xffffffffu, any) == 0u) continue;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 unsigned pass = __ballot_sync(0xffffffffu, knn_less(d[q], base + l0 + q, thr_v, thr_i));
@@ -175,7 +182,7 @@ __global__ void __launch_bounds__(KNN_THREADS) knn_kernel(const float *__restric
                             if (kv < max_dist) {  // the list holds K entries inside max_dist: its last one is the new threshold
                                 thr_v = kv;
                                 thr_i = ki;
-                                thr2 = kv * kv * 1.000001f;
+                                thr2 = kv * kv * 1.000002f;
                             }
                         }
                     }
