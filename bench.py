@@ -41,7 +41,7 @@ SFU_NOMINAL_PAIRS_PER_CLK_SM = 8.0  # 16 SFU results per clock per SM = 8 sin+co
 
 
 def workload():
-    from oracle import chains
+    from proteusai_b200 import synthetic as chains
     coords, _ = chains.chain_batch([N_SEQ], N_SEQ, seed=SEED)
     return torch.from_numpy(coords), torch.from_numpy(chains.wavenumbers(D_MODEL))
 
@@ -106,7 +106,7 @@ GA_Z, GA_H, GA_N, GA_D, GA_SEED = 8, 8, 1024, 64, 1003
 def geoattn_workload():
     """Config: B=8, H=8, N=1024, d_head=64, bf16; Q,K,V ~ N(0,1)/sqrt(d); random-walk chains with lengths
     uniform in 256..1024 (key-padding mask); sigma_h linear 3..15 A; upstream gradient N(0,1)."""
-    from oracle import chains
+    from proteusai_b200 import synthetic as chains
     lengths = chains.draw_lengths(GA_Z, 256, 1024, seed=GA_SEED)
     coords, mask = chains.chain_batch(lengths, GA_N, seed=GA_SEED)
     g = torch.Generator().manual_seed(GA_SEED)
@@ -184,7 +184,7 @@ def bench_encoder(dev, world, rank, steps, dist, graphed=False):
     layers of geometric attention (H=8, sigma 3..15 A) and a 2048-wide GELU FFN, linear head to 20 logits.  64 chains with
     lengths uniform in 64..1024 padded to 1024, data-parallel: each rank takes a contiguous slice of the batch.  Returns
     tokens/s over valid tokens (rank 0)."""
-    from oracle import chains
+    from proteusai_b200 import synthetic as chains
     from proteusai_b200 import sharding
     from proteusai_b200.utils.model_utils.base_modules.encoder import ProteusEncoderModel
     lengths = chains.draw_lengths(EN_Z, 64, 1024, seed=EN_SEED)
@@ -266,7 +266,7 @@ def bench_graph(dev, steps, cpu_baseline):
     """Neighbour graph (K = 30) and radial-basis edge features (4 x 4 atom pairs x 16 centres) of one chain of
     N = 16384 nodes, the step after the WE in the reference's featuriser.  One GPU (rank 0): the reference
     runs this per sample; nothing to shard inside one chain.  The edge-feature kernel is HBM-write bound (1 kB per edge)."""
-    from oracle import chains
+    from proteusai_b200 import synthetic as chains
     from proteusai_b200.utils.model_utils.gnn.gnn import edge_rbf, knn_neighbors
     n, k = 16384, 30
     c, _ = chains.chain_batch([n], n, seed=SEED)
