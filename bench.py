@@ -251,14 +251,15 @@ def bench_encoder(dev, world, rank, steps, dist, graphed=False):
         for _ in range(3):
             step_graph()
         torch.cuda.synchronize()
-        same = bool(torch.equal(ref_logits, out_host))
+        # (not bit-equal in general: with a padding mask the WE kernel adds its partial sums in a run-dependent order)
+        diff = float((ref_logits.float() - out_host.float()).abs().max())
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(steps):
             step_graph()
         b.record()
         torch.cuda.synchronize()
-        res["cuda_graph"] = {"ms_per_step": a.elapsed_time(b) / steps, "logits_equal_eager": same}
+        res["cuda_graph"] = {"ms_per_step": a.elapsed_time(b) / steps, "max_abs_diff_vs_eager": diff}
     return res
 
 
