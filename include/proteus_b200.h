@@ -37,6 +37,11 @@ enum pai_status {
     PAI_ERR_EXCEEDS_STATIC_SCRATCH = -9
 };
 
+/* Bits of the `flags` argument of pai_we_fwd. */
+enum pai_we_flags {
+    PAI_WE_REPRODUCIBLE = 1 /* bit-identical sums from run to run (see pai_we_fwd) */
+};
+
 /* ABI version of this header (bumped on any signature change). */
 int pai_abi_version(void);
 
@@ -71,13 +76,27 @@ int pai_device_status(void *stream);
  *                              [0,1] keeps the evaluation when >= dropout_p; kept terms, in `out` and in both
  *                              stored sums, are scaled by 1/(1-dropout_p).  The same seed gives the same pattern
  *                              for any row range, shard or launch configuration.
+ *   flags                      0, or PAI_WE_REPRODUCIBLE: by default the kernel cuts the work into equal runs that add
+ *                              their partial sums into the outputs with fp32 reductions in arrival order, so the
+ *                              last bit of a sum can differ from one launch to the next; with this flag every run
+ *                              covers whole items, at most two runs touch an output element and the results are
+ *                              bit-identical from launch to launch (a few per cent slower on small shards).  Other
+ *                              bits: PAI_ERR_UNSUPPORTED.
  * Pairs with j == i, coincident points (r == 0) and padded tokens contribute nothing.
  * Requires 1 <= N, 1 <= K, 1 <= Z <= 65535.
+ *
+ * Launches with a padding mask draw their work from one of 256 four-byte counters inside the library image,
+ * handed out round-robin per call (pai_we_aniso_fwd shares them).  Consequences for the caller:
+ *   - more than 256 masked launches in flight at once on one device would share a counter and give wrong sums;
+ *   - the first call on a device looks the counters up (cudaGetSymbolAddress), which is not allowed during stream
+ *     capture: make one warm-up call per device before capturing;
+ *   - a captured masked launch has its counter baked into the graph: do not let two replays of that graph (or a
+ *     replay and more than 255 other masked launches) overlap in time.
  */
 int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *wavenumbers,
                float *out, float *cos_sums, float *sin_sums,
                int Z, int N, int K, int row_begin, int row_end,
-               int magnitude_type, float dropout_p, uint32_t seed, void *stream);
+               int magnitude_type, float dropout_p, uint32_t seed, uint32_t flags, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Wavefunction Embedding, backward w.r.t. the wavenumbers.
@@ -148,6 +167,19 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
                          int Z, int N, int K, int row_begin, int row_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Geometric attention: batch plan.
+ * No counterpart in the reference, whose kernel walks every tile of the padded sequence
+ *   (old/old_scripts/attn/geometric_attn.py:183-219).  The plan lists, per sample, the 128-token tiles that hold a
+ *   valid token and orders the samples longest first; the attention kernels then never load a tile of padding and
+ *   issue the long samples first.  One plan serves every call (all layers and heads, forward and backward) that
+ *   uses the same mask; a call that passes `valid` must pass the plan made from it (with the same Z and N).
+ *
+ *   valid [Z,N] u8; plan: at least pai_geoattn_plan_bytes(Z,N) bytes, 16-byte aligned, written by the call.
+ */
+size_t pai_geoattn_plan_bytes(int Z, int N);
+int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Geometric attention, forward.
  * Replaces the Triton launch `_attn_fwd[grid](...)` in _geometric_attn.forward
  *   (old/old_scripts/attn/geometric_attn.py:553-607; kernel :57-260).  Two logit forms:
@@ -165,20 +197,22 @@ int pai_we_bwd_dk_static(const float *dO, const float *cos_sums, const float *si
  *   sigma    [H]       fp32                 per-head RBF spread
  *   betas    [H]       fp32                 per-head RBF weight (logit_form 1)
  *   valid    [Z,N]     u8                   1 = real token, 0 = padding; NULL = all valid
- *   sample_order [Z]   i32                  optional permutation of the samples (NULL = natural order): CTAs are issued
- *                                            sample by sample in this order; passing the samples longest-first evens out
- *                                            the work of neighbouring CTAs on padded batches.  Needs the full zh range.
- *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros
+ *   plan                                    from pai_geoattn_plan for this `valid` (required with `valid`, ignored without)
+ *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros (whatever Q, K, V hold there)
  *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for rows without a valid pair
  *   scale                                    softmax scale, 1/sqrt(d) in the reference
  *   zh_begin, zh_end                         only the (batch, head) pairs z*H + h in [zh_begin, zh_end) are
  *                                            computed and written (multi-GPU shard); other rows are not touched
+ *   q_begin, q_end                           only the query rows [q_begin, q_end) of those pairs are computed and written
+ *                                            (multi-GPU shard by query blocks, the reference grid's first axis,
+ *                                            geometric_attn.py:582-585); q_begin a multiple of 128, q_end a multiple of
+ *                                            128 or N.  Keys and values are always read in full.
  * bf16 x bf16 -> fp32 tensor-core products, fp32 softmax, P rounded to bf16 before P V.
  */
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L,
+                    const float *betas, const uint8_t *valid, const void *plan, void *O, float *L,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
-                    int zh_begin, int zh_end, void *stream);
+                    int zh_begin, int zh_end, int q_begin, int q_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, forward, on strided tensors.
@@ -195,10 +229,10 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
  */
 int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides,
                             const void *V, const int64_t *v_strides, const float *coords, const float *sigma,
-                            const float *betas, const uint8_t *valid, const int32_t *sample_order,
+                            const float *betas, const uint8_t *valid, const void *plan,
                             void *O, const int64_t *o_strides, float *L,
                             int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
-                            int zh_begin, int zh_end, void *stream);
+                            int zh_begin, int zh_end, int q_begin, int q_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Geometric attention, backward.
@@ -207,22 +241,24 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
  *   logit forms of pai_geoattn_fwd.
  *
  *   Q, K, V, O, dO [Z,H,N,d] bf16 contiguous (d must be 64); L [Z,H,N] fp32 as written by the forward
- *   dQ, dK, dV     [Z,H,N,d] fp32, like the reference's gradients (:626-628); every row of the
- *                  (batch, head) range is written, rows of padded tokens as zeros; dQ is accumulated
- *                  across key tiles with fp32 reductions, so its summation order is not fixed
+ *   dQ, dK, dV     [Z,H,N,d] fp32, like the reference's gradients (:626-628).  Of the (batch, head) range: every
+ *                  row of dK and dV is written, and the rows [q_begin, q_end) of dQ; rows of padded tokens as zeros;
+ *                  dQ is accumulated across key tiles with fp32 reductions, so its summation order is not fixed
  *   dsigma         [H] fp32, overwritten: gradient w.r.t. the spreads summed over the (batch, head) range
  *   dbetas         [H] fp32, overwritten: gradient w.r.t. betas (logit_form 1; may be NULL for logit_form 0)
  *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned
  *                  (holds D, one fp32 per query row)
- *   sample_order, zh_begin, zh_end  as in the forward
+ *   valid, plan, zh_begin, zh_end  as in the forward
+ *   q_begin, q_end only the query rows [q_begin, q_end) contribute: dK, dV, dsigma, dbetas are then partial sums
+ *                  that the caller adds over the query shards (an all-reduce across ranks); same alignment rule
  */
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d);
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
                     const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
-                    const int32_t *sample_order, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
+                    const void *plan, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
                     void *workspace, size_t workspace_bytes,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
-                    int zh_begin, int zh_end, void *stream);
+                    int zh_begin, int zh_end, int q_begin, int q_end, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Row operations of the encoder block on either side of the attention kernel (bf16 in and out, fp32 arithmetic).
@@ -278,6 +314,32 @@ int pai_edge_rbf(const float *atoms, const int64_t *idx, const float *centers, d
  * denominator of the WE roofline; has no counterpart in the reference.
  */
 int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms);
+
+/* ---------------------------------------------------------------------------------------
+ * Test-only entries (no counterpart in the reference; not for production callers).
+ *
+ * pai_tune_set            sets a process-wide tuning knob of the kernels (launch geometry and kernel variants that
+ *                         do not change results beyond rounding); the hot entry points read the knobs as plain
+ *                         integers, there is no environment lookup anywhere.  Value 0 = the library's own choice
+ *                         unless stated.  PAI_ERR_UNSUPPORTED for an unknown key.
+ * pai_selftest_wait_timeout  launches one CTA whose warps wait, with a limit of a few thousand cycles, on an mbarrier
+ *                         that nobody arrives on: exercises the path a kernel takes when a bounded device-side wait
+ *                         runs out.  The kernel returns normally; afterwards pai_device_status() reports
+ *                         PAI_ERR_DEVICE_WAIT_TIMEOUT once and the device is usable as before.
+ */
+enum pai_tune_key {
+    PAI_TUNE_WE_KS = 0,           /* wavenumbers per lane: 2, 8 or 16 */
+    PAI_TUNE_WE_TJ = 1,           /* sources per staged tile: multiple of 4 up to 512 */
+    PAI_TUNE_WE_WAVES = 2,        /* runs per resident CTA slot */
+    PAI_TUNE_WE_RANGE_REDUCE = 3, /* 1: explicit range reduction of the phase before the SFU */
+    PAI_TUNE_WE_POLY_PAIRS = 4,   /* wavenumber pairs per lane evaluated on the FMA pipe (default 1) */
+    PAI_TUNE_WE_NO_TMA = 5,       /* 1: plain loads instead of bulk copies for the source tiles */
+    PAI_TUNE_GA_NO_FAR_SKIP = 6,  /* 1: evaluate the RBF of every key group, however far */
+    PAI_TUNE_GA_NO_ORDER = 7,     /* 1: issue the samples in natural order instead of longest first */
+    PAI_TUNE_COUNT = 8
+};
+int pai_tune_set(int key, int value);
+int pai_selftest_wait_timeout(void *stream);
 
 #ifdef __cplusplus
 }

@@ -19,7 +19,7 @@ SIGNATURES = {
     "pai_status_str": (c_char_p, [c_int]),
     "pai_device_status": (c_int, [c_void_p]),
     "pai_we_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                           c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_uint32, c_void_p]),
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_uint32, c_uint32, c_void_p]),
     "pai_we_bwd_dk_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "pai_we_bwd_dk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                               c_int, c_int, c_int, c_int, c_int, c_void_p]),
@@ -28,19 +28,30 @@ SIGNATURES = {
     "pai_we_aniso_bwd": (c_int, [c_void_p] * 6 + [c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_we_bwd_dk_static_max_k": (c_int, []),
     "pai_we_bwd_dk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+    "pai_geoattn_plan_bytes": (c_size_t, [c_int, c_int]),
+    "pai_geoattn_plan": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+                                c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_fwd_strided": (c_int, [c_void_p, _I64P, c_void_p, _I64P, c_void_p, _I64P] + [c_void_p] * 6 + [_I64P, c_void_p] +
-                                [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_void_p]),
+                                [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "pai_geoattn_bwd": (c_int, [c_void_p] * 16 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
-                                c_int, c_int, c_void_p]),
+                                c_int, c_int, c_int, c_int, c_void_p]),
     "pai_add_layernorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p]),
     "pai_gelu_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_void_p]),
     "pai_knn_neighbors": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "pai_edge_rbf": (c_int, [c_void_p, c_void_p, c_void_p, c_double, c_void_p, c_void_p, c_float, c_void_p,
                              c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_measure_sfu_peak": (c_int, [ctypes.POINTER(c_double), ctypes.POINTER(c_double)]),
+    "pai_tune_set": (c_int, [c_int, c_int]),
+    "pai_selftest_wait_timeout": (c_int, [c_void_p]),
 }
+
+# enum pai_we_flags / enum pai_tune_key of the header
+WE_REPRODUCIBLE = 1
+TUNE = {"we_ks": 0, "we_tj": 1, "we_waves": 2, "we_range_reduce": 3, "we_poly_pairs": 4, "we_no_tma": 5,
+        "ga_no_far_skip": 6, "ga_no_order": 7}
+TUNE_DEFAULTS = {"we_poly_pairs": 1}
 
 _lib = None
 
@@ -82,6 +93,16 @@ def current_stream():
 def device_status():
     """Synchronise the current stream and raise if a kernel reported a bounded-wait timeout."""
     check(lib().pai_device_status(current_stream()), "device status")
+
+
+def tune(**knobs):
+    """Test-only: set tuning knobs of the kernels by name (see ``enum pai_tune_key``); ``tune_reset()`` restores them."""
+    for name, value in knobs.items():
+        check(lib().pai_tune_set(TUNE[name], int(value)), f"pai_tune_set({name})")
+
+
+def tune_reset():
+    tune(**{name: TUNE_DEFAULTS.get(name, 0) for name in TUNE})
 
 
 def measure_sfu_peak():

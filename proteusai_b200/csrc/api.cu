@@ -10,7 +10,6 @@
 #include "we_fwd.cuh"
 #include "we_aniso_fwd.cuh"
 
-#include <cstdlib>
 #include <cstring>
 
 namespace {
@@ -83,10 +82,13 @@ int require_sm100() {
     return cc == 100 ? 0 : (int)PAI_ERR_NOT_SM100;
 }
 
-int env_int(const char *name, int dflt) {
-    const char *v = std::getenv(name);
-    return v && *v ? std::atoi(v) : dflt;
-}
+// Tuning knobs of the test-only entry pai_tune_set (plain process-wide integers; the hot entry points read
+// them without any environment lookup).  Defaults are what the library ships with.
+int g_tune[PAI_TUNE_COUNT] = {
+    /* PAI_TUNE_WE_KS */ 0,        /* PAI_TUNE_WE_TJ */ 0,          /* PAI_TUNE_WE_WAVES */ 0,
+    /* PAI_TUNE_WE_RANGE_REDUCE */ 0, /* PAI_TUNE_WE_POLY_PAIRS */ 1, /* PAI_TUNE_WE_NO_TMA */ 0,
+    /* PAI_TUNE_GA_NO_FAR_SKIP */ 0,  /* PAI_TUNE_GA_NO_ORDER */ 0,
+};
 
 // register-only sin+cos loop: 8 independent chains per thread
 __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
 
 extern "C" {
 
-int pai_abi_version(void) { return 4; }  // 4: dropout in pai_we_fwd; strided attention forward; encoder row kernels; neighbour graph and edge features
+int pai_abi_version(void) { return 5; }  // 5: flags in pai_we_fwd; attention batch plan and query-row ranges; test-only entries
 
 const char *pai_status_str(int status) {
     switch (status) {
@@ -148,12 +150,13 @@ int pai_device_status(void *stream) {
 
 int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *wavenumbers, float *out, float *cos_sums,
                float *sin_sums, int Z, int N, int K, int row_begin, int row_end, int magnitude_type, float dropout_p,
-               uint32_t seed, void *stream) {
+               uint32_t seed, uint32_t flags, void *stream) {
     if (!coords_soa || !wavenumbers || !out || !cos_sums || !sin_sums) return PAI_ERR_NULL_POINTER;
     if (Z < 1 || Z > 65535 || N < 1 || K < 1 || (long long)N * K > (1ll << 40)) return PAI_ERR_BAD_SHAPE;
     if (row_begin < 0 || row_end > N || row_begin > row_end) return PAI_ERR_BAD_ROW_RANGE;
     if (magnitude_type < 0 || magnitude_type > 3) return PAI_ERR_UNSUPPORTED;
     if (!(dropout_p >= 0.0f && dropout_p < 1.0f)) return PAI_ERR_UNSUPPORTED;
+    if (flags & ~(uint32_t)PAI_WE_REPRODUCIBLE) return PAI_ERR_UNSUPPORTED;
     if (!aligned(coords_soa, 4) || !aligned(wavenumbers, 4)) return PAI_ERR_MISALIGNED;
     if ((K & 1) == 0 ? (!aligned(out, 16) || !aligned(cos_sums, 8) || !aligned(sin_sums, 8))
                      : (!aligned(out, 4) || !aligned(cos_sums, 4) || !aligned(sin_sums, 4)))
@@ -190,7 +193,7 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
         p.drop_scale = 1.0f / (1.0f - dropout_p);
     }
     // bulk copies need 16-byte aligned plane segments: base aligned and N a multiple of 4
-    p.use_tma = (aligned(coords_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
+    p.use_tma = (aligned(coords_soa, 16) && (N % 4) == 0 && g_tune[PAI_TUNE_WE_NO_TMA] == 0) ? 1 : 0;
     // the kernel adds partial sums into the outputs: zero the rows of the shard first
     cudaStream_t st = (cudaStream_t)stream;
     const size_t rows = (size_t)(row_end - row_begin);
@@ -207,9 +210,9 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     if (int e = current_device_sms(&sms)) return e;
     unsigned *counter = nullptr;
     if (int e = next_we_counter(&counter)) return e;
-    return pai::we_fwd_launch(p, Z, env_int("PAI_WE_KS", 0), env_int("PAI_WE_TJ", 0), env_int("PAI_WE_WAVES", 0),
-                              env_int("PAI_WE_REPRODUCIBLE", 0) != 0, env_int("PAI_WE_RANGE_REDUCE", 0) != 0,
-                              env_int("PAI_WE_POLY_PAIRS", 1), sms, counter, st);
+    return pai::we_fwd_launch(p, Z, g_tune[PAI_TUNE_WE_KS], g_tune[PAI_TUNE_WE_TJ], g_tune[PAI_TUNE_WE_WAVES],
+                              (flags & PAI_WE_REPRODUCIBLE) != 0, g_tune[PAI_TUNE_WE_RANGE_REDUCE] != 0,
+                              g_tune[PAI_TUNE_WE_POLY_PAIRS], sms, counter, st);
 }
 
 size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {
@@ -236,20 +239,55 @@ int pai_we_bwd_dk(const float *dO, const float *cos_sums, const float *sin_sums,
                               (cudaStream_t)stream);
 }
 
-int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides, const void *V,
-                            const int64_t *v_strides, const float *coords, const float *sigma, const float *betas,
-                            const uint8_t *valid, const int32_t *sample_order, void *O, const int64_t *o_strides, float *L, int Z,
-                            int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin,
-                            int zh_end, void *stream) {
-    if (!Q || !K || !V || !coords || !sigma || !O || !L || !q_strides || !k_strides || !v_strides || !o_strides)
-        return PAI_ERR_NULL_POINTER;
+size_t pai_geoattn_plan_bytes(int Z, int N) {
+    if (Z < 1 || N < 1) return 0;
+    return pai::ga_plan_words(Z, N) * sizeof(int);
+}
+
+int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan_bytes, void *stream) {
+    if (!valid || !plan) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || Z > 65535 || N < 1 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
+    if (!aligned(plan, 16)) return PAI_ERR_MISALIGNED;
+    if (plan_bytes < pai_geoattn_plan_bytes(Z, N)) return PAI_ERR_WORKSPACE_TOO_SMALL;
+    if (int e = require_sm100()) return e;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t ce = cudaMemsetAsync(plan, 0, pai::GA_PLAN_HEADER * sizeof(int), st);  // the arrival counter starts at 0
+    if (ce != cudaSuccess) return (int)ce;
+    pai::geoattn_plan_kernel<<<Z, 256, 0, st>>>(valid, (int *)plan, Z, N);
+    return (int)cudaPeekAtLastError();
+}
+
+namespace {
+// argument checks shared by the attention entry points; *qt0, *qt1: query tiles of the row range
+int check_attn_common(int Z, int H, int N, int d, int logit_form, const float *betas, float min_rbf, float max_rbf,
+                      const uint8_t *valid, const void *plan, int zh_begin, int zh_end, int q_begin, int q_end) {
     if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
     if (logit_form == 1 && !betas) return PAI_ERR_NULL_POINTER;
     if (logit_form == 1 && !(max_rbf > min_rbf)) return PAI_ERR_BAD_SHAPE;
     if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
     if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
     if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
-    if (sample_order && (zh_begin != 0 || zh_end != Z * H)) return PAI_ERR_UNSUPPORTED;  // a permutation needs the full range
+    if (q_begin < 0 || q_end > N || q_begin > q_end || (q_begin % pai::GA_BM) != 0 || (q_end != N && (q_end % pai::GA_BM) != 0))
+        return PAI_ERR_BAD_ROW_RANGE;
+    if (valid && !plan) return PAI_ERR_NULL_POINTER;  // a mask needs its plan
+    if (plan && !aligned(plan, 16)) return PAI_ERR_MISALIGNED;
+    return 0;
+}
+// the plan's longest-first order applies when the range covers whole samples from the first to the last
+bool order_applies(const void *plan, int Z, int H, int zh_begin, int zh_end) {
+    return plan != nullptr && zh_begin == 0 && zh_end == Z * H && g_tune[PAI_TUNE_GA_NO_ORDER] == 0;
+}
+}  // namespace
+
+int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides, const void *V,
+                            const int64_t *v_strides, const float *coords, const float *sigma, const float *betas,
+                            const uint8_t *valid, const void *plan, void *O, const int64_t *o_strides, float *L, int Z, int H,
+                            int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
+                            int q_begin, int q_end, void *stream) {
+    if (!Q || !K || !V || !coords || !sigma || !O || !L || !q_strides || !k_strides || !v_strides || !o_strides)
+        return PAI_ERR_NULL_POINTER;
+    if (int e = check_attn_common(Z, H, N, d, logit_form, betas, min_rbf, max_rbf, valid, plan, zh_begin, zh_end, q_begin, q_end))
+        return e;
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(coords, 4) ||
         !aligned(sigma, 4) || !aligned(L, 4))
         return PAI_ERR_MISALIGNED;
@@ -262,7 +300,7 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
             if (st[a] < d && extent > 1) return PAI_ERR_BAD_SHAPE;  // rows of d elements must not overlap
         }
     if (int e = require_sm100()) return e;
-    if (zh_begin == zh_end) return PAI_OK;
+    if (zh_begin == zh_end || q_begin == q_end) return PAI_OK;
     const int nzh = zh_end - zh_begin;
     auto stride_of = [&](const int64_t *st, int a, int extent) { return extent > 1 ? (long long)st[a] : (long long)d; };
     CUtensorMap mq, mk, mv;
@@ -287,6 +325,7 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
     pai::GaFwdParams p;
     p.coords = coords;
     p.valid = valid;
+    p.plan = valid ? (const int *)plan : nullptr;
     p.sigma = sigma;
     p.out = (__nv_bfloat16 *)O;
     p.so_z = stride_of(o_strides, 0, Z);
@@ -297,24 +336,26 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
     p.H = H;
     p.N = N;
     p.zh_begin = zh_begin;
+    p.q_begin = q_begin;
+    p.use_order = order_applies(p.plan, Z, H, zh_begin, zh_end) ? 1 : 0;
+    p.far_skip = g_tune[PAI_TUNE_GA_NO_FAR_SKIP] == 0 ? 1 : 0;
     p.scale = scale;
     p.form = logit_form;
     p.beta = betas;
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
-    p.order = sample_order;
-    dim3 grid((N + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
+    dim3 grid((q_end - q_begin + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
     pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
 }
 
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, const int32_t *sample_order, void *O, float *L, int Z, int H,
+                    const float *betas, const uint8_t *valid, const void *plan, void *O, float *L, int Z, int H,
                     int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
-                    void *stream) {
+                    int q_begin, int q_end, void *stream) {
     const int64_t st[3] = {(int64_t)H * N * d, (int64_t)N * d, (int64_t)d};  // contiguous [Z,H,N,d]
-    return pai_geoattn_fwd_strided(Q, st, K, st, V, st, coords, sigma, betas, valid, sample_order, O, st, L, Z, H, N, d, scale,
-                                   min_rbf, max_rbf, logit_form, zh_begin, zh_end, stream);
+    return pai_geoattn_fwd_strided(Q, st, K, st, V, st, coords, sigma, betas, valid, plan, O, st, L, Z, H, N, d, scale,
+                                   min_rbf, max_rbf, logit_form, zh_begin, zh_end, q_begin, q_end, stream);
 }
 
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
@@ -325,18 +366,14 @@ size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
 
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
                     const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
-                    const int32_t *sample_order, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas, void *workspace,
+                    const void *plan, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas, void *workspace,
                     size_t workspace_bytes, int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf,
-                    int logit_form, int zh_begin, int zh_end, void *stream) {
+                    int logit_form, int zh_begin, int zh_end, int q_begin, int q_end, void *stream) {
     if (!Q || !K || !V || !O || !dO || !L || !coords || !sigma || !dQ || !dK || !dV || !dsigma || !workspace)
         return PAI_ERR_NULL_POINTER;
-    if (logit_form != 0 && logit_form != 1) return PAI_ERR_UNSUPPORTED;
-    if (logit_form == 1 && (!betas || !dbetas)) return PAI_ERR_NULL_POINTER;
-    if (logit_form == 1 && !(max_rbf > min_rbf)) return PAI_ERR_BAD_SHAPE;
-    if (Z < 1 || H < 1 || N < 1 || (long long)Z * H > 65535 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
-    if (d != pai::GA_D) return PAI_ERR_UNSUPPORTED;
-    if (zh_begin < 0 || zh_end > Z * H || zh_begin > zh_end) return PAI_ERR_BAD_ROW_RANGE;
-    if (sample_order && (zh_begin != 0 || zh_end != Z * H)) return PAI_ERR_UNSUPPORTED;  // a permutation needs the full range
+    if (logit_form == 1 && !dbetas) return PAI_ERR_NULL_POINTER;
+    if (int e = check_attn_common(Z, H, N, d, logit_form, betas, min_rbf, max_rbf, valid, plan, zh_begin, zh_end, q_begin, q_end))
+        return e;
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(dO, 16) || !aligned(dQ, 16) ||
         !aligned(dK, 16) || !aligned(dV, 16) || !aligned(L, 4) || !aligned(coords, 4) || !aligned(sigma, 4) ||
         !aligned(dsigma, 4) || !aligned(workspace, 16))
@@ -354,8 +391,6 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     const int nzh = zh_end - zh_begin;
     const size_t rows0 = (size_t)zh_begin * N;
     const size_t off = rows0 * d * 2;
-    ce = cudaMemsetAsync(dQ + rows0 * d, 0, (size_t)nzh * N * d * sizeof(float), st);
-    if (ce != cudaSuccess) return (int)ce;
     CUtensorMap mq, mk, mv, mdo;
     if (int e = pai::make_map_bf16_rows(&mq, (const char *)Q + off, nzh, N, d, pai::GA_BM)) return e;
     if (int e = pai::make_map_bf16_rows(&mk, (const char *)K + off, nzh, N, d, pai::GA_BN)) return e;
@@ -370,10 +405,14 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
         if (ce != cudaSuccess) return (int)ce;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
+    // pre-pass: D = rowsum(O * dO) and zeros into dQ, both over the query rows of the range
     float *dsum = (float *)workspace;
-    const long long rows = (long long)nzh * N;
-    pai::geoattn_bwd_dsum_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-        (const __nv_bfloat16 *)O + rows0 * d, (const __nv_bfloat16 *)dO + rows0 * d, dsum, rows);
+    if (q_end > q_begin) {
+        const int q_rows = q_end - q_begin;
+        const long long rows = (long long)nzh * q_rows;
+        pai::geoattn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+            (const __nv_bfloat16 *)O + rows0 * d, (const __nv_bfloat16 *)dO + rows0 * d, dsum, dQ + rows0 * d, N, q_begin, q_rows, rows);
+    }
     pai::GaBwdParams p;
     p.coords = coords;
     p.valid = valid;
@@ -389,7 +428,11 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.beta = betas;
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
-    p.order = sample_order;
+    p.plan = valid ? (const int *)plan : nullptr;
+    p.use_order = order_applies(p.plan, Z, H, zh_begin, zh_end) ? 1 : 0;
+    p.far_skip = g_tune[PAI_TUNE_GA_NO_FAR_SKIP] == 0 ? 1 : 0;
+    p.qt_begin = q_begin / pai::GA_BM;
+    p.qt_end = (q_end + pai::GA_BM - 1) / pai::GA_BM;
     p.Z = Z;
     p.H = H;
     p.N = N;
@@ -433,7 +476,7 @@ int pai_we_aniso_fwd(const float *coords_a_soa, const float *coords_b_soa, const
     p.K = K;
     p.row_begin = row_begin;
     p.row_end = row_end;
-    p.use_tma = (aligned(coords_a_soa, 16) && aligned(coords_b_soa, 16) && (N % 4) == 0 && env_int("PAI_WE_NO_TMA", 0) == 0) ? 1 : 0;
+    p.use_tma = (aligned(coords_a_soa, 16) && aligned(coords_b_soa, 16) && (N % 4) == 0 && g_tune[PAI_TUNE_WE_NO_TMA] == 0) ? 1 : 0;
     unsigned *counter = nullptr;
     if (valid)
         if (int e = next_we_counter(&counter)) return e;
@@ -590,6 +633,19 @@ int pai_measure_sfu_peak(double *sincos_pairs_per_s, double *elapsed_ms) {
     *elapsed_ms = best;
     *sincos_pairs_per_s = (double)blocks * threads * iters * 8.0 / (best * 1e-3);
     return PAI_OK;
+}
+
+// ---- test-only entries ---------------------------------------------------------------------------
+int pai_tune_set(int key, int value) {
+    if (key < 0 || key >= PAI_TUNE_COUNT) return PAI_ERR_UNSUPPORTED;
+    g_tune[key] = value;
+    return PAI_OK;
+}
+
+int pai_selftest_wait_timeout(void *stream) {
+    if (int e = require_sm100()) return e;
+    pai::selftest_wait_timeout_kernel<<<1, 64, 0, (cudaStream_t)stream>>>();
+    return (int)cudaPeekAtLastError();
 }
 
 }  // extern "C"

@@ -2,8 +2,8 @@
 //
 // Replaces the Triton kernel `_attn_bwd` (old/old_scripts/attn/geometric_attn.py:265-543) and the
 // PyTorch row-sum in front of it (:616), for the logit form SR = S (1 + R), S = scale q.k,
-// R = exp(-d^2 / (2 sigma_h^2)):
-//     D_i   = sum_d O_id dO_id                       (pre-kernel, fp32 scratch)
+// R = exp(-d^2 / (2 sigma_h^2)) (and for the reference tree's own form, FORM = 1):
+//     D_i   = sum_d O_id dO_id                       (pre-pass, fp32 scratch; the same pass zeroes dQ)
 //     P_ij  = exp(SR_ij - L_i)                        (recomputed from the stored log-sum-exp)
 //     dV_j  = sum_i P_ij dO_i
 //     dP_ij = dO_i . V_j
@@ -11,48 +11,54 @@
 //     dS    = dSR (1 + R) scale        -> dQ_i = sum_j dS_ij K_j,   dK_j = sum_i dS_ij Q_i
 //     dsigma_h = sum_{z,i,j} dSR S R d^2 / sigma_h^3
 //
-// One CTA = 128 keys of one (batch, head); it loops over the 128-row query tiles.  16 math warps and one
-// producer warp: query row r = TMEM lane r of the current tile is shared by four math threads (warps
-// w, w+4, w+8, w+12), each taking 32 of the 128 key columns; no row reduction is needed in the backward
-// because the log-sum-exp L and D are known.  Lane 0 of the producer warp issues every TMA load and MMA.
-// Five MMAs per query tile, all operands straight from the TMA-written swizzled tiles, transposes
-// expressed through the operand major-ness:
-//     S   = Q_i K_j^T     A K-major,  B K-major     -> TMEM [128 x 128]
-//     dP  = dO_i V_j^T    A K-major,  B K-major     -> TMEM [128 x 128]
-//     dV += P^T dO_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
-//     dK += dS^T Q_i      A MN-major, B MN-major    -> TMEM [128 x 64], accumulated over i
-//     dQ_i = dS K_j       A K-major,  B MN-major    -> TMEM [128 x 64], read back and added into the global
-//                                                      fp32 dQ with 16-byte vector reductions
-// P and dS are written by the math threads as bf16 into shared memory in the swizzled [i][j] layout,
-// which serves both as K-major (dQ) and MN-major (dV, dK) operand.  The element-wise stage runs in
-// packed fp32x2 arithmetic with |r_i - r_j|^2 from centred coordinates (three FMAs).  Query tiles
-// without a valid query are skipped, a key tile without a valid key only writes zeros.
+// One CTA = 128 keys of one (batch, head); it loops over the live 128-row query tiles.  The logit tile is
+// computed TRANSPOSED, keys on the TMEM lanes and queries along the columns, so that a math thread owns a key:
+//     S^T  = K_j Q_i^T     A, B K-major                          -> TMEM [128 keys x 128 queries]
+//     dP^T = V_j dO_i^T    A, B K-major                          -> TMEM [128 x 128]
+//     dV  += P^T dO_i      A = P^T read from TENSOR MEMORY (bf16 pairs written by the math threads), B = dO MN-major
+//     dK  += dS^T Q_i      A = dS^T from shared memory, K-major (the math threads write row j = their key, the
+//                          queries contiguous: 16-byte stores), B = Q MN-major
+//     dQ_i = dS K_j        A = the same dS^T tile read MN-major, B = K MN-major -> TMEM [128 queries x 64], read
+//                          back and added into the global fp32 dQ with 16-byte vector reductions
+// Eight math warps and one producer warp: key row r = TMEM lane r is shared by two math threads (warps w, w + 4),
+// each taking 64 of the 128 query columns in two passes of 32.  After the second pass has loaded its
+// columns the S^T / dP^T accumulators are released and the tensor core computes the next query tile's underneath
+// the element-wise work of this one; dV / dK / dQ of tile t run under the element-wise work of tile t + 1, and
+// dQ(t) is read out after tile t + 1 has been handed over, when it has long completed.  Per-query inputs (centred
+// coordinates, log-sum-exp, D, validity, bounding spheres of 16 queries) are staged in shared memory one tile
+// ahead; no row reduction is needed in the backward.  Query groups farther than 5.9 sigma_h from a warp's 32 keys
+// skip the RBF arithmetic (R < 2^-25 there).  Query tiles without a valid query are skipped, a key tile without a
+// valid key only writes zeros.  Every wait is bounded and abortable (tc.cuh).
 #pragma once
 #include "geoattn_fwd.cuh"
 
 namespace pai {
 
 constexpr uint32_t GA_BWD_TMEM_COLS = 512;
-constexpr int GA_BWD_MATH_THREADS = 512;
+constexpr int GA_BWD_MATH_THREADS = 256;
 constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 32;  // + the producer warp
+constexpr int GA_ROW_BUFS = 3;
+
+struct GaQueryRows {                  // per-query inputs of one query tile, two queries per entry
+    float4 qa[GA_BM / 2];             // {x_i, x_i+1, y_i, y_i+1}   centred on the key tile's first valid key
+    float4 qc[GA_BM / 2];             // {z_i, z_i+1, |q_i|^2, |q_i+1|^2}
+    float2 l2[GA_BM / 2];             // log-sum-exp in base-2 units (+inf: padded query or row without a valid pair)
+    float2 dsum[GA_BM / 2];           // D_i
+    alignas(16) float qb[GA_BM];      // 0 for a valid query, -inf for a padded one
+    float4 sph[GA_BM / 16];           // bounding sphere of each group of 16 queries (radius < 0: no valid query)
+};
 
 struct GaBwdSmem {
     alignas(1024) uint8_t k[GA_TILE_BYTES];
     alignas(1024) uint8_t v[GA_TILE_BYTES];
     alignas(1024) uint8_t q[2][GA_TILE_BYTES];
     alignas(1024) uint8_t dout[2][GA_TILE_BYTES];
-    alignas(1024) uint8_t p[2 * GA_TILE_BYTES];
-    alignas(1024) uint8_t ds[2 * GA_TILE_BYTES];
-    // centred key coordinates, two keys per entry:
-    float4 ka[GA_BN / 2];                  // {x_j, x_j+1, y_j, y_j+1}
-    float4 kc[GA_BN / 2];                  // {z_j, z_j+1, |k_j|^2, |k_j+1|^2}
-    alignas(16) float kb[GA_BN];           // additive mask: 0 for a valid key, -inf for a padded one
-    uint16_t tiles[GA_MAX_TILES];          // query tiles that hold at least one valid query
-    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_g, bar_vk, bar_pds, bar_dqr;
+    alignas(1024) uint8_t ds[2][2 * GA_TILE_BYTES];  // dS^T [128 keys x 128 queries] bf16: two [128 x 64] swizzled sub-tiles
+    GaQueryRows rows[GA_ROW_BUFS];
+    uint16_t tiles[GA_MAX_TILES];          // live query tiles of the range; bit 15: the tile also holds a padded query
+    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_spfree, bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS];
     uint32_t tmem_base;
-    int ntiles;
-    int first_k;                           // first valid key of the tile (origin of the centring)
-    int has_hole;                          // the key tile holds a padded or out-of-range key
+    int abort;
     float dsig[GA_BWD_MATH_THREADS / 32];
     float dbeta[GA_BWD_MATH_THREADS / 32];
 };
@@ -60,6 +66,7 @@ struct GaBwdSmem {
 struct GaBwdParams {
     const float *coords;   // [Z,N,3]
     const uint8_t *valid;  // [Z,N] or nullptr
+    const int *plan;       // batch plan (geoattn_plan.cuh); nullptr iff valid is nullptr
     const float *sigma;    // [H]
     const float *lse;      // [Z,H,N]
     const float *dsum;     // [nzh,N]   D = rowsum(O * dO), indexed from zh_begin
@@ -73,126 +80,189 @@ struct GaBwdParams {
     int form;              // logit form, as in the forward
     const float *beta;     // [H], form 1 only
     float min_rbf, max_rbf;
-    const int *order;      // [Z] permutation of the samples or nullptr (only with the full (batch, head) range)
+    int use_order;         // issue the samples in the plan's longest-first order
+    int far_skip;          // skip the RBF arithmetic of far query groups
+    int qt_begin, qt_end;  // query tiles [qt_begin, qt_end) are visited
 };
 
-// D[zh_local, i] = sum_d O * dO; one warp per row, 2 elements per lane.
-__global__ void __launch_bounds__(256) geoattn_bwd_dsum_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *d_out, float *dsum,
-                                                               long long rows) {
-    const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+// Pre-pass: D[pair, i] = sum_d O * dO for the query rows [q_begin, q_begin + q_rows) of every (batch, head) pair of
+// the range, and zeros into the same rows of dQ, which the main kernel accumulates with reductions.  One warp per
+// row; o, d_out, dsum and dq point at the first pair of the range.
+__global__ void __launch_bounds__(256) geoattn_bwd_prep_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *d_out, float *dsum,
+                                                               float *dq, int N, int q_begin, int q_rows, long long rows) {
+    const long long idx = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // (pair, row inside the range)
     const int lane = threadIdx.x & 31;
-    if (row >= rows) return;
+    if (idx >= rows) return;
+    const long long pair = idx / q_rows;
+    const long long row = pair * N + q_begin + (idx - pair * q_rows);
     const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162 *>(o + row * GA_D)[lane];
     const __nv_bfloat162 b = reinterpret_cast<const __nv_bfloat162 *>(d_out + row * GA_D)[lane];
     float s = __bfloat162float(a.x) * __bfloat162float(b.x) + __bfloat162float(a.y) * __bfloat162float(b.y);
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
     if (lane == 0) dsum[row] = s;
+    reinterpret_cast<float2 *>(dq + row * GA_D)[lane] = make_float2(0.f, 0.f);
 }
 
 __device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-struct GaBwdRow {  // per-thread constants of the current query row, packed for fp32x2 arithmetic
-    f2_t qx2, qy2, qz2, cqn2, l22, dsum2;
+struct GaBwdKey {  // per-thread constants of the thread's key, packed for fp32x2 arithmetic
+    f2_t kx2, ky2, kz2, ckn2;  // -2 k (centred), c_rbf |k|^2
+    bool k_ok;
 };
 
-// 16 key columns (8 pairs) of one query row: recompute P, form dS and the spread-gradient term, write P and
-// dS as bf16 into the swizzled [i][j] tiles.  `chunk0` is the index of the first 16-byte chunk (8 keys).
-template <bool MASKED, int FORM>
-__device__ __forceinline__ void ga_bwd_chunk(uint32_t t_s, uint32_t t_dp, const float4 *ka, const float4 *kc, const float *kb,
-                                             const GaBwdRow &rw, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
-                                             f2_t &dbeta2, uint8_t *p_tile, uint8_t *ds_tile, int r, int chunk0, uint64_t *gate,
-                                             uint32_t gate_parity) {
-    uint32_t sv[16], dpv[16];
-    tmem_ld16(t_s, sv);
-    tmem_ld16(t_dp, dpv);
+// Stages the per-query inputs of one query tile.  Executed by the 128 threads of warps 0..3 (thread = query).
+__device__ __forceinline__ void ga_stage_rows(GaQueryRows &rw, int tid, bool ok, float x, float y, float z, float l2, float dsum) {
+    float *a = reinterpret_cast<float *>(&rw.qa[tid >> 1]);
+    float *c = reinterpret_cast<float *>(&rw.qc[tid >> 1]);
+    a[tid & 1] = x;
+    a[2 + (tid & 1)] = y;
+    c[tid & 1] = z;
+    c[2 + (tid & 1)] = x * x + y * y + z * z;
+    reinterpret_cast<float *>(&rw.l2[tid >> 1])[tid & 1] = l2;
+    reinterpret_cast<float *>(&rw.dsum[tid >> 1])[tid & 1] = dsum;
+    rw.qb[tid] = ok ? 0.f : -INFINITY;
+    float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded queries carry 0
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) {
+        n += __shfl_xor_sync(0xffffffffu, n, off);
+        sx += __shfl_xor_sync(0xffffffffu, sx, off);
+        sy += __shfl_xor_sync(0xffffffffu, sy, off);
+        sz += __shfl_xor_sync(0xffffffffu, sz, off);
+    }
+    const float inv = n > 0.f ? 1.f / n : 0.f;
+    const float cx = sx * inv, cy = sy * inv, cz = sz * inv;
+    float d2 = ok ? (x - cx) * (x - cx) + (y - cy) * (y - cy) + (z - cz) * (z - cz) : 0.f;
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) d2 = fmaxf(d2, __shfl_xor_sync(0xffffffffu, d2, off));
+    if ((tid & 15) == 0) rw.sph[tid >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
+}
+
+// 16 query columns (8 pairs) of one key row: recompute P, form dS and the spread-gradient term.  sv / dpv hold the
+// raw S^T and dP^T values of the thread's 32 columns of this pass, of which this call takes OFF .. OFF + 15; the
+// results come back as bf16 pairs in pw / dw [POFF .. POFF + 7].  `p0` is the index of the first of the 8 query
+// pairs inside the tile's row arrays.
+// MASKED: the key tile or the query tile holds a padded token (validity is then applied by selection, so whatever
+// the padding holds, Inf or NaN included, never reaches a result).  `far` (warp-uniform): the 16 queries are too far
+// from the warp's keys for R to count.
+template <bool MASKED, int FORM, int OFF>
+__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], bool far, const GaQueryRows &rw, int p0,
+                                             const GaBwdKey &key, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
+                                             f2_t &dbeta2, uint32_t (&pw)[16], uint32_t (&dw)[16]) {
+    constexpr int POFF = OFF / 2;
     const f2_t one2 = f2_pack(1.f, 1.f);
+    if (far && FORM == 1 && fm.far_masked) {  // every pair of the group is outside the RBF window: P = 0
 #pragma unroll
-    for (int g = 0; g < 2; ++g) {  // 8 keys = one 16-byte chunk
-        f2_t arg[4], rb[4];
+        for (int e = 0; e < 8; ++e) pw[POFF + e] = dw[POFF + e] = 0u;
+        return;
+    }
+    f2_t arg[8], rb[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float4 a = ka[g * 4 + e], k4 = kc[g * 4 + e];
-            f2_t d2 = f2_fma(rw.qz2, f2_pack(k4.x, k4.y), f2_pack(k4.z, k4.w));
-            d2 = f2_fma(rw.qy2, f2_pack(a.z, a.w), d2);
-            d2 = f2_fma(rw.qx2, f2_pack(a.x, a.y), d2);
-            arg[e] = f2_fma(d2, crbf2, rw.cqn2);  // c_rbf * d^2
+    for (int e = 0; e < 8; ++e) arg[e] = rb[e] = 0ull;
+    if (!far) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float4 a = rw.qa[p0 + e], q4 = rw.qc[p0 + e];
+            f2_t d2 = f2_fma(key.kz2, f2_pack(q4.x, q4.y), f2_pack(q4.z, q4.w));
+            d2 = f2_fma(key.ky2, f2_pack(a.z, a.w), d2);
+            d2 = f2_fma(key.kx2, f2_pack(a.x, a.y), d2);
+            arg[e] = f2_fma(d2, crbf2, key.ckn2);  // c_rbf * d^2
         }
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 8; ++e) {
             float a0, a1;
             f2_unpack(arg[e], a0, a1);
             if (FORM == 1) {
                 a0 = fminf(a0, 0.f);
                 a1 = fminf(a1, 0.f);
+                arg[e] = f2_pack(a0, a1);
             }
             rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
         }
-        if (g == 0) tmem_wait_ld();
-        uint32_t pw[4], dw[4];
-        f2_t x[4];
+    }
+    f2_t x[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
-            const f2_t t2 = f2_mul(s_raw, cs2);
-            f2_t sr;
-            if (FORM == 0) {
-                sr = f2_fma(t2, rb[e], t2);
+    for (int e = 0; e < 8; ++e) {
+        const f2_t s_raw = f2_pack(__uint_as_float(sv[OFF + 2 * e]), __uint_as_float(sv[OFF + 2 * e + 1]));
+        const f2_t t2 = f2_mul(s_raw, cs2);
+        f2_t sr;
+        if (FORM == 0) {
+            sr = far ? t2 : f2_fma(t2, rb[e], t2);
+        } else {
+            float t0, t1, r0, r1;
+            f2_unpack(t2, t0, t1);
+            f2_unpack(rb[e], r0, r1);  // 0 for a far group
+            const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
+            const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
+            sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
+        }
+        const float2 l = rw.l2[p0 + e];
+        x[e] = f2_sub(sr, f2_pack(l.x, l.y));
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        float a0, a1;
+        f2_unpack(x[e], a0, a1);
+        float p0v = ex2_approx(a0), p1v = ex2_approx(a1);  // P
+        if (MASKED) {
+            const float2 b = *reinterpret_cast<const float2 *>(&rw.qb[2 * (p0 + e)]);
+            p0v = (key.k_ok && b.x == 0.f) ? p0v : 0.f;
+            p1v = (key.k_ok && b.y == 0.f) ? p1v : 0.f;
+        }
+        x[e] = f2_pack(p0v, p1v);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const f2_t s_raw = f2_pack(__uint_as_float(sv[OFF + 2 * e]), __uint_as_float(sv[OFF + 2 * e + 1]));
+        const f2_t dp = f2_pack(__uint_as_float(dpv[OFF + 2 * e]), __uint_as_float(dpv[OFF + 2 * e + 1]));
+        const float2 dd = rw.dsum[p0 + e];
+        f2_t dsr = f2_mul(x[e], f2_sub(dp, f2_pack(dd.x, dd.y)));
+        float p0v, p1v;
+        f2_unpack(x[e], p0v, p1v);
+        if (MASKED || FORM == 1) {  // P = 0 (padding, or a pair outside the window): nothing flows back, whatever dP holds
+            float g0, g1;
+            f2_unpack(dsr, g0, g1);
+            dsr = f2_pack(p0v != 0.f ? g0 : 0.f, p1v != 0.f ? g1 : 0.f);
+        }
+        f2_t ds;
+        if (FORM == 0) {
+            if (far) {
+                ds = f2_mul(dsr, scale2);
             } else {
-                float t0, t1, r0, r1;
-                f2_unpack(t2, t0, t1);
-                f2_unpack(rb[e], r0, r1);
-                const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
-                const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
-                sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
-            }
-            if (MASKED) sr = f2_add(sr, *reinterpret_cast<const f2_t *>(kb + g * 8 + 2 * e));
-            x[e] = f2_sub(sr, rw.l22);
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            float a0, a1;
-            f2_unpack(x[e], a0, a1);
-            x[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // P
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const f2_t s_raw = f2_pack(__uint_as_float(sv[g * 8 + 2 * e]), __uint_as_float(sv[g * 8 + 2 * e + 1]));
-            const f2_t dp = f2_pack(__uint_as_float(dpv[g * 8 + 2 * e]), __uint_as_float(dpv[g * 8 + 2 * e + 1]));
-            const f2_t dsr = f2_mul(x[e], f2_sub(dp, rw.dsum2));
-            f2_t ds;
-            if (FORM == 0) {
                 ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
-                dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
-            } else {  // dS = dSR (1 + beta Rn sign(S)),  dR = dSR |S| 2 beta / (max - min),  dbeta = sum dSR Rn |S|
-                float s0, s1, r0, r1, g0, g1, a0, a1;
-                f2_unpack(s_raw, s0, s1);
-                f2_unpack(rb[e], r0, r1);
-                f2_unpack(dsr, g0, g1);
-                f2_unpack(arg[e], a0, a1);
-                const float rn0 = fmaf(r0, fm.rn_a, fm.rn_b), rn1 = fmaf(r1, fm.rn_a, fm.rn_b);
-                const float sg0 = (s0 > 0.f) ? 1.f : ((s0 < 0.f) ? -1.f : 0.f), sg1 = (s1 > 0.f) ? 1.f : ((s1 < 0.f) ? -1.f : 0.f);
-                float sc0, sc1;
-                f2_unpack(scale2, sc0, sc1);
-                const float f0 = s0 != 0.f ? fmaf(fm.beta * rn0, sg0, 1.f) : 0.f, f1 = s1 != 0.f ? fmaf(fm.beta * rn1, sg1, 1.f) : 0.f;
-                ds = f2_pack(g0 * sc0 * f0, g1 * sc1 * f1);
-                dsig2 = f2_fma(f2_pack(g0 * fabsf(s0) * r0, g1 * fabsf(s1) * r1), f2_pack(fminf(a0, 0.f), fminf(a1, 0.f)), dsig2);
-                dbeta2 = f2_add(dbeta2, f2_pack(g0 * rn0 * fabsf(s0), g1 * rn1 * fabsf(s1)));
+                f2_t w = f2_mul(f2_mul(dsr, s_raw), rb[e]);
+                if (MASKED) {  // S of a padded pair may be Inf / NaN: keep it out of the sum
+                    float w0, w1;
+                    f2_unpack(w, w0, w1);
+                    w = f2_pack(p0v != 0.f ? w0 : 0.f, p1v != 0.f ? w1 : 0.f);
+                }
+                dsig2 = f2_fma(w, arg[e], dsig2);
             }
-            float p0, p1, d0, d1;
-            f2_unpack(x[e], p0, p1);
-            f2_unpack(ds, d0, d1);
-            pw[e] = pack_bf16x2(p0, p1);
-            dw[e] = pack_bf16x2(d0, d1);
+        } else {  // dS = dSR (1 + beta Rn sign(S)),  dR = dSR |S| 2 beta / (max - min),  dbeta = sum dSR Rn |S|
+            float s0, s1, r0, r1, g0, g1, a0, a1;
+            f2_unpack(s_raw, s0, s1);
+            f2_unpack(dsr, g0, g1);
+            f2_unpack(rb[e], r0, r1);
+            f2_unpack(arg[e], a0, a1);
+            if (MASKED) {
+                s0 = p0v != 0.f ? s0 : 0.f;
+                s1 = p1v != 0.f ? s1 : 0.f;
+            }
+            const float rn0 = fmaf(r0, fm.rn_a, fm.rn_b), rn1 = fmaf(r1, fm.rn_a, fm.rn_b);
+            const float sg0 = (s0 > 0.f) ? 1.f : ((s0 < 0.f) ? -1.f : 0.f), sg1 = (s1 > 0.f) ? 1.f : ((s1 < 0.f) ? -1.f : 0.f);
+            float sc0, sc1;
+            f2_unpack(scale2, sc0, sc1);
+            const float f0 = s0 != 0.f ? fmaf(fm.beta * rn0, sg0, 1.f) : 0.f, f1 = s1 != 0.f ? fmaf(fm.beta * rn1, sg1, 1.f) : 0.f;
+            ds = f2_pack(g0 * sc0 * f0, g1 * sc1 * f1);
+            dsig2 = f2_fma(f2_pack(g0 * fabsf(s0) * r0, g1 * fabsf(s1) * r1), f2_pack(a0, a1), dsig2);  // r = 0 for a far group
+            dbeta2 = f2_add(dbeta2, f2_pack(g0 * rn0 * fabsf(s0), g1 * rn1 * fabsf(s1)));
         }
-        // the previous tile's dV / dK MMAs read the P and dS tiles: no store before they have completed
-        if (gate != nullptr && g == 0) mbar_wait_timed(gate, gate_parity);
-        const int chunk = chunk0 + g;
-        const uint32_t off = (chunk >> 3) * GA_TILE_BYTES + sw128_offset(r, chunk & 7);
-        *reinterpret_cast<uint4 *>(p_tile + off) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-        *reinterpret_cast<uint4 *>(ds_tile + off) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+        float d0, d1;
+        f2_unpack(ds, d0, d1);
+        pw[POFF + e] = pack_bf16x2(p0v, p1v);
+        dw[POFF + e] = pack_bf16x2(d0, d1);
     }
 }
 
@@ -203,174 +273,189 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     GaBwdSmem &sm = *reinterpret_cast<GaBwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
-    const int qtr = (warp >> 2) & 3;              // which 32 key columns / which 16 output columns
-    const int r = (warp & 3) * 32 + lane;         // row inside a tile = TMEM lane
+    const int half = (warp >> 2) & 1;             // which 64 query columns / which 32 output columns
+    const int r = (warp & 3) * 32 + lane;         // key row inside the tile = TMEM lane
+    const int N = p.N;
+    const int tiles_all = (N + GA_BM - 1) / GA_BM;
     int zh_local = blockIdx.y;
-    if (p.order) {  // samples in the given order (longest first): neighbouring CTAs get similar amounts of work
+    if (p.use_order) {  // samples longest first
         const int zp = zh_local / p.H;
-        zh_local = p.order[zp] * p.H + (zh_local - zp * p.H);
+        zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
     }
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
     const int j0 = blockIdx.x * GA_BN;
-    const int N = p.N;
     const float *cz = p.coords + (size_t)z * N * 3;
     const uint8_t *vz = p.valid ? p.valid + (size_t)z * N : nullptr;
 
-    // ---- this CTA's keys ---------------------------------------------------------------------------
-    const int jrow = j0 + r;  // the key whose dK / dV row this thread writes (16 of its 64 columns)
+    // ---- this CTA's keys, the live query tiles of the range ------------------------------------------
+    const int jrow = j0 + r;  // the key whose dK / dV row this thread writes (32 of its 64 columns)
     const bool k_ok = is_math && jrow < N && (vz ? vz[jrow] != 0 : true);
-    if (tid == 0) {
-        sm.first_k = 0x7fffffff;
-        sm.has_hole = 0;
-    }
-    // ---- query tiles with at least one valid query --------------------------------------------------
-    const int all_tiles = (N + GA_BM - 1) / GA_BM;
-    for (int t = warp; t < all_tiles; t += GA_BWD_THREADS / 32) {
-        bool any = false;
-        for (int i = t * GA_BM + lane; i < min(N, (t + 1) * GA_BM); i += 32) any |= vz ? (vz[i] != 0) : true;
-        any = __any_sync(0xffffffffu, any);
-        if (lane == 0) sm.tiles[t] = any ? 1 : 0;
-    }
-    __syncthreads();
-    if (is_math && qtr == 0) {
-        if (k_ok) atomicMin(&sm.first_k, r);
-        else sm.has_hole = 1;
-    }
-    const bool cta_has_key = __syncthreads_or(k_ok ? 1 : 0) != 0;
-    if (tid == 0) {
-        int n = 0;
-        for (int t = 0; t < all_tiles; ++t)
-            if (sm.tiles[t]) sm.tiles[n++] = (uint16_t)t;
-        sm.ntiles = n;
-    }
-    __syncthreads();
-    const int nt = sm.ntiles;
-
-    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + qtr * 16;
-    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + qtr * 16;
-    if (!cta_has_key || nt == 0) {
+    const int k_info = p.plan ? ga_plan_info(p.plan, p.Z, N, z)[j0 / GA_BN] : ga_plan_info_unmasked(N, j0 / GA_BN);
+    const int *tl = p.plan ? ga_plan_tiles(p.plan, p.Z, N, z) : nullptr;
+    const int nt_all = p.plan ? ga_plan_count(p.plan, p.Z)[z] : tiles_all;
+    auto word_g = [&](int t) -> int { return tl ? tl[t] : (ga_plan_info_unmasked(N, t) | t); };
+    // the list is ascending: the tiles of [qt_begin, qt_end) are a contiguous run of it
+    int first = 0, nt = 0;
+    while (first < nt_all && (word_g(first) & 0x7fff) < p.qt_begin) ++first;
+    while (first + nt < nt_all && (word_g(first + nt) & 0x7fff) < p.qt_end) ++nt;
+    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + half * 32;
+    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + half * 32;
+    if (k_info < 0 || nt == 0) {  // no valid key here, or no query to hear from: zeros
         if (is_math && jrow < N) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 8; ++c) {
                 reinterpret_cast<float4 *>(dk_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
                 reinterpret_cast<float4 *>(dv_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
         }
         return;
     }
+    for (int t = tid; t < nt; t += GA_BWD_THREADS) sm.tiles[t] = (uint16_t)word_g(first + t);
+    const bool key_hole = (k_info & 0x8000) != 0;
     // origin of the centred coordinates: the first valid key of this tile
-    const int ok_row = j0 + sm.first_k;
+    const int ok_row = j0 + (k_info & 0x7f);
     const float orx = cz[ok_row * 3], ory = cz[ok_row * 3 + 1], orz = cz[ok_row * 3 + 2];
-    const bool has_hole = sm.has_hole != 0;
-    if (is_math && qtr == 0) {  // stage the centred keys
-        const float x = k_ok ? cz[jrow * 3] - orx : 0.f, y = k_ok ? cz[jrow * 3 + 1] - ory : 0.f, zc = k_ok ? cz[jrow * 3 + 2] - orz : 0.f;
-        float *a = reinterpret_cast<float *>(&sm.ka[r >> 1]);
-        float *c = reinterpret_cast<float *>(&sm.kc[r >> 1]);
-        a[r & 1] = x;
-        a[2 + (r & 1)] = y;
-        c[r & 1] = zc;
-        c[2 + (r & 1)] = x * x + y * y + zc * zc;
-        sm.kb[r] = k_ok ? 0.f : -INFINITY;
-    }
+    volatile int *abort_flag = &sm.abort;
 
     // ---- set-up ------------------------------------------------------------------------------------
     if (!is_math) {
-        tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
-        tmem_relinquish();
         if (lane == 0) {
             mbar_init(&sm.bar_kv, 1);
             mbar_init(&sm.bar_qdo[0], 1);
             mbar_init(&sm.bar_qdo[1], 1);
             mbar_init(&sm.bar_sp, 1);
-            mbar_init(&sm.bar_g, 1);
             mbar_init(&sm.bar_vk, 1);
+            mbar_init(&sm.bar_dq, 1);
+            mbar_init(&sm.bar_spfree, GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_pds, GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_dqr, GA_BWD_MATH_THREADS);
+#pragma unroll
+            for (int b = 0; b < GA_ROW_BUFS; ++b) mbar_init(&sm.bar_rows[b], GA_BM);
             mbar_fence_init();
             fence_proxy_async();
-            tma_prefetch_desc(&map_q);
-            tma_prefetch_desc(&map_k);
-            tma_prefetch_desc(&map_v);
-            tma_prefetch_desc(&map_do);
+            // the first loads leave before anything else is set up
+            mbar_expect_tx(&sm.bar_kv, 2 * GA_TILE_BYTES);
+            tma_load_3d(sm.k, &map_k, 0, j0, zh_local, &sm.bar_kv);
+            tma_load_3d(sm.v, &map_v, 0, j0, zh_local, &sm.bar_kv);
+            for (int t = 0; t < 2 && t < nt; ++t) {
+                const int i0 = (word_g(first + t) & 0x7fff) * GA_BM;
+                mbar_expect_tx(&sm.bar_qdo[t], 2 * GA_TILE_BYTES);
+                tma_load_3d(sm.q[t], &map_q, 0, i0, zh_local, &sm.bar_qdo[t]);
+                tma_load_3d(sm.dout[t], &map_do, 0, i0, zh_local, &sm.bar_qdo[t]);
+            }
+            sm.abort = 0;
         }
+        __syncwarp();
+        tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
+        tmem_relinquish();
+    }
+    // per-query inputs of a tile: thread tid < 128 loads query tile*128 + tid
+    auto row_inputs = [&](int tile, bool &ok, float &x, float &y, float &zc, float &l2, float &dsum) {
+        const int i = tile * GA_BM + tid;
+        ok = i < N && (vz ? vz[i] != 0 : true);
+        x = y = zc = 0.f;
+        l2 = INFINITY;  // +inf: P = 0 for a padded query
+        dsum = 0.f;
+        if (ok) {
+            x = cz[i * 3] - orx;
+            y = cz[i * 3 + 1] - ory;
+            zc = cz[i * 3 + 2] - orz;
+            const float lse = p.lse[(size_t)zh * N + i];
+            l2 = lse == -INFINITY ? INFINITY : lse * 1.4426950408889634f;  // a row without any valid pair: P = 0
+            dsum = p.dsum[(size_t)zh_local * N + i];
+        }
+    };
+    if (tid < GA_BM) {
+        bool ok;
+        float x, y, zc, l2, dsum;
+        row_inputs(word_g(first) & 0x7fff, ok, x, y, zc, l2, dsum);
+        ga_stage_rows(sm.rows[0], tid, ok, x, y, zc, l2, dsum);
     }
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();  // barriers initialised, TMEM allocated, tile list and the first tile's row inputs in place
     tc_fence_after();
+    if (tid < GA_BM) mbar_arrive(&sm.bar_rows[0]);
+    auto tile_word = [&](int t) -> int { return (int)sm.tiles[t]; };
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_dv = tmem + 256, tm_dk = tmem + 320, tm_dq = tmem + 384;
+    const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_p = tmem + 256, tm_dv = tmem + 320, tm_dk = tmem + 384, tm_dq = tmem + 448;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
     if (!is_math) {
         // ================================ producer warp ==============================================
         if (lane == 0) {
-            const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v), p_addr = smem_u32(sm.p), ds_addr = smem_u32(sm.ds);
+            const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
             constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, 128, false, false);
-            constexpr uint32_t IDESC_TT = umma_idesc_bf16(128, GA_D, true, true);   // dV, dK
-            constexpr uint32_t IDESC_DQ = umma_idesc_bf16(128, GA_D, false, true);  // dQ
-            auto load_qdo = [&](int buf, int tile) {
-                mbar_expect_tx(&sm.bar_qdo[buf], 2 * GA_TILE_BYTES);
-                tma_load_3d(sm.q[buf], &map_q, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
-                tma_load_3d(sm.dout[buf], &map_do, 0, tile * GA_BM, zh_local, &sm.bar_qdo[buf]);
+            constexpr uint32_t IDESC_KN = umma_idesc_bf16(128, GA_D, false, true);  // dV (A in TMEM), dK: A K-major, B MN-major
+            constexpr uint32_t IDESC_NN = umma_idesc_bf16(128, GA_D, true, true);   // dQ: A MN-major, B MN-major
+            auto load_qdo = [&](int t) {
+                const int b = t & 1;
+                const int i0 = (tile_word(t) & 0x7fff) * GA_BM;
+                mbar_expect_tx(&sm.bar_qdo[b], 2 * GA_TILE_BYTES);
+                tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
+                tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
             };
-            auto issue_s_dp = [&](int buf) {
-                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
+            auto issue_s_dp = [&](int b) {  // S^T = K Q^T, dP^T = V dO^T: 4 + 4 MMAs of K = 16 over d = 64
+                const uint32_t q_addr = smem_u32(sm.q[b]), do_addr = smem_u32(sm.dout[b]);
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_s, umma_desc_sw128(q_addr + kk * 32, 16, 1024), umma_desc_sw128(k_addr + kk * 32, 16, 1024),
+                    umma_ss(tm_s, umma_desc_sw128(k_addr + kk * 32, 16, 1024), umma_desc_sw128(q_addr + kk * 32, 16, 1024),
                             IDESC_SP, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_dp, umma_desc_sw128(do_addr + kk * 32, 16, 1024), umma_desc_sw128(v_addr + kk * 32, 16, 1024),
+                    umma_ss(tm_dp, umma_desc_sw128(v_addr + kk * 32, 16, 1024), umma_desc_sw128(do_addr + kk * 32, 16, 1024),
                             IDESC_SP, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_sp);
             };
-            auto issue_dq = [&]() {  // the math warps wait for this one; K = 16 keys per step
+            auto issue_dv_dk = [&](int b, bool first_tile) {  // K = 16 queries per step
+                const uint32_t q_addr = smem_u32(sm.q[b]), do_addr = smem_u32(sm.dout[b]), ds_addr = smem_u32(sm.ds[b]);
 #pragma unroll
-                for (int kk = 0; kk < GA_BN / 16; ++kk)
-                    umma_ss(tm_dq, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                            umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_DQ, kk > 0 ? 1u : 0u);
-                umma_commit(&sm.bar_g);
-            };
-            auto issue_dv_dk = [&](int buf, bool first) {  // K = 16 query rows per step: 2 KiB down the [i][j] tiles
-                const uint32_t q_addr = smem_u32(sm.q[buf]), do_addr = smem_u32(sm.dout[buf]);
+                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
+                    umma_ts(tm_dv, tm_p + kk * 8, umma_desc_sw128(do_addr + kk * 2048, 0, 1024), IDESC_KN,
+                            (first_tile && kk == 0) ? 0u : 1u);
 #pragma unroll
-                for (int kk = 0; kk < GA_BM / 16; ++kk) {
-                    umma_ss(tm_dv, umma_desc_sw128(p_addr + kk * 2048, GA_TILE_BYTES, 1024),
-                            umma_desc_sw128(do_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
-                    umma_ss(tm_dk, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024),
-                            umma_desc_sw128(q_addr + kk * 2048, 0, 1024), IDESC_TT, (first && kk == 0) ? 0u : 1u);
-                }
+                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dK += dS^T Q: dS^T advances 32 B inside the swizzled row
+                    umma_ss(tm_dk, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                            umma_desc_sw128(q_addr + kk * 2048, 0, 1024), IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
                 umma_commit(&sm.bar_vk);
             };
-            mbar_expect_tx(&sm.bar_kv, 2 * GA_TILE_BYTES);
-            tma_load_3d(sm.k, &map_k, 0, j0, zh_local, &sm.bar_kv);
-            tma_load_3d(sm.v, &map_v, 0, j0, zh_local, &sm.bar_kv);
-            load_qdo(0, sm.tiles[0]);
-            if (nt > 1) load_qdo(1, sm.tiles[1]);
-            mbar_wait_timed(&sm.bar_kv, 0);
-            mbar_wait_timed(&sm.bar_qdo[0], 0);
-            tc_fence_after();
-            issue_s_dp(0);
-            for (int t = 0; t < nt; ++t) {
-                const int buf = t & 1;
-                const uint32_t par = (uint32_t)(t & 1);
-                mbar_wait_timed(&sm.bar_pds, par);  // P, dS(t) written; S, dP(t) consumed
-                if (t > 0) mbar_wait_timed(&sm.bar_dqr, par ^ 1);  // dQ(t-1) has been read out of TMEM
+            auto issue_dq = [&](int b) {  // dQ = dS K: K = 16 keys per step, 2 KiB down the dS^T tile (M = queries: two sub-tiles)
+                const uint32_t ds_addr = smem_u32(sm.ds[b]);
+#pragma unroll
+                for (int kk = 0; kk < GA_BN / 16; ++kk)
+                    umma_ss(tm_dq, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024),
+                            umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_NN, kk > 0 ? 1u : 0u);
+                umma_commit(&sm.bar_dq);
+            };
+            bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag);
+            if (ok) {
                 tc_fence_after();
-                // dQ(t) first (the math warps stage it next), then the next tile's S and dP so that its element-wise
-                // stage can start while dV / dK(t) are still running; P and dS(t) stay untouched until bar_vk(t)
-                issue_dq();
-                if (t + 1 < nt) {
-                    mbar_wait_timed(&sm.bar_qdo[buf ^ 1], (uint32_t)(((t + 1) >> 1) & 1));
-                    issue_s_dp(buf ^ 1);
+                issue_s_dp(0);
+            }
+            for (int t = 0; ok && t < nt; ++t) {
+                const int b = t & 1;
+                const uint32_t par = (uint32_t)(t & 1);
+                if (t + 1 < nt) {  // every math thread holds its S^T, dP^T(t) in registers: compute the next tile's
+                    if (!(ok = mbar_wait_abortable(&sm.bar_spfree, par, abort_flag))) break;
+                    if (!(ok = mbar_wait_abortable(&sm.bar_qdo[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
+                    tc_fence_after();
+                    issue_s_dp(b ^ 1);
                 }
-                issue_dv_dk(buf, t == 0);
-                if (t + 2 < nt) {  // Q / dO buffer `buf` is free once S, dP(t) and the gradient MMAs(t) are done
-                    mbar_wait_timed(&sm.bar_vk, par);
-                    load_qdo(buf, sm.tiles[t + 2]);
+                if (!(ok = mbar_wait_abortable(&sm.bar_pds, par, abort_flag))) break;  // P^T(t) in TMEM, dS^T(t) in shared memory
+                tc_fence_after();
+                issue_dv_dk(b, t == 0);
+                if (t > 0 && !(ok = mbar_wait_abortable(&sm.bar_dqr, par ^ 1, abort_flag))) break;  // dQ(t-1) read out of TMEM
+                tc_fence_after();
+                issue_dq(b);
+                if (t + 2 < nt) {  // Q / dO buffer b is free once S^T, dP^T(t) and dV, dK(t) are done
+                    if (!(ok = mbar_wait_abortable(&sm.bar_vk, par, abort_flag))) break;
+                    load_qdo(t + 2);
                 }
+            }
+            if (!ok) {  // gave up: let the copies already issued land before the CTA exits (bounded)
+                mbar_wait_bounded(&sm.bar_kv, 0, 1u << 12);
+                mbar_wait_bounded(&sm.bar_qdo[0], 0, 1u << 12);
+                mbar_wait_bounded(&sm.bar_qdo[1], 0, 1u << 12);
             }
         }
         __syncwarp();
@@ -381,92 +466,154 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float c_s = p.scale * 1.4426950408889634f;
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cs2 = f2_pack(c_s, c_s), scale2 = f2_pack(p.scale, p.scale);
         f2_t dsig2 = 0ull, dbeta2 = 0ull;
-        GaForm fm = {0.f, 0.f, 0.f, 0.f, 1.f};
-        if (p.form == 1) {
-            fm.beta = p.beta[h];
-            fm.rn_a = 2.f / (p.max_rbf - p.min_rbf);
-            fm.rn_b = -2.f * p.min_rbf / (p.max_rbf - p.min_rbf) - 1.f;
-            fm.rmin = p.min_rbf;
-            fm.rmax = p.max_rbf;
+        GaForm fm;
+        ga_form_setup(fm, p.form, p.form == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
+        GaBwdKey key;
+        float kcx = 0.f, kcy = 0.f, kcz = 0.f;
+        if (k_ok) {
+            kcx = cz[jrow * 3] - orx;
+            kcy = cz[jrow * 3 + 1] - ory;
+            kcz = cz[jrow * 3 + 2] - orz;
         }
-
-        float qcx, qcy, qcz, l2, dsum;
-        auto load_row = [&](int tile) {
-            const int row = tile * GA_BM + r;
-            const bool q_ok = row < N && (vz ? vz[row] != 0 : true);
-            qcx = qcy = qcz = 0.f;
-            l2 = INFINITY;  // +inf: P = 0 for a padded query
-            dsum = 0.f;
-            if (q_ok) {
-                qcx = cz[row * 3] - orx;
-                qcy = cz[row * 3 + 1] - ory;
-                qcz = cz[row * 3 + 2] - orz;
-                const float lse = p.lse[(size_t)zh * N + row];
-                l2 = lse == -INFINITY ? INFINITY : lse * 1.4426950408889634f;  // a row without any valid pair: P = 0
-                dsum = p.dsum[(size_t)zh_local * N + row];
+        key.kx2 = f2_pack(-2.f * kcx, -2.f * kcx);
+        key.ky2 = f2_pack(-2.f * kcy, -2.f * kcy);
+        key.kz2 = f2_pack(-2.f * kcz, -2.f * kcz);
+        const float ckn = c_rbf * (kcx * kcx + kcy * kcy + kcz * kcz);
+        key.ckn2 = f2_pack(ckn, ckn);
+        key.k_ok = k_ok;
+        // bounding sphere of the warp's valid keys; wk_reach = (distance beyond which R does not count) + radius
+        float wkx, wky, wkz, wk_reach;
+        {
+            float n = k_ok ? 1.f : 0.f, sx = kcx, sy = kcy, sz = kcz;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                n += __shfl_xor_sync(0xffffffffu, n, off);
+                sx += __shfl_xor_sync(0xffffffffu, sx, off);
+                sy += __shfl_xor_sync(0xffffffffu, sy, off);
+                sz += __shfl_xor_sync(0xffffffffu, sz, off);
+            }
+            const float inv = n > 0.f ? 1.f / n : 0.f;
+            wkx = sx * inv;
+            wky = sy * inv;
+            wkz = sz * inv;
+            float d2 = k_ok ? (kcx - wkx) * (kcx - wkx) + (kcy - wky) * (kcy - wky) + (kcz - wkz) * (kcz - wkz) : 0.f;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) d2 = fmaxf(d2, __shfl_xor_sync(0xffffffffu, d2, off));
+            wk_reach = fm.far_cut * sig + sqrtf(d2) * 1.0001f + 1e-4f;
+            if (!p.far_skip || !(fm.far_cut < INFINITY)) wk_reach = -INFINITY;  // test off
+        }
+        // `ok` is kept uniform across the warp: tcgen05.ld / st need all 32 lanes
+        bool ok = true;
+        auto wait_w = [&](uint64_t *bar, uint32_t parity) -> bool {
+            return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
+        };
+        auto read_dq = [&](int t) {  // dQ tile of query tile t: TMEM -> registers -> vector reductions into the global fp32 dQ
+            uint32_t v[32];
+            tmem_ld32(tm_dq + lane_base + half * 32, v);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sm.bar_dqr);
+            const int row = (tile_word(t) & 0x7fff) * GA_BM + r;
+            if (row < N) {
+                float *dst = p.dq + ((size_t)zh * N + row) * GA_D + half * 32;
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                    red_add_v4(dst + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
+                               __uint_as_float(v[e + 3]));
             }
         };
-        load_row(sm.tiles[0]);
-        for (int t = 0; t < nt; ++t) {
+
+        for (int t = 0; ok && t < nt; ++t) {
             const uint32_t par = (uint32_t)(t & 1);
-            const int i0 = sm.tiles[t] * GA_BM;
-            // per-row inputs of this query tile (loaded during the previous tile, see the end of the loop body)
-            GaBwdRow rw;
-            rw.qx2 = f2_pack(-2.f * qcx, -2.f * qcx);
-            rw.qy2 = f2_pack(-2.f * qcy, -2.f * qcy);
-            rw.qz2 = f2_pack(-2.f * qcz, -2.f * qcz);
-            const float cqn = c_rbf * (qcx * qcx + qcy * qcy + qcz * qcz);
-            rw.cqn2 = f2_pack(cqn, cqn);
-            rw.l22 = f2_pack(l2, l2);
-            rw.dsum2 = f2_pack(dsum, dsum);
-            mbar_wait_timed(&sm.bar_sp, par);
+            const int rbuf = t % GA_ROW_BUFS;
+            const bool masked = key_hole || (tile_word(t) & 0x8000) != 0;
+            // per-query inputs of the next tile: issue the global loads now, stage them after the first pass
+            bool n_ok = false;
+            float nx = 0.f, ny = 0.f, nz = 0.f, nl2 = INFINITY, nds = 0.f;
+            const bool stage_next = t + 1 < nt && tid < GA_BM;
+            if (stage_next) row_inputs(tile_word(t + 1) & 0x7fff, n_ok, nx, ny, nz, nl2, nds);
+            if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T(t) have landed in TMEM
             tc_fence_after();
-#define PAI_GA_BWD(MASKED, FORM)                                                                                             \
-    _Pragma("unroll") for (int c = 0; c < 2; ++c) ga_bwd_chunk<MASKED, FORM>(                                                \
-        tm_s + lane_base + qtr * 32 + c * 16, tm_dp + lane_base + qtr * 32 + c * 16, &sm.ka[qtr * 16 + c * 8],               \
-        &sm.kc[qtr * 16 + c * 8], &sm.kb[qtr * 32 + c * 16], rw, crbf2, cs2, scale2, fm, dsig2, dbeta2, sm.p, sm.ds, r,       \
-        qtr * 4 + c * 2, (t > 0 && c == 0) ? &sm.bar_vk : nullptr, par ^ 1)
-            if (p.form == 0) {
-                if (has_hole) { PAI_GA_BWD(true, 0); } else { PAI_GA_BWD(false, 0); }
-            } else {
-                if (has_hole) { PAI_GA_BWD(true, 1); } else { PAI_GA_BWD(false, 1); }
+            const GaQueryRows &rw = sm.rows[rbuf];
+            uint8_t *ds_tile = sm.ds[t & 1];
+            auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
+                const float4 sp = rw.sph[g];
+                const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
+                const float reach = wk_reach + sp.w;
+                return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+            };
+#pragma unroll
+            for (int pass = 0; pass < 2; ++pass) {
+                const int col0 = half * 64 + pass * 32;  // first query column of this pass
+                uint32_t sv[32], dpv[32];
+                tmem_ld32(tm_s + lane_base + col0, sv);
+                tmem_ld32(tm_dp + lane_base + col0, dpv);
+                tmem_wait_ld();
+                if (pass == 1) {  // both passes are in registers: the accumulators may be overwritten
+                    tc_fence_before();
+                    mbar_arrive(&sm.bar_spfree);
+                } else {
+                    if (!(ok = wait_w(&sm.bar_rows[rbuf], (uint32_t)((t / GA_ROW_BUFS) & 1)))) break;
+                }
+                uint32_t pw[16], dw[16];
+                const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
+#define PAI_GA_BWD2(MASKED, FORM)                                                                                          \
+    do {                                                                                                                   \
+        ga_bwd_chunk<MASKED, FORM, 0>(sv, dpv, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);      \
+        ga_bwd_chunk<MASKED, FORM, 16>(sv, dpv, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
+    } while (0)
+                if (p.form == 0) {
+                    if (masked) PAI_GA_BWD2(true, 0); else PAI_GA_BWD2(false, 0);
+                } else {
+                    if (masked) PAI_GA_BWD2(true, 1); else PAI_GA_BWD2(false, 1);
+                }
+#undef PAI_GA_BWD2
+                // P^T(t-1) is read by dV(t-1), the dS^T buffer of tile t-2 by dK / dQ(t-2): no store before dV, dK(t-1)
+                // have completed (dQ(t-2) was read out by these very threads during tile t-1)
+                if (pass == 0 && t > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
+                tmem_st16(tm_p + lane_base + col0 / 2, pw);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {  // 8 queries = one 16-byte chunk of the swizzled key row
+                    const int chunk = col0 / 8 + c;
+                    *reinterpret_cast<uint4 *>(ds_tile + (chunk >> 3) * GA_TILE_BYTES + sw128_offset(r, chunk & 7)) =
+                        make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
+                }
+                if (pass == 0 && stage_next) {
+                    // buffer (t+1) % 3 was last read during tile t-2, which every thread has left (S^T(t) was only issued
+                    // after all of them had loaded the second pass of tile t-1)
+                    ga_stage_rows(sm.rows[(t + 1) % GA_ROW_BUFS], tid, n_ok, nx, ny, nz, nl2, nds);
+                    mbar_arrive(&sm.bar_rows[(t + 1) % GA_ROW_BUFS]);
+                }
             }
-#undef PAI_GA_BWD
-            fence_proxy_async();
+            if (!ok) break;
+            tmem_wait_st();
+            fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
             tc_fence_before();
             mbar_arrive(&sm.bar_pds);
-            if (t + 1 < nt) load_row(sm.tiles[t + 1]);  // the loads fly while the MMAs run
-            // dQ tile: TMEM -> registers -> vector reductions into the global fp32 dQ
-            mbar_wait_timed(&sm.bar_g, par);
-            tc_fence_after();
-            {
-                uint32_t v[16];
-                tmem_ld16(tm_dq + lane_base + qtr * 16, v);
-                tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(&sm.bar_dqr);
-                const int row = i0 + r;
-                if (row < N) {
-                    float *dst = p.dq + ((size_t)zh * N + row) * GA_D + qtr * 16;
-#pragma unroll
-                    for (int e = 0; e < 16; e += 4)
-                        red_add_v4(dst + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
-                                   __uint_as_float(v[e + 3]));
-                }
+            if (t > 0) {  // dQ(t-1) completed long ago: read it out now, off the tensor core's critical path
+                if (!(ok = wait_w(&sm.bar_dq, par ^ 1))) break;
+                tc_fence_after();
+                read_dq(t - 1);
             }
         }
 
-        // ---- epilogue: dV, dK rows of this key tile; dsigma -------------------------------------------
-        mbar_wait_timed(&sm.bar_vk, (uint32_t)((nt - 1) & 1));  // the last dV / dK accumulation has completed
-        tc_fence_after();
-        {
-            uint32_t a[16], b[16];
-            tmem_ld16(tm_dv + lane_base + qtr * 16, a);
-            tmem_ld16(tm_dk + lane_base + qtr * 16, b);
+        // ---- epilogue: the last dQ tile; dV, dK rows of this key tile; dsigma ------------------------------
+        if (ok) ok = wait_w(&sm.bar_dq, (uint32_t)((nt - 1) & 1));
+        if (ok) {
+            tc_fence_after();
+            read_dq(nt - 1);
+            ok = wait_w(&sm.bar_vk, (uint32_t)((nt - 1) & 1));  // the last dV / dK accumulation has completed
+        }
+        if (ok) {
+            tc_fence_after();
+            uint32_t a[32], b[32];
+            tmem_ld32(tm_dv + lane_base + half * 32, a);
+            tmem_ld32(tm_dk + lane_base + half * 32, b);
             tmem_wait_ld();
             if (jrow < N) {
 #pragma unroll
-                for (int e = 0; e < 16; e += 4) {
+                for (int e = 0; e < 32; e += 4) {
+                    // a padded key row holds exact zeros (its P and dS were selected to 0)
                     *reinterpret_cast<uint4 *>(dv_row + e) = make_uint4(a[e], a[e + 1], a[e + 2], a[e + 3]);
                     *reinterpret_cast<uint4 *>(dk_row + e) = make_uint4(b[e], b[e + 1], b[e + 2], b[e + 3]);
                 }
@@ -475,7 +622,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         float d0, d1, b0, b1;
         f2_unpack(dsig2, d0, d1);
         f2_unpack(dbeta2, b0, b1);
-        float dsig_acc = d0 + d1, dbeta_acc = b0 + b1;
+        float dsig_acc = ok ? d0 + d1 : 0.f, dbeta_acc = ok ? b0 + b1 : 0.f;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) {
             dsig_acc += __shfl_xor_sync(0xffffffffu, dsig_acc, off);
@@ -488,7 +635,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) {
+    if (tid == 0 && !sm.abort) {
         float tot = 0.f, totb = 0.f;
         for (int w = 0; w < GA_BWD_MATH_THREADS / 32; ++w) {
             tot += sm.dsig[w];

@@ -8,18 +8,46 @@
 namespace pai {
 
 // ---- time-bounded mbarrier wait ---------------------------------------------------------------
-// Gives up after ~0.1 s of SM clock and records the failure in the device status word; the caller
-// carries on (results are then garbage, the host sees the status), so no wait can hang the GPU.
-__device__ __forceinline__ bool mbar_wait_timed(uint64_t *bar, uint32_t parity) {
+// A wait gives up after about 0.1 s of SM clock (2e8 cycles), records PAI_ERR_DEVICE_WAIT_TIMEOUT in the
+// device status word and raises the CTA's abort flag (a word in shared memory).  Every wait of the CTA
+// polls that flag, so once one wait has expired all the others return at once: a stalled pipeline costs
+// one wait period per CTA, not one per wait.  A caller that gets `false` leaves its tile loop, issues no
+// further copy or MMA, skips its global stores and goes to the common exit (barrier, TMEM release).
+constexpr long long MBAR_WAIT_LIMIT_CYCLES = 200000000ll;
+
+__device__ __forceinline__ bool mbar_wait_abortable(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                                    long long limit = MBAR_WAIT_LIMIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 200000000ll) {
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 64; ++spin)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > limit) {
+            *abort_flag = 1;
             atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
             return false;
         }
     }
-    return true;
+}
+
+// Test kernel for the wait above: two warps wait (with a limit of a few thousand cycles instead of 0.1 s) on
+// an mbarrier that nobody arrives on.  The first wait to expire raises the abort flag and the status word,
+// the others then return through the flag; the CTA leaves by its ordinary exit.  Nothing faults or hangs.
+__global__ void __launch_bounds__(64) selftest_wait_timeout_kernel() {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const long long limit = threadIdx.x < 32 ? 20000ll : 2000000ll;  // the second warp can only leave through the flag
+    const bool ok = mbar_wait_abortable(&bar, 0, &abort_flag, limit);
+    if (ok) g_sink = 1.f;  // cannot happen
+    __syncthreads();
 }
 
 // ---- tiled TMA load (3-D tensor map), completion on an mbarrier ---------------------------------
@@ -130,6 +158,16 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (row m of A on lane m, two
+// consecutive 16-bit K elements per 32-bit column, so K = 16 spans 8 columns); issued by ONE thread.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 // All MMAs issued so far by this thread arrive on `bar` when they have completed.

@@ -5,11 +5,14 @@ Same names, argument order and gradient tuple as ``old/old_scripts/attn/geometri
 ``geometric_attn(Q, K, V, coords, spreads, betas, mask=None, min_rbf=0.0, max_rbf=1.0)`` returns
 ``[Z, H, N, d]``; the backward returns ``(dQ, dK, dV, None, d_spreads, d_betas, None, None, None)``.
 
-Two logit forms are available (``set_logit_form``):
+Two logit forms are available, chosen per call (``form=`` of ``geometric_attn``, ``logit_form=`` of ``GeoAttention``)
+or, when a call does not say, by the module default (``set_logit_form``):
 
 ``"one_plus_rbf"`` (default)  the form the reference's README states, ``S * (1 + exp(-d^2 / (2 sigma_h^2)))``, a pair
                               valid iff both tokens are unpadded; ``betas``, ``min_rbf`` and ``max_rbf`` stay in the
-                              signature for compatibility and do not enter; ``d_betas`` is ``None``.
+                              signature for compatibility and do not enter; ``d_betas`` is ``None``.  A call that
+                              hands this form trainable ``betas`` or a window other than ``[0, 1]`` gets a warning:
+                              a model trained with the reference tree's kernel needs ``"beta_abs"``.
 ``"beta_abs"``                the form the reference tree's Triton kernel and its test implement,
                               ``S + beta * Rn * |S|`` with ``Rn = 2 (R - min_rbf) / (max_rbf - min_rbf) - 1`` and pairs with
                               ``R`` outside ``[min_rbf, max_rbf]`` masked out (``geometric_attn.py:193-201``); ``d_betas``
@@ -20,6 +23,8 @@ back in the dtype of ``Q``.  Heads of up to 64 dimensions are supported (narrowe
 """
 import ctypes
 import os
+import warnings
+from collections import OrderedDict
 
 import torch
 
@@ -60,18 +65,75 @@ class spreads_known_positive:
         _check_spreads = self.prev
 
 
-def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00, max_rbf=1.00):
-    """wrapper so that the Function can be called with keyword arguments"""
-    return _geometric_attn.apply(Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf)
+def geometric_attn(Q, K, V, coords, spreads, betas=None, mask=None, min_rbf=0.00, max_rbf=1.00, form=None):
+    """wrapper so that the Function can be called with keyword arguments.  ``form``: ``"one_plus_rbf"``, ``"beta_abs"``
+    or ``None`` for the module default (see the module docstring); the other arguments are the reference's."""
+    if form is None:
+        return _geometric_attn.apply(Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf)
+    return _geometric_attn.apply(Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf, form)
 
 
-def longest_first(mask):
-    """int32 permutation of the samples by decreasing number of valid tokens (computed on the device, no host sync).
-    Passed as ``order=`` to ``geoattn_forward`` / ``geoattn_backward`` it makes neighbouring CTAs carry similar amounts of
-    work on padded batches (measured: 5 % on the forward of a B=8 batch with lengths 256..1024, nothing on the backward).
-    Computing it costs several small kernels, more than it saves for one call, so ``geometric_attn`` does not use it;
-    it pays when one permutation serves many calls with the same mask."""
-    return torch.argsort((~mask).sum(dim=1), descending=True, stable=True).to(torch.int32)
+_warned_ignored = False
+
+
+def _warn_ignored_once(betas, min_rbf, max_rbf):
+    """The ``one_plus_rbf`` form has no beta and no RBF window: say so once if the caller seems to rely on them."""
+    global _warned_ignored
+    if _warned_ignored:
+        return
+    what = []
+    if betas is not None and betas.requires_grad:
+        what.append("trainable betas (they receive no gradient)")
+    if float(min_rbf) != 0.0 or float(max_rbf) != 1.0:
+        what.append(f"the RBF window [{min_rbf}, {max_rbf}]")
+    if what:
+        _warned_ignored = True
+        warnings.warn("geometric_attn: the 'one_plus_rbf' logit form ignores " + " and ".join(what) +
+                      "; pass form='beta_abs' (or set_logit_form('beta_abs')) for the reference tree's S + beta*Rn*|S| form",
+                      stacklevel=3)
+
+
+class GeoPlan:
+    """Per-mask data shared by every attention call of a batch: the validity bytes the kernels read and the
+    batch plan (non-empty 128-token tiles per sample, samples longest first) made by ``pai_geoattn_plan``."""
+
+    __slots__ = ("mask", "version", "valid", "plan")
+
+    def __init__(self, mask):
+        self.mask, self.version = mask, mask._version
+        batch, n = mask.shape
+        self.valid = (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
+        lib = _lib.lib()
+        nbytes = lib.pai_geoattn_plan_bytes(batch, n)
+        self.plan = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=mask.device)
+        with torch.cuda.device(mask.device):
+            _lib.check(lib.pai_geoattn_plan(_lib.ptr(self.valid), batch, n, _lib.ptr(self.plan), nbytes, _lib.current_stream()),
+                       "pai_geoattn_plan")
+
+
+_plans = OrderedDict()  # (data_ptr, shape, device) -> GeoPlan; the entry keeps its mask alive, so the address cannot be reused
+_PLAN_CACHE = 8
+
+
+def geoattn_plan(mask):
+    """The ``GeoPlan`` of a key-padding mask ``[Z,N]`` (True = padded), or ``None`` for ``mask=None``.  Plans are cached
+    by mask tensor (address and version counter), so the layers of a model, and forward and backward, share one:
+    the mask is inverted and scanned once per batch, not once per call."""
+    if mask is None:
+        return None
+    if not mask.is_cuda:
+        raise RuntimeError("geometric_attn needs CUDA tensors: there is no CPU path")
+    key = (mask.data_ptr(), tuple(mask.shape), mask.dtype, mask.device)
+    hit = _plans.get(key)
+    if hit is not None and hit.mask is mask and hit.version == mask._version:
+        _plans.move_to_end(key)
+        return hit
+    plan = GeoPlan(mask)
+    _plans[key] = plan
+    _plans.move_to_end(key)
+    while len(_plans) > _PLAN_CACHE:
+        _plans.popitem(last=False)
+    return plan
 
 
 def _strided_ok(t):
@@ -84,22 +146,25 @@ def _strides3(t):
 
 
 def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None, out=None, lse=None,
-                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, out_layout="zhnd", scale=None):
-    """Forward on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V are bf16 ``[Z,H,N,d]``, read in place through
+                    betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", out_layout="zhnd", scale=None,
+                    q_begin=0, q_end=None):
+    """Forward on the (batch, head) pairs ``[zh_begin, zh_end)`` and the query rows ``[q_begin, q_end)`` (``q_begin`` a
+    multiple of 128, ``q_end`` a multiple of 128 or N).  Q, K, V are bf16 ``[Z,H,N,d]``, read in place through
     their strides when ``d`` is contiguous and the other strides are multiples of 8 elements (for instance the permuted
     views of a fused projection output ``[Z,N,3,H,d]``), copied otherwise.  Returns ``(O bf16 [Z,H,N,d], L fp32 [Z,H,N])``;
-    only the pairs of the range are written.  ``out_layout="znhd"`` allocates O as ``[Z,N,H,d]`` in memory and returns
-    its ``[Z,H,N,d]`` view, so that ``O.permute(0, 2, 1, 3).reshape(Z, N, H*d)`` is free.  ``scale`` is the softmax scale
-    (default ``1/sqrt(d)``)."""
+    only the pairs and rows of the ranges are written.  ``out_layout="znhd"`` allocates O as ``[Z,N,H,d]`` in memory and
+    returns its ``[Z,H,N,d]`` view, so that ``O.permute(0, 2, 1, 3).reshape(Z, N, H*d)`` is free.  ``scale`` is the
+    softmax scale (default ``1/sqrt(d)``)."""
     if not Q.is_cuda:
         raise RuntimeError("geometric_attn needs CUDA tensors: there is no CPU path")
     batch, nheads, n, d_k = Q.shape
     Q, K, V = (t if _strided_ok(t) else t.contiguous() for t in (Q, K, V))
     zh_end = batch * nheads if zh_end is None else zh_end
+    q_end = n if q_end is None else q_end
     dev = Q.device
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
-    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
+    gp = geoattn_plan(mask)
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
     if out is None:
         if out_layout == "znhd":
@@ -113,23 +178,25 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().pai_geoattn_fwd_strided(
             _lib.ptr(Q), _strides3(Q), _lib.ptr(K), _strides3(K), _lib.ptr(V), _strides3(V), _lib.ptr(coords), _lib.ptr(sigma),
-            _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(order), _lib.ptr(out), _strides3(out), _lib.ptr(lse), batch, nheads, n, d_k,
-            float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin,
-            zh_end, _lib.current_stream()), "pai_geoattn_fwd_strided")
+            _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(out), _strides3(out),
+            _lib.ptr(lse), batch, nheads, n, d_k, float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf),
+            float(max_rbf), _FORMS[form], zh_begin, zh_end, q_begin, q_end, _lib.current_stream()), "pai_geoattn_fwd_strided")
     return out, lse
 
 
 def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0, zh_end=None,
-                     betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", order=None, scale=None):
+                     betas=None, min_rbf=0.0, max_rbf=1.0, form="one_plus_rbf", scale=None, q_begin=0, q_end=None):
     """Gradients on the (batch, head) pairs ``[zh_begin, zh_end)``.  Q, K, V, O, dO bf16 contiguous.
     Returns fp32 ``(dQ, dK, dV [Z,H,N,d], d_spreads [H])`` and, for the ``beta_abs`` form, ``d_betas [H]`` as a fifth
-    element; only the pairs of the range are written."""
+    element; only the pairs of the range are written.  With a query range ``[q_begin, q_end)`` only those query rows
+    contribute: their dQ rows are written and dK, dV, d_spreads, d_betas are partial sums to be added over the shards."""
     batch, nheads, n, d_k = Q.shape
     zh_end = batch * nheads if zh_end is None else zh_end
+    q_end = n if q_end is None else q_end
     dev = Q.device
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
-    valid = None if mask is None else (~mask.bool()).contiguous().view(torch.uint8)  # a bool is one byte, 0 or 1
+    gp = geoattn_plan(mask)
     dq, dk, dv = (torch.empty(batch, nheads, n, d_k, dtype=torch.float32, device=dev) for _ in range(3))
     dsig = torch.empty(nheads, dtype=torch.float32, device=dev)
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
@@ -140,9 +207,10 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
     with torch.cuda.device(dev):
         _lib.check(lib.pai_geoattn_bwd(
             _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(dO), _lib.ptr(lse), _lib.ptr(coords),
-            _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(valid), _lib.ptr(order), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig),
-            _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k, float(scale) if scale is not None else 1.0 / (d_k ** 0.5),
-            float(min_rbf), float(max_rbf), _FORMS[form], zh_begin, zh_end, _lib.current_stream()), "pai_geoattn_bwd")
+            _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(dq),
+            _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig), _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k,
+            float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin,
+            zh_end, q_begin, q_end, _lib.current_stream()), "pai_geoattn_bwd")
     if form == "beta_abs":
         return dq, dk, dv, dsig, dbeta
     return dq, dk, dv, dsig
@@ -151,7 +219,9 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
 class _geometric_attn(torch.autograd.Function):
 
     @staticmethod
-    def forward(ctx, Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf):
+    def forward(ctx, Q, K, V, coords, spreads, betas, mask, min_rbf, max_rbf, form=None):
+        # (the reference's nine arguments; the optional tenth selects the logit form for this call)
+        ctx.n_inputs = 9 if form is None else 10
         assert Q.shape == K.shape == V.shape, f"Q, K, and V projection shapes must match, but got {Q.shape=}, {K.shape=}, {V.shape=}"
         batch, nheads, N, d_k = Q.shape
         assert coords.dim() == 3 and coords.size(2) == 3, f"coordinates must be of shape (batch, N, 3), not {coords.shape}"
@@ -175,15 +245,17 @@ class _geometric_attn(torch.autograd.Function):
             qb, kb, vb = (t.to(torch.bfloat16).contiguous() for t in (Q, K, V))
         else:
             qb, kb, vb = (t.to(torch.bfloat16) for t in (Q, K, V))
-        form = _logit_form
+        form = _logit_form if form is None else form
+        if form not in _FORMS:
+            raise ValueError(f"logit form must be one of {sorted(_FORMS)}, not {form!r}")
         if form == "beta_abs" and betas is None:
             raise ValueError("the beta_abs logit form needs betas")
-        order = None
+        if form == "one_plus_rbf":
+            _warn_ignored_once(betas, min_rbf, max_rbf)
         out, lse = geoattn_forward(qb, kb, vb, coords, spreads, mask, betas=betas, min_rbf=min_rbf, max_rbf=max_rbf, form=form,
-                                   order=order, out_layout="zhnd" if needs_bwd else "znhd", scale=scale)
+                                   out_layout="zhnd" if needs_bwd else "znhd", scale=scale)
         ctx.save_for_backward(qb, kb, vb, out, lse, coords, spreads, mask if mask is not None else torch.empty(0),
-                              betas if betas is not None else torch.empty(0), order if order is not None else torch.empty(0))
-        ctx.has_order = order is not None
+                              betas if betas is not None else torch.empty(0))
         ctx.has_mask = mask is not None
         ctx.form, ctx.min_rbf, ctx.max_rbf = form, min_rbf, max_rbf
         ctx.in_dtype = Q.dtype
@@ -193,19 +265,19 @@ class _geometric_attn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dO):
-        qb, kb, vb, out, lse, coords, spreads, mask, betas, order = ctx.saved_tensors
+        qb, kb, vb, out, lse, coords, spreads, mask, betas = ctx.saved_tensors
         mask = mask if ctx.has_mask else None
-        order = order if ctx.has_order else None
         dt = ctx.in_dtype
         d_k = ctx.d_k
         if d_k < _KERNEL_D:
             dO = torch.nn.functional.pad(dO, (0, _KERNEL_D - d_k))
+        tail = (None,) * (ctx.n_inputs - 6)  # mask, min_rbf, max_rbf (and the form, when it was passed)
         if ctx.form == "beta_abs":
             dq, dk, dv, dsig, dbeta = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads,
                                                        mask, betas=betas, min_rbf=ctx.min_rbf, max_rbf=ctx.max_rbf, form=ctx.form,
-                                                       order=order, scale=ctx.scale)
+                                                       scale=ctx.scale)
             return (dq[..., :d_k].to(dt), dk[..., :d_k].to(dt), dv[..., :d_k].to(dt), None, dsig.to(ctx.spread_dtype),
-                    dbeta.to(betas.dtype), None, None, None)
+                    dbeta.to(betas.dtype)) + tail
         dq, dk, dv, dsig = geoattn_backward(qb, kb, vb, out, dO.to(torch.bfloat16).contiguous(), lse, coords, spreads, mask,
-                                            order=order, scale=ctx.scale)
-        return dq[..., :d_k].to(dt), dk[..., :d_k].to(dt), dv[..., :d_k].to(dt), None, dsig.to(ctx.spread_dtype), None, None, None, None
+                                            scale=ctx.scale)
+        return (dq[..., :d_k].to(dt), dk[..., :d_k].to(dt), dv[..., :d_k].to(dt), None, dsig.to(ctx.spread_dtype), None) + tail

@@ -6,7 +6,10 @@ encoder-only model used as the end-to-end inference configuration.
 with biases ``[H, d_k]``, ``spreads = min_spread + exp(spread_weights)``, ``betas = exp(beta_weights)``,
 heads concatenated d_k-major / head-minor before the bias-free ``out_proj``.  The projections run as one GEMM
 over all heads (and over Q, K, V together for self-attention) instead of the reference's per-head broadcast
-matmul, which copies the input once per head.
+matmul, which copies the input once per head.  ``logit_form`` (an addition to the reference's constructor) selects
+the attention logit form for this module: ``"one_plus_rbf"`` (``S (1 + R)``; ``beta_weights``, ``min_rbf`` and ``max_rbf``
+are then unused), ``"beta_abs"`` (the reference tree's ``S + beta Rn |S|`` with the RBF window, what a checkpoint trained
+with the reference's own kernel expects), or ``None`` for the default of ``geometric_attn``.
 
 ``Encoder`` is the reference's post-norm block (``old/old_scripts/encoder.py:8-41``): ``LN(x + drop(attn))``
 then ``LN(x + drop(ffn))``, each one fused kernel in bf16 inference.  The reference's ``forward`` passes ``coords_beta`` positionally into a
@@ -16,6 +19,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from proteusai_b200.utils.model_utils.attn import geometric_attn as _ga
 from proteusai_b200.utils.model_utils.attn.geometric_attn import geometric_attn, spreads_known_positive
 from proteusai_b200.utils.model_utils.base_modules import fused_ops
 from proteusai_b200.utils.model_utils.base_modules.base_modules import MLP
@@ -24,8 +28,12 @@ from proteusai_b200.utils.model_utils.wf_embedding.wf_embedding import WaveFunct
 
 class GeoAttention(nn.Module):
 
-    def __init__(self, d_model=512, heads=8, min_spread=2.0, min_rbf=0.001, max_rbf=1.00, learn_spreads=True):
+    def __init__(self, d_model=512, heads=8, min_spread=2.0, min_rbf=0.001, max_rbf=1.00, learn_spreads=True, logit_form=None):
         super().__init__()
+        if logit_form is not None and logit_form not in ("one_plus_rbf", "beta_abs"):
+            raise ValueError(f"logit_form must be 'one_plus_rbf', 'beta_abs' or None, not {logit_form!r}")
+        self.logit_form = logit_form
+        self._packed = {}  # inference-time cache of the fused projection weights (see _packed_weights)
         if d_model % heads != 0:
             raise ValueError(f"number of dimensions ({d_model}) must be divisible by number of attention heads ({heads})")
         self.heads, self.d_model, self.d_k = heads, d_model, d_model // heads
@@ -44,40 +52,77 @@ class GeoAttention(nn.Module):
     def get_betas(self):
         return torch.exp(self.beta_weights)
 
-    def _project(self, x, weights, biases):
+    def _packed_weights(self, names, dtype):
+        """``[D, S*H*dk]`` weight and ``[S*H*dk]`` bias of the fused projection for the weight sets ``names`` (``"q"``,
+        ``"k"``, ``"v"``), in ``dtype``.  Without gradient recording the packed tensors are kept and reused until a
+        parameter changes (its version counter moves), so a forward does no concatenation or cast; with gradients they
+        are rebuilt every call so that autograd sees the parameters."""
+        ws = [getattr(self, f"{n}_proj") for n in names]
+        bs = [getattr(self, f"{n}_bias") for n in names]
+        build = lambda: (
+            torch.cat([w.permute(1, 0, 2).reshape(self.d_model, self.heads * self.d_k) for w in ws], dim=1).to(dtype).contiguous(),
+            torch.cat([b.reshape(self.heads * self.d_k) for b in bs]).to(dtype).contiguous())
+        if torch.is_grad_enabled() and any(t.requires_grad for t in ws + bs):
+            return build()
+        key = ("proj", names, dtype, ws[0].device)
+        stamp = tuple((t.data_ptr(), t._version) for t in ws + bs)
+        hit = self._packed.get(key)
+        if hit is None or hit[0] != stamp:
+            hit = (stamp, build())
+            self._packed[key] = hit
+        return hit[1]
+
+    def _out_weight(self, dtype):
+        """``out_proj.weight`` with its input columns reordered from the reference's d_k-major / head-minor feature order
+        (feature dd*H + h) to heads kept whole (feature h*d_k + dd), cached like the projection weights."""
+        w = self.out_proj.weight
+        build = lambda: w.view(self.d_model, self.d_k, self.heads).transpose(1, 2).reshape(self.d_model, self.d_model).to(dtype).contiguous()
+        if torch.is_grad_enabled() and w.requires_grad:
+            return build()
+        key = ("out", dtype, w.device)
+        stamp = (w.data_ptr(), w._version)
+        hit = self._packed.get(key)
+        if hit is None or hit[0] != stamp:
+            hit = (stamp, build())
+            self._packed[key] = hit
+        return hit[1]
+
+    def _project(self, x, names):
         """Per-head projections ``x W_h + b_h`` for one or several weight sets as ONE GEMM:
         ``[Z*N, D] x [D, S*H*dk]`` (the reference's broadcast ``matmul(x.unsqueeze(1), W.unsqueeze(0))`` materialises
         ``x`` once per head).  Returns a list of ``[Z, H, N, dk]`` views."""
         z, n, d = x.shape
-        w2 = torch.cat([w.permute(1, 0, 2).reshape(d, self.heads * self.d_k) for w in weights], dim=1).to(x.dtype)
-        b2 = torch.cat([b.reshape(self.heads * self.d_k) for b in biases]).to(x.dtype)
-        y = torch.addmm(b2, x.reshape(z * n, d), w2).view(z, n, len(weights), self.heads, self.d_k)
-        return [y[:, :, i].permute(0, 2, 1, 3) for i in range(len(weights))]
+        w2, b2 = self._packed_weights(names, x.dtype)
+        y = torch.addmm(b2, x.reshape(z * n, d), w2).view(z, n, len(names), self.heads, self.d_k)
+        return [y[:, :, i].permute(0, 2, 1, 3) for i in range(len(names))]
 
     def forward(self, q, k, v, coords, mask=None, flash=True):
         assert q.shape == k.shape == v.shape and q.dim() == 3 and q.shape[2] == self.d_model
         batch, n, _ = q.shape
         if q is k and k is v:  # self-attention: one fused GEMM for Q, K and V
-            Q, K, V = self._project(q, (self.q_proj, self.k_proj, self.v_proj), (self.q_bias, self.k_bias, self.v_bias))
+            Q, K, V = self._project(q, ("q", "k", "v"))
         else:
-            (Q,), (K,), (V,) = (self._project(x, (w,), (b,)) for x, w, b in
-                                ((q, self.q_proj, self.q_bias), (k, self.k_proj, self.k_bias), (v, self.v_proj, self.v_bias)))
+            (Q,), (K,), (V,) = (self._project(x, (nm,)) for x, nm in ((q, "q"), (k, "k"), (v, "v")))
+        form = self.logit_form if self.logit_form is not None else _ga.get_logit_form()
         with spreads_known_positive():  # min_spread + exp(w) > 0: no need to read it back from the device
-            out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
-                                 min_rbf=self.min_rbf, max_rbf=self.max_rbf)  # [Z,H,N,dk]
+            if form == "one_plus_rbf":  # no beta, no window in this form: hand it neither
+                out = geometric_attn(Q, K, V, coords, self.get_spreads(), None, mask=mask, form=form)
+            else:
+                out = geometric_attn(Q, K, V, coords, self.get_spreads(), self.get_betas(), mask=mask,
+                                     min_rbf=self.min_rbf, max_rbf=self.max_rbf, form=form)  # [Z,H,N,dk]
         # The reference concatenates the heads d_k-major / head-minor (feature dd*H + h) before out_proj.  The same
         # product with the heads kept whole (feature h*d_k + dd) and the columns of the weight reordered to match:
         # the activation view below is free when the kernel wrote O as [Z,N,H,d_k] (inference), the weight is small.
-        w = self.out_proj.weight.view(self.d_model, self.d_k, self.heads).transpose(1, 2).reshape(self.d_model, self.d_model)
-        return F.linear(out.permute(0, 2, 1, 3).reshape(batch, n, self.d_model), w.to(out.dtype))
+        return F.linear(out.permute(0, 2, 1, 3).reshape(batch, n, self.d_model), self._out_weight(out.dtype))
 
 
 class Encoder(nn.Module):
 
     def __init__(self, d_model=512, heads=8, min_spread=2.0, min_rbf=0.001, d_hidden=2048, hidden_layers=0,
-                 dropout=0.10, learn_spreads=True):
+                 dropout=0.10, learn_spreads=True, logit_form=None):
         super().__init__()
-        self.attn = GeoAttention(d_model=d_model, heads=heads, min_spread=min_spread, min_rbf=min_rbf, learn_spreads=learn_spreads)
+        self.attn = GeoAttention(d_model=d_model, heads=heads, min_spread=min_spread, min_rbf=min_rbf, learn_spreads=learn_spreads,
+                                 logit_form=logit_form)
         self.attn_norm = nn.LayerNorm(d_model)
         self.ffn = MLP(d_in=d_model, d_out=d_model, d_hidden=d_hidden, hidden_layers=hidden_layers, dropout=dropout)
         self.ffn_norm = nn.LayerNorm(d_model)

@@ -20,7 +20,7 @@ def wf_embedding(coords, wavenumbers, magnitude_type=1, dropout_p=0.0, mask=None
 
 
 def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=0, row_end=None,
-                    out=None, cos_sums=None, sin_sums=None, dropout_p=0.0, seed=0):
+                    out=None, cos_sums=None, sin_sums=None, dropout_p=0.0, seed=0, reproducible=False):
     """Run the forward kernel on observer rows ``[row_begin, row_end)`` of every batch element.
 
     Returns ``(out [Z,N,2K], cos_sums [Z,N,K], sin_sums [Z,N,K])``; only the rows of the range are
@@ -28,6 +28,8 @@ def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=
     multi-GPU building block: every rank holds all coordinates and computes its own rows.
     With ``dropout_p > 0`` evaluations are dropped by the reference kernel's index hash under ``seed``
     (the pattern does not depend on the row range, so all ranks of a sharded call pass the same seed).
+    ``reproducible=True`` asks for sums that are bit-identical from launch to launch (``PAI_WE_REPRODUCIBLE``
+    of the C ABI): by default partial sums are added in arrival order and the last bit can differ.
     """
     assert magnitude_type in [0, 1, 2, 3]  # mag=1, 1/|R|, 1/log2(|R|), 1/sqrt(|R|)
     if not coords.is_cuda:
@@ -51,7 +53,7 @@ def we_forward_rows(coords, wavenumbers, magnitude_type=1, mask=None, row_begin=
         _lib.check(_lib.lib().pai_we_fwd(
             _lib.ptr(planes), _lib.ptr(valid), _lib.ptr(wn), _lib.ptr(out), _lib.ptr(cos_sums), _lib.ptr(sin_sums),
             batch, n, k, row_begin, row_end, magnitude_type, float(dropout_p), int(seed) & 0xFFFFFFFF,
-            _lib.current_stream()), "pai_we_fwd")
+            _lib.WE_REPRODUCIBLE if reproducible else 0, _lib.current_stream()), "pai_we_fwd")
     return out, cos_sums, sin_sums
 
 

@@ -6,6 +6,8 @@ constructor arguments, same parameter names (``wavenumbers`` holds log-wavenumbe
 ``i / (K - 1)``), same ``forward(coords_alpha, coords_beta, key_padding_mask)`` signature, so a
 reference checkpoint loads.  Both branches of the reference are provided: the isotropic kernel and the
 anisotropic one with per-wavenumber C-beta scaling (``wf_embedding_learnCB``, the reference's default).
+``get_CaCb_coords`` (``:48-49``, the first call of ``FeaturizeProtein.forward``, ``utils/model_utils/gnn/gnn.py:44``)
+builds the C-alpha positions and virtual C-beta directions the anisotropic branch takes.
 """
 import torch
 import torch.nn as nn
@@ -32,3 +34,30 @@ class WaveFunctionEmbedding(nn.Module):
         if self.aniso:
             return wf_embedding_learnCB(coords_alpha, coords_beta, self.aa_magnitudes, self.get_wavenumbers(), mask=key_padding_mask)
         return wf_embedding_iso(coords_alpha, self.get_wavenumbers(), magnitude_type=1, dropout_p=0.0, mask=key_padding_mask)
+
+    def get_CaCb_coords(self, coords, chain_idxs=None, norm=False):
+        """``(C-alpha [Z,N,3], virtual C-beta relative to C-alpha [Z,N,3])``.
+
+        Backbone input ``[Z,N,3(N,CA,C),3]`` (what the model passes): the ideal-geometry construction from the two bond
+        vectors and their cross product with ProteinMPNN's coefficients, as ``get_Cb_from_BB``
+        (``utils/model_utils/base_modules/Cb_utils.py:97-116``); padded residues (all zeros) give a zero C-beta;
+        ``norm=True`` scales to unit vectors.  C-alpha-only input ``[Z,N,3]`` with ``chain_idxs`` is passed on to the
+        reference's own ``get_coords`` when the reference tree is importable (it is not restated here)."""
+        if coords.dim() == 4:
+            n, ca, c = coords[:, :, 0, :], coords[:, :, 1, :], coords[:, :, 2, :]
+            b1, b2 = ca - n, c - ca
+            b3 = torch.linalg.cross(b1, b2, dim=2)
+            cb = -0.58273431 * b2 + 0.56802827 * b1 - 0.54067466 * b3
+            if norm:
+                cb = cb * (1 / torch.linalg.vector_norm(cb, dim=2, keepdim=True).clamp(1e-6))
+            return ca, cb
+        if coords.dim() == 3:
+            try:
+                from utils.model_utils.base_modules.Cb_utils import get_coords
+            except ImportError as exc:
+                raise NotImplementedError(
+                    "C-alpha-only input needs the reference's utils.model_utils.base_modules.Cb_utils on sys.path; "
+                    "backbone input [Z,N,3,3] is handled here") from exc
+            return get_coords(coords, chain_idxs, norm)
+        raise ValueError(f"invalid input size for coordinates, expected (batch,N,3) for Ca only model or (batch,N,3,3) "
+                         f"for backbone model, but got {coords.shape=}")

@@ -47,17 +47,18 @@ def test_we_fwd_argument_errors(lib):
     p = ctypes.c_void_p(0x1000)  # never dereferenced: validation fails first
     null = None
     f = lib.pai_we_fwd
-    assert f(null, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, None) == -1
-    assert f(p, null, p, p, p, p, 0, 8, 4, 0, 8, 1, 0.0, 0, None) == -2
-    assert f(p, null, p, p, p, p, 1, 0, 4, 0, 0, 1, 0.0, 0, None) == -2
-    assert f(p, null, p, p, p, p, 1, 8, 0, 0, 8, 1, 0.0, 0, None) == -2
-    assert f(p, null, p, p, p, p, 1, 8, 4, 5, 4, 1, 0.0, 0, None) == -6
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 9, 1, 0.0, 0, None) == -6
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 7, 0.0, 0, None) == -4
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 1.0, 0, None) == -4   # dropout_p must be in [0, 1)
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, -0.1, 0, None) == -4
-    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, float("nan"), 0, None) == -4
-    assert f(p, null, p, ctypes.c_void_p(0x1004), p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, None) == -3
+    assert f(null, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, 0, None) == -1
+    assert f(p, null, p, p, p, p, 0, 8, 4, 0, 8, 1, 0.0, 0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 0, 4, 0, 0, 1, 0.0, 0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 8, 0, 0, 8, 1, 0.0, 0, 0, None) == -2
+    assert f(p, null, p, p, p, p, 1, 8, 4, 5, 4, 1, 0.0, 0, 0, None) == -6
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 9, 1, 0.0, 0, 0, None) == -6
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 7, 0.0, 0, 0, None) == -4
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 1.0, 0, 0, None) == -4   # dropout_p must be in [0, 1)
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, -0.1, 0, 0, None) == -4
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, float("nan"), 0, 0, None) == -4
+    assert f(p, null, p, ctypes.c_void_p(0x1004), p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, 0, None) == -3
+    assert f(p, null, p, p, p, p, 1, 8, 4, 0, 8, 1, 0.0, 0, 2, None) == -4       # unknown flag bit
 
 
 def test_we_bwd_argument_errors(lib):
@@ -91,9 +92,9 @@ def test_dropin_aliases():
 def test_geoattn_argument_errors(lib):
     p = ctypes.c_void_p(0x1000)
     f = lib.pai_geoattn_fwd
-    ok = dict(Z=2, H=2, N=64, d=64)
-    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), None, kw.get("order", None), p, p, kw.get("Z", 2), kw.get("H", 2), kw.get("N", 64),
-                         kw.get("d", 64), 0.125, kw.get("lo", 0.0), kw.get("hi", 1.0), kw.get("form", 0), kw.get("zb", 0), kw.get("ze", 4), None]
+    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), kw.get("valid", None), kw.get("plan", None), p, p,
+                         kw.get("Z", 2), kw.get("H", 2), kw.get("N", 256), kw.get("d", 64), 0.125, kw.get("lo", 0.0), kw.get("hi", 1.0),
+                         kw.get("form", 0), kw.get("zb", 0), kw.get("ze", 4), kw.get("qb", 0), kw.get("qe", 256), None]
     assert f(*args(Q=None)) == -1
     assert f(*args(Z=0)) == -2
     assert f(*args(d=32)) == -4           # only d_head = 64 is built
@@ -102,12 +103,17 @@ def test_geoattn_argument_errors(lib):
     assert f(*args(form=1, lo=1.0, hi=1.0)) == -2
     assert f(*args(zb=3, ze=2)) == -6
     assert f(*args(ze=5)) == -6
+    assert f(*args(qb=64)) == -6          # query ranges start on a tile of 128 ...
+    assert f(*args(qe=200)) == -6         # ... and end on one, or at N
+    assert f(*args(qb=128, qe=0)) == -6
+    assert f(*args(qe=257)) == -6
     assert f(*args(Q=ctypes.c_void_p(0x1008))) == -3
-    assert f(*args(order=p, zb=1)) == -4  # a sample permutation needs the full (batch, head) range
+    assert f(*args(valid=p)) == -1        # a mask needs the plan made from it
+    assert f(*args(valid=p, plan=ctypes.c_void_p(0x1004))) == -3
     g = lib.pai_geoattn_bwd
     need = lib.pai_geoattn_bwd_workspace_bytes(2, 2, 64, 64)
     assert need == 2 * 2 * 64 * 4
-    base = [p] * 8 + [p, None, None] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, None]
+    base = [p] * 8 + [p, None, None] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, 0, 64, None]
     bad = list(base)
     bad[17] = need - 1
     assert g(*bad) == -5
@@ -118,6 +124,19 @@ def test_geoattn_argument_errors(lib):
     bad[25] = 1      # logit form 1 ...
     bad[15] = None   # ... without a dbetas buffer
     assert g(*bad) == -1
+    bad = list(base)
+    bad[28] = 32     # query range off the tile grid
+    assert g(*bad) == -6
+    # the batch plan
+    nbytes = lib.pai_geoattn_plan_bytes(4, 1000)
+    assert nbytes == 4 * (4 + 3 * 4 + 2 * 4 * 8)
+    assert lib.pai_geoattn_plan_bytes(0, 10) == 0
+    h = lib.pai_geoattn_plan
+    assert h(None, 4, 1000, p, nbytes, None) == -1
+    assert h(p, 4, 1000, p, nbytes - 1, None) == -5
+    assert h(p, 0, 1000, p, nbytes, None) == -2
+    assert h(p, 4, 1000, ctypes.c_void_p(0x1004), nbytes, None) == -3
+    assert lib.pai_tune_set(999, 1) == -4
 
 
 def test_strided_attention_and_row_op_argument_errors(lib):
@@ -126,7 +145,7 @@ def test_strided_attention_and_row_op_argument_errors(lib):
     ok = i64(2 * 64 * 64, 64 * 64, 64)
     f = lib.pai_geoattn_fwd_strided
     call = lambda **kw: f(p, kw.get("qs", ok), p, ok, p, ok, p, p, None, None, None, p, kw.get("os", ok), p, 2, 2, 64,
-                          kw.get("d", 64), 0.125, 0.0, 1.0, 0, 0, kw.get("ze", 4), None)
+                          kw.get("d", 64), 0.125, 0.0, 1.0, 0, 0, kw.get("ze", 4), 0, 64, None)
     assert call(qs=None) == -1
     assert call(d=32) == -4
     assert call(ze=5) == -6

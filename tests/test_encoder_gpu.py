@@ -9,25 +9,28 @@ from oracle.we_ref import wf_embedding_ref
 pytestmark = pytest.mark.gpu
 
 
-def _reference_forward(model, tokens, coords, mask):
-    """The model's arithmetic in fp32 on the CPU with the oracle in place of both kernels."""
+def _reference_forward(model, tokens, coords, mask, act=None):
+    """The model's arithmetic in fp32 on the CPU with the oracle in place of both kernels.  ``act`` rounds an
+    activation where the GPU path stores one (identity by default; bf16 rounding to follow the bf16 inference path
+    operator by operator, so that what is compared is the kernels, not the storage format)."""
     m = model
+    act = act or (lambda t: t)
     wn = m.wf_embedding.get_wavenumbers().detach().float().cpu()
-    x = m.embed.weight.detach().float().cpu()[tokens] + wf_embedding_ref(coords, wn, 1, mask)
+    x = act(act(m.embed.weight.detach().float().cpu()[tokens]) + act(wf_embedding_ref(coords, wn, 1, mask)))
     for enc in m.encoders:
         a = enc.attn
         z, n, _ = x.shape
         proj = lambda w, b: torch.matmul(x.unsqueeze(1), w.detach().float().cpu().unsqueeze(0)) + b.detach().float().cpu()[None, :, None, :]
         q, k, v = proj(a.q_proj, a.q_bias), proj(a.k_proj, a.k_bias), proj(a.v_proj, a.v_bias)
         q, k, v = (t.to(torch.bfloat16).float() for t in (q, k, v))  # the kernel's input rounding
-        o = geoattn_ref(q, k, v, coords, a.get_spreads().detach().float().cpu(), mask=mask)
-        o = o.permute(0, 2, 3, 1).reshape(z, n, a.d_model) @ a.out_proj.weight.detach().float().cpu().T
-        ln = lambda mod, t: torch.nn.functional.layer_norm(t, (t.shape[-1],), mod.weight.detach().float().cpu(), mod.bias.detach().float().cpu())
+        o = act(geoattn_ref(q, k, v, coords, a.get_spreads().detach().float().cpu(), mask=mask))
+        o = act(o.permute(0, 2, 3, 1).reshape(z, n, a.d_model) @ a.out_proj.weight.detach().float().cpu().T)
+        ln = lambda mod, t: act(torch.nn.functional.layer_norm(t, (t.shape[-1],), mod.weight.detach().float().cpu(), mod.bias.detach().float().cpu()))
         x = ln(enc.attn_norm, x + o)
         f = enc.ffn
-        h = torch.nn.functional.gelu(x @ f.in_proj.weight.detach().float().cpu().T + f.in_proj.bias.detach().float().cpu())
-        x = ln(enc.ffn_norm, x + h @ f.out_proj.weight.detach().float().cpu().T + f.out_proj.bias.detach().float().cpu())
-    return x @ m.head.weight.detach().float().cpu().T + m.head.bias.detach().float().cpu()
+        h = act(torch.nn.functional.gelu(act(x @ f.in_proj.weight.detach().float().cpu().T + f.in_proj.bias.detach().float().cpu())))
+        x = ln(enc.ffn_norm, x + act(h @ f.out_proj.weight.detach().float().cpu().T + f.out_proj.bias.detach().float().cpu()))
+    return act(x @ m.head.weight.detach().float().cpu().T + m.head.bias.detach().float().cpu())
 
 
 def test_geoattention_module_head_layout_and_grads():
@@ -89,6 +92,31 @@ def test_encoder_model_bf16_inference_uses_fused_ops_and_matches_oracle_composit
     err = (logits[valid] - ref[valid]).abs().max().item()
     agree = (logits[valid].argmax(-1) == ref[valid].argmax(-1)).float().mean().item()
     assert err < 1e-1 and agree >= 0.95, (err, agree)
+
+
+def test_config5_shape_bf16_matches_oracle_composition():
+    """The encoder at the configuration the benchmark times: d_model 512, 8 heads, 4 layers, FFN 2048, bf16, chains padded
+    to N = 1024 (five chains with lengths from 64 to 1024 keep the CPU oracle to seconds).  The oracle composes the CPU
+    restatements of both kernels with fp32 arithmetic on the bf16 weights, rounding activations to bf16 where the GPU
+    path stores them.  Bar: logits within 5e-2, the same arg-max on at least 99 % of the valid tokens."""
+    from proteusai_b200.utils.model_utils.base_modules.encoder import ProteusEncoderModel
+    torch.manual_seed(1005)
+    model = ProteusEncoderModel(d_model=512, heads=8, layers=4, d_hidden=2048).cuda().eval().to_compute_dtype_(torch.bfloat16)
+    lengths = [1024, 700, 333, 129, 64]
+    n = 1024
+    c, m = chains.chain_batch(lengths, n, seed=1005)
+    c, m = torch.from_numpy(c), torch.from_numpy(m)
+    tokens = torch.randint(0, 33, (len(lengths), n), generator=torch.Generator().manual_seed(1005))
+    with torch.no_grad():
+        logits = model(tokens.cuda(), c.cuda(), m.cuda()).float().cpu()
+        ref = _reference_forward(model, tokens, c, m, act=lambda t: t.to(torch.bfloat16).float())
+    from proteusai_b200 import _lib
+    _lib.device_status()
+    valid = ~m
+    err = (logits[valid] - ref[valid]).abs().max().item()
+    agree = (logits[valid].argmax(-1) == ref[valid].argmax(-1)).float().mean().item()
+    print(f"config-5 shape: logits max-abs {err:.3e}, arg-max agreement {agree:.4f} on {int(valid.sum())} tokens")
+    assert err < 5e-2 and agree >= 0.99, (err, agree)
 
 
 @pytest.mark.parametrize("d", [8, 128, 512, 520, 1024, 4096])

@@ -239,3 +239,125 @@ def test_masks_with_holes_and_an_empty_sample(ga):
     assert torch.all((sd.grad.cpu().double() - dsig).abs() <= 2e-2 * dsig.abs() + 5e-3)
     from proteusai_b200 import _lib
     _lib.device_status()
+
+
+def test_batch_plan_lists_live_tiles_and_orders_samples(ga):
+    """pai_geoattn_plan against the same bookkeeping done in numpy: live 128-token tiles per sample with their hole flags,
+    first valid offsets, valid counts, and the samples by decreasing tile count (stable)."""
+    import numpy as np
+    z, n = 6, 700
+    g = torch.Generator().manual_seed(5)
+    m = torch.ones(z, n, dtype=torch.bool)
+    for b, length in enumerate([700, 1, 300, 129, 0, 512]):
+        m[b, :length] = False
+    m[2, 130:200] = True   # a hole
+    m[5, 0:128] = True     # an empty first tile
+    plan = ga.geoattn_plan(m.cuda()).plan.cpu().numpy()
+    tiles = (n + 127) // 128
+    assert plan[0] == z and plan[1] == n and plan[2] == tiles and plan[3] == 0
+    order, count, nvalid = plan[4:4 + z], plan[4 + z:4 + 2 * z], plan[4 + 2 * z:4 + 3 * z]
+    lists = plan[4 + 3 * z:4 + 3 * z + z * tiles].reshape(z, tiles)
+    info = plan[4 + 3 * z + z * tiles:4 + 3 * z + 2 * z * tiles].reshape(z, tiles)
+    valid = ~m.numpy()
+    want_count = []
+    for b in range(z):
+        live = []
+        for t in range(tiles):
+            seg = valid[b, t * 128:(t + 1) * 128]
+            if seg.any():
+                hole = 0x8000 if seg.sum() < 128 else 0
+                live.append(t | hole)
+                assert info[b, t] == (int(np.argmax(seg)) | hole)
+            else:
+                assert info[b, t] == -1
+        assert list(lists[b, :len(live)]) == live and count[b] == len(live) and nvalid[b] == valid[b].sum()
+        want_count.append(len(live))
+    assert list(order) == sorted(range(z), key=lambda b: (-want_count[b], b))
+    assert ga.geoattn_plan(None) is None
+    assert ga.geoattn_plan(m.cuda()) is not ga.geoattn_plan(m.cuda())   # different tensors: different plans
+    mc = m.cuda()
+    assert ga.geoattn_plan(mc) is ga.geoattn_plan(mc)                    # the same tensor: one plan for all layers
+
+
+def test_query_row_ranges_shard_forward_and_backward(ga):
+    """Sharding by query blocks: the forward on row ranges reproduces the full call bit for bit; in the backward dQ rows
+    come from their own shard and dK, dV, d_sigma are partial sums that add up to the full gradients."""
+    z, h, n = 2, 2, 600
+    q, k, v, d_out, c, m, sig = (t.cuda() for t in _inputs(z, h, n, [600, 333], seed=61, std=1.0))
+    o_full, l_full = ga.geoattn_forward(q, k, v, c, sig, m)
+    o = torch.full_like(o_full, float("nan"))
+    l = torch.full_like(l_full, float("nan"))
+    ranges = ((0, 256), (256, 512), (512, 600))
+    for a, b in ranges:
+        ga.geoattn_forward(q, k, v, c, sig, m, out=o, lse=l, q_begin=a, q_end=b)
+    assert torch.equal(o, o_full) and torch.equal(l, l_full)
+    dq_f, dk_f, dv_f, ds_f = ga.geoattn_backward(q, k, v, o_full, d_out, l_full, c, sig, m)
+    dq = torch.full_like(dq_f, float("nan"))
+    dk, dv, ds = torch.zeros_like(dk_f), torch.zeros_like(dv_f), torch.zeros_like(ds_f)
+    for a, b in ranges:
+        dq_p, dk_p, dv_p, ds_p = ga.geoattn_backward(q, k, v, o_full, d_out, l_full, c, sig, m, q_begin=a, q_end=b)
+        dq[:, :, a:b] = dq_p[:, :, a:b]
+        dk += dk_p
+        dv += dv_p
+        ds += ds_p
+    scale = max(dk_f.abs().max().item(), dv_f.abs().max().item(), dq_f.abs().max().item())
+    assert (dq - dq_f).abs().max().item() < 1e-4 * scale      # same tiles, fp32 reductions in another order
+    assert (dk - dk_f).abs().max().item() < 1e-4 * scale and (dv - dv_f).abs().max().item() < 1e-4 * scale
+    assert torch.allclose(ds, ds_f, rtol=1e-3, atol=1e-4)
+    from proteusai_b200 import _lib
+    _lib.device_status()
+
+
+def test_far_key_groups_skip_changes_nothing(ga):
+    """Key groups farther than 5.9 sigma from a warp's queries skip the RBF arithmetic; there 1 + R == 1 in fp32, so the
+    output with the skip switched off (test-only tuning entry) is the same, bit for bit."""
+    from proteusai_b200 import _lib
+    q, k, v, _, c, m, sig = (t.cuda() for t in _inputs(2, 8, 1024, [1024, 700], seed=71))
+    o_skip, l_skip = ga.geoattn_forward(q, k, v, c, sig, m)
+    try:
+        _lib.tune(ga_no_far_skip=1)
+        o_all, l_all = ga.geoattn_forward(q, k, v, c, sig, m)
+    finally:
+        _lib.tune_reset()
+    assert torch.equal(o_skip, o_all) and torch.equal(l_skip, l_all)
+
+
+def test_padding_may_hold_nan(ga):
+    """Rows of padded tokens are never read into the result: NaN in Q and K there changes nothing (V of padded keys
+    meets P = 0 in the tensor core, where 0 x NaN is NaN as in the reference's own dot product, so V stays finite)."""
+    z, h, n = 2, 2, 300
+    q, k, v, d_out, c, m, sig = (t.cuda() for t in _inputs(z, h, n, [300, 150], seed=81, std=1.0))
+    o_ref, l_ref = ga.geoattn_forward(q, k, v, c, sig, m)
+    pad = m[:, None, :, None].expand(z, h, n, 64)
+    qn, kn = q.clone(), k.clone()
+    qn[pad] = float("nan")
+    kn[pad] = float("inf")
+    o, l = ga.geoattn_forward(qn, kn, v, c, sig, m)
+    assert torch.isfinite(o).all() and torch.equal(o, o_ref) and torch.equal(l, l_ref)
+
+
+def test_logit_form_is_an_argument_and_ignored_inputs_warn(ga):
+    import warnings
+    q, k, v, d_out, c, m, sig = (t.cuda() for t in _inputs(1, 2, 200, [180], seed=91, std=1.0))
+    betas = torch.tensor([0.7, 1.3], device="cuda", requires_grad=True)
+    with torch.no_grad():
+        a = ga.geometric_attn(q, k, v, c, sig, betas, m, 0.001, 1.0, form="beta_abs")
+        prev = ga.set_logit_form("beta_abs")
+        try:
+            b = ga.geometric_attn(q, k, v, c, sig, betas, m, 0.001, 1.0)
+        finally:
+            ga.set_logit_form(prev)
+        one = ga.geometric_attn(q, k, v, c, sig, None, m)
+    assert torch.equal(a, b) and not torch.equal(a, one)
+    ga._warned_ignored = False
+    with warnings.catch_warnings(record=True) as w:
+        warnings.simplefilter("always")
+        ga.geometric_attn(q, k, v, c, sig, betas, m, 0.001, 1.0, form="one_plus_rbf")
+    assert any("one_plus_rbf" in str(x.message) for x in w)
+    # gradients flow through the ten-argument call too
+    qd = q.clone().requires_grad_(True)
+    out = ga.geometric_attn(qd, k, v, c, sig, betas, m, 0.001, 1.0, form="beta_abs")
+    out.backward(d_out)
+    assert betas.grad is not None and qd.grad is not None
+    with pytest.raises(ValueError):
+        ga.geometric_attn(q, k, v, c, sig, betas, m, form="nope")

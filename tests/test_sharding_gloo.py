@@ -37,13 +37,27 @@ def _dk_kernel(d_out, cs, sn, r0, r1):
     return dk_analytic(d_out[:, r0:r1], cs[:, r0:r1], sn[:, r0:r1])
 
 
-def _attn_kernel(Q, K, V, coords, spreads, mask, b, e):
+def _attn_kernel(Q, K, V, coords, spreads, mask, b, e, qb, qe):
     z, h, n, d = Q.shape
     o, lse, *_ = geoattn_grads_closed_form(Q, K, V, coords, spreads, torch.zeros_like(Q), mask, dtype=torch.float32)
     out, l2 = torch.full_like(o, float("nan")), torch.full_like(lse, float("nan"))
-    out.view(z * h, n, d)[b:e] = o.reshape(z * h, n, d)[b:e]
-    l2.view(z * h, n)[b:e] = lse.reshape(z * h, n)[b:e]
+    out.view(z * h, n, d)[b:e, qb:qe] = o.reshape(z * h, n, d)[b:e, qb:qe]
+    l2.view(z * h, n)[b:e, qb:qe] = lse.reshape(z * h, n)[b:e, qb:qe]
     return out, l2
+
+
+def _attn_bwd_kernel(Q, K, V, O, dO, lse, coords, spreads, mask, b, e, qb, qe):
+    """Stand-in for the backward kernel: only the (batch, head) pairs [b, e) and the query rows [qb, qe) contribute."""
+    z, h, n, d = Q.shape
+    d_sel = torch.zeros_like(dO)
+    d_sel.view(z * h, n, d)[b:e, qb:qe] = dO.reshape(z * h, n, d)[b:e, qb:qe]
+    _, _, dq, dk, dv, dsig = geoattn_grads_closed_form(Q, K, V, coords, spreads, d_sel, mask, dtype=torch.float32)
+    nan = float("nan")
+    dq_o, dk_o, dv_o = torch.full_like(dq, nan), torch.full_like(dk, nan), torch.full_like(dv, nan)
+    dq_o.view(z * h, n, d)[b:e, qb:qe] = dq.reshape(z * h, n, d)[b:e, qb:qe]
+    dk_o.view(z * h, n, d)[b:e] = dk.reshape(z * h, n, d)[b:e]
+    dv_o.view(z * h, n, d)[b:e] = dv.reshape(z * h, n, d)[b:e]
+    return dq_o, dk_o, dv_o, dsig
 
 
 def _worker(rank, world, port, case, ret):
@@ -73,6 +87,21 @@ def _worker(rank, world, port, case, ret):
                 out, lse, _ = sharding.geoattn_forward_sharded(q, k, v, c, sp, m, kernel=_attn_kernel)
                 o_ref, l_ref, *_ = geoattn_grads_closed_form(q, k, v, c, sp, torch.zeros_like(q), m, dtype=torch.float32)
                 assert torch.equal(out, o_ref) and torch.equal(lse, l_ref), (z, h)
+            # query-block sharding: 300 rows = 3 blocks of 128 over 2 ranks (uneven), gradients summed over the shards
+            g = torch.Generator().manual_seed(77)
+            z, h, n = 2, 2, 300
+            q, k, v, d_o = (torch.randn(z, h, n, 8, generator=g) for _ in range(4))
+            c, m = chains.chain_batch([n, 190], n, seed=6)
+            c, m = torch.from_numpy(c), torch.from_numpy(m)
+            sp = torch.linspace(3, 15, h)
+            o_ref, l_ref, dq_r, dk_r, dv_r, ds_r = geoattn_grads_closed_form(q, k, v, c, sp, d_o, m, dtype=torch.float32)
+            out, lse, rows = sharding.geoattn_forward_sharded(q, k, v, c, sp, m, kernel=_attn_kernel, by="query")
+            assert rows == ((0, 256) if rank == 0 else (256, 300))
+            assert torch.equal(out, o_ref) and torch.equal(lse, l_ref)
+            for by in ("zh", "query"):
+                dq, dk, dv, ds = sharding.geoattn_backward_sharded(q, k, v, out, d_o, lse, c, sp, m, kernel=_attn_bwd_kernel, by=by)
+                for got, ref in ((dq, dq_r), (dk, dk_r), (dv, dv_r), (ds, ds_r)):
+                    assert torch.allclose(got, ref, rtol=1e-4, atol=1e-5), by
         elif case == "peer_fails":
             if rank == 1:
                 raise RuntimeError("injected failure before the collective")

@@ -139,15 +139,17 @@ def test_row_shards_and_code_paths_agree(we, monkeypatch):
     assert not torch.isnan(out).any()
     assert rel_l2(full, out) < 1e-5 and rel_l2(fcs, cs) < 1e-5 and rel_l2(fsn, sn) < 1e-5
     ref = wf_embedding_ref(c_t.cpu(), wn.cpu(), 1, m_t.cpu(), dtype=torch.float64)
-    for env in ({"PAI_WE_NO_TMA": "1"}, {"PAI_WE_KS": "8"}, {"PAI_WE_KS": "2"}, {"PAI_WE_RANGE_REDUCE": "1"},
-                {"PAI_WE_KS": "16"}, {"PAI_WE_TJ": "64"}, {"PAI_WE_TJ": "512"}, {"PAI_WE_TJ": "36", "PAI_WE_NO_TMA": "1"}, {"PAI_WE_POLY_PAIRS": "0"}, {"PAI_WE_POLY_PAIRS": "3"}):
-        for key, val in env.items():
-            monkeypatch.setenv(key, val)
-        alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
-        for key in env:
-            monkeypatch.delenv(key)
-        assert rel_l2(ref, alt.cpu()) < OUT_TOL, env
+    # every kernel variant behind the test-only tuning entry gives the same result
     from proteusai_b200 import _lib
+    try:
+        for knobs in ({"we_no_tma": 1}, {"we_ks": 8}, {"we_ks": 2}, {"we_range_reduce": 1}, {"we_ks": 16}, {"we_tj": 64},
+                      {"we_tj": 512}, {"we_tj": 36, "we_no_tma": 1}, {"we_poly_pairs": 0}, {"we_poly_pairs": 3}):
+            _lib.tune_reset()
+            _lib.tune(**knobs)
+            alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
+            assert rel_l2(ref, alt.cpu()) < OUT_TOL, knobs
+    finally:
+        _lib.tune_reset()
     _lib.device_status()
 
 
@@ -164,11 +166,9 @@ def test_config4_long_sequence_slice_and_properties(we, monkeypatch):
     c, _ = chains.chain_batch([n], n, seed=1004)
     c_t, wn_t = torch.from_numpy(c), torch.from_numpy(chains.wavenumbers(512))
     # reproducible mode: bit-identical from run to run
-    monkeypatch.setenv("PAI_WE_REPRODUCIBLE", "1")
-    first, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
-    again, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
+    first, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None, reproducible=True)
+    again, _, _ = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None, reproducible=True)
     assert torch.equal(first, again)
-    monkeypatch.delenv("PAI_WE_REPRODUCIBLE")
     # default mode: more, shorter runs; sums may differ in the last bit only
     out, cs, sn = we.we_forward_rows(c_t.cuda(), wn_t.cuda(), 1, None)
     assert rel_l2(first, out) < 1e-5  # fp32 sums of 16384 terms grouped differently

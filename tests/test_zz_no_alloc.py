@@ -75,3 +75,32 @@ def test_static_scratch_rejects_too_many_wavenumbers():
     status = lib.pai_we_bwd_dk_static(p, p, p, p, 1, 8, 1025, 0, 8, None)
     assert status == -9
     assert b"1024" in lib.pai_status_str(status)
+
+
+def test_static_entry_point_allocates_nothing_and_keeps_one_scratch_per_device():
+    """What the entry point exists for: once the first call on a device has looked the scratch up, further calls leave
+    the amount of free device memory exactly where it was (cudaMemGetInfo), whatever K they use.  With a second GPU
+    visible the same holds there, and the results are right on both: the address kept per device is that device's own."""
+    from proteusai_b200 import _lib
+    lib = _lib.lib()
+    for dev in range(min(torch.cuda.device_count(), 2)):
+        with torch.cuda.device(dev):
+            g = torch.Generator().manual_seed(40 + dev)
+            shapes = ((2, 128, 64), (1, 77, 200), (3, 50, 1024))
+            data = [(torch.randn(z, n, 2 * k, generator=g).cuda(), torch.randn(z, n, k, generator=g).cuda(),
+                     torch.randn(z, n, k, generator=g).cuda(), torch.empty(k, device="cuda")) for z, n, k in shapes]
+            call = lambda d_out, cs, sn, dk: _lib.check(lib.pai_we_bwd_dk_static(
+                _lib.ptr(d_out), _lib.ptr(cs), _lib.ptr(sn), _lib.ptr(dk), cs.shape[0], cs.shape[1], cs.shape[2], 0, cs.shape[1],
+                _lib.current_stream()), "pai_we_bwd_dk_static")
+            call(*data[0])                       # first call on this device: looks the scratch address up
+            torch.cuda.synchronize()
+            free_before, _ = torch.cuda.mem_get_info()
+            for _ in range(3):
+                for item in data:
+                    call(*item)
+            torch.cuda.synchronize()
+            free_after, _ = torch.cuda.mem_get_info()
+            assert free_after == free_before, (dev, free_before, free_after)
+            for d_out, cs, sn, dk in data:
+                ref = (d_out[:, :, 1::2].double() * cs.double() - d_out[:, :, 0::2].double() * sn.double()).sum(dim=(0, 1))
+                assert _rel(ref, dk) < DK_TOL, dev
