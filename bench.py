@@ -38,6 +38,39 @@ def set_sequence_length(n):
     EVALS_PER_STEP = N_SEQ * (N_SEQ - 1) * K_WN
 
 SFU_NOMINAL_PAIRS_PER_CLK_SM = 8.0  # 16 SFU results per clock per SM = 8 sin+cos pairs
+# With a share of the evaluations moved to FMA-pipe polynomials both pipes can be busy at once: 8 evaluations per clock
+# on the SFU plus what the fp32 pipe has left after the 5 operations every evaluation costs it, about 12.2 per clock per SM.
+BALANCED_PIPE_PAIRS_PER_CLK_SM = 12.2
+# DRAM bytes per launch of the HBM-bound kernels, from one ncu capture each (dram__bytes_read.sum + dram__bytes_write.sum;
+# profiles/edge_rbf_n16384_ncu_full.md, profiles/encoder_row_kernels_dram.md): writes still in L2 when the launch ends are
+# not counted by the counter, so traffic sits a little below the algorithmic bytes; no re-reads in any of them.
+NCU_TRAFFIC_BYTES = {"edge_rbf_4x4x16_kernel": 445.1e6 + 4.9e6, "add_layernorm_bf16_kernel": 134.2e6 + 40.3e6,
+                     "gelu_bf16_kernel": 268.4e6 + 205.7e6}
+
+
+def hbm_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy bandwidth)"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def device_ms(fn, steps, warmup=3, flush=None):
+    """Mean device time of ``fn`` over ``steps`` calls (CUDA events on the current stream, L2 flushed between calls
+    when ``flush`` is given)."""
+    for _ in range(warmup):
+        fn()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        if flush is not None:
+            flush.zero_()
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs) / steps
 
 
 def workload():
@@ -125,11 +158,36 @@ def measured_peaks():
         return 1590.0, "fallback (earlier measurement on this pool)"
 
 
-def bench_geoattn(dev, world, rank, steps, dist):
+def geoattn_cpu_baseline(q, k, v, d_out, coords, mask, sig, lengths):
+    """The oracle (restated `torch_attn`, fp32, autograd backward) on the host cores, on ONE sample of the batch (the
+    dense formulation holds several [H, N, N] fp32 tensors per sample).  Returns a cpu_baseline dict in TFLOP/s on the
+    valid pairs of that sample."""
+    from oracle.geoattn_ref import geoattn_grads_autograd
+    torch.set_num_threads(os.cpu_count() or 1)
+    b = int(np.argmax(lengths))
+    sl = slice(b, b + 1)
+    args = (q[sl].float(), k[sl].float(), v[sl].float(), coords[sl], sig, d_out[sl].float(), mask[sl])
+    geoattn_grads_autograd(*args)  # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 3 or time.perf_counter() - t0 < 8.0:
+        geoattn_grads_autograd(*args)
+        reps += 1
+        if time.perf_counter() - t0 > 20.0:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    flop = 14.0 * GA_H * GA_D * float(lengths[b]) ** 2
+    return {"value": flop / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"sample {b} of the batch (length {int(lengths[b])}, all 8 heads), forward + autograd backward, "
+                      f"{reps} repetitions of {dt:.2f} s"}
+
+
+def bench_geoattn(dev, world, rank, steps, dist, cpu_baseline=False):
     """Geometric attention forward+backward, (batch, head) pairs sharded over the ranks.
     Returns a dict for the JSON line (rank 0) with TFLOP/s on the valid pairs and on the padded shape."""
     from proteusai_b200.utils.model_utils.attn.geometric_attn import geoattn_backward, geoattn_forward
     q, k, v, d_out, coords, mask, sig, lengths = geoattn_workload()
+    host = (q, k, v, d_out, coords, mask, sig)
     q, k, v, d_out, coords, mask, sig = (t.to(dev) for t in (q, k, v, d_out, coords, mask, sig))
     from proteusai_b200 import sharding
     z0, z1 = sharding.shard_range(GA_Z * GA_H, world, rank)
@@ -166,20 +224,63 @@ def bench_geoattn(dev, world, rank, steps, dist):
     ms = total / steps
     valid_flop = 14.0 * GA_H * GA_D * float((lengths.astype(np.float64) ** 2).sum())
     padded_flop = 14.0 * GA_Z * GA_H * GA_N * GA_N * GA_D
+    # Outside the timed region: reassemble O over the ranks once (NCCL all-gather) and check rows that ANOTHER rank
+    # computed against the CPU oracle, so that a wrong offset in the gather cannot pass unnoticed.
+    gather_check = None
+    if world > 1:
+        from oracle.geoattn_ref import geoattn_ref
+        o_all, _, _ = sharding.geoattn_forward_sharded(q, k, v, coords, sig, mask)
+        zh = ((rank + 1) % world) * ((GA_Z * GA_H + world - 1) // world)  # first pair of the next rank's shard
+        zc, hc = zh // GA_H, zh % GA_H
+        hq, hk, hv, _, hcoords, hmask, hsig = host
+        ref = geoattn_ref(hq[zc:zc + 1, hc:hc + 1].float(), hk[zc:zc + 1, hc:hc + 1].float(), hv[zc:zc + 1, hc:hc + 1].float(),
+                          hcoords[zc:zc + 1], hsig[hc:hc + 1], mask=hmask[zc:zc + 1])
+        err = torch.tensor([(o_all[zc, hc].float().cpu() - ref[0, 0]).abs().max().item()], device=dev, dtype=torch.float64)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        gather_check = float(err.item())
     peak, src = measured_peaks()
-    return {"metric": "geo-attn fwd+bwd TFLOP/s (valid pairs)", "value": valid_flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-            "padded_tflops": padded_flop / (ms * 1e-3) / 1e12, "ms_per_step": ms, "fwd_ms": fwd_ms, "dtype": "bf16",
-            "config": {"workload": "geometric attention fwd+bwd, B=8, H=8, N=1024, d_head=64, lengths U{256..1024}, seed 1003",
-                       "sharding": f"(batch, head) pairs over {world} rank(s)"},
-            "roofline": {"bound": "tensor", "achieved": valid_flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
-                         "frac": valid_flop / (ms * 1e-3) / 1e12 / peak, "peak_source": src, "traffic": None},
-            "gpu_launches": 3 * steps}
+    res = {"metric": "geo-attn fwd+bwd TFLOP/s (valid pairs)", "value": valid_flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "padded_tflops": padded_flop / (ms * 1e-3) / 1e12, "ms_per_step": ms, "fwd_ms": fwd_ms, "dtype": "bf16",
+           "config": {"workload": "geometric attention fwd+bwd, B=8, H=8, N=1024, d_head=64, lengths U{256..1024}, seed 1003",
+                      "sharding": f"(batch, head) pairs over {world} rank(s)"},
+           "roofline": {"bound": "tensor", "achieved": valid_flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                        "frac": valid_flop / (ms * 1e-3) / 1e12 / peak, "peak_source": src, "traffic": None,
+                        "note": "compute-bound kernels: DRAM traffic (about 0.1 GB per step) is not the limiter"},
+           "gather_check_max_abs": gather_check,
+           "gpu_launches": 3 * steps}
+    if cpu_baseline and rank == 0:
+        res["cpu_baseline"] = geoattn_cpu_baseline(*host, lengths)
+    return res
 
 
 EN_Z, EN_N, EN_SEED = 64, 1024, 1005
 
 
-def bench_encoder(dev, world, rank, steps, dist, graphed=False):
+def encoder_cpu_baseline(model, lengths):
+    """The oracle composition of the same model (fp32 arithmetic on its weights, CPU restatements of both kernels) on the
+    host cores, on a bounded sample: one chain of the batch's median length, unpadded."""
+    from oracle.encoder_ref import encoder_forward_ref
+    from proteusai_b200 import synthetic as chains
+    torch.set_num_threads(os.cpu_count() or 1)
+    n = int(np.sort(lengths)[len(lengths) // 2])
+    coords, mask = chains.chain_batch([n], n, seed=EN_SEED)
+    tokens = torch.randint(0, 33, (1, n), generator=torch.Generator().manual_seed(EN_SEED))
+    args = (model, tokens, torch.from_numpy(coords), torch.from_numpy(mask))
+    with torch.no_grad():
+        encoder_forward_ref(*args)  # warm-up
+        t0 = time.perf_counter()
+        reps = 0
+        while reps < 2 or time.perf_counter() - t0 < 6.0:
+            encoder_forward_ref(*args)
+            reps += 1
+            if time.perf_counter() - t0 > 20.0:
+                break
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": n / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"one chain of {n} residues (the batch's median length), unpadded, {reps} repetitions of {dt:.2f} s"}
+
+
+def bench_encoder(dev, world, rank, steps, dist, graphed=False, cpu_baseline=False):
     """Encoder inference (bf16, random weights): token embedding (vocabulary 33 -> 512) + wavefunction embedding, 4 post-norm
     layers of geometric attention (H=8, sigma 3..15 A) and a 2048-wide GELU FFN, linear head to 20 logits.  64 chains with
     lengths uniform in 64..1024 padded to 1024, data-parallel: each rank takes a contiguous slice of the batch.  Returns
@@ -224,7 +325,31 @@ def bench_encoder(dev, world, rank, steps, dist, graphed=False):
     res = {"metric": "encoder inference tokens/s (valid tokens, host inputs and outputs included)", "value": valid_tokens / (ms * 1e-3),
            "unit": "tokens/s", "padded_tokens_per_s": EN_Z * EN_N / (ms * 1e-3), "ms_per_step": ms, "dtype": "bf16",
            "config": {"workload": "4-layer geometric-attention encoder, d_model 512, H 8, FFN 2048, 64 chains of 64..1024 padded to 1024, seed 1005",
-                      "sharding": f"batch over {world} rank(s), no collective"}}
+                      "sharding": f"batch over {world} rank(s), no collective"},
+           "e2e": {"value": valid_tokens / (ms * 1e-3), "unit": "tokens/s",
+                   "h2d_bytes_per_step": int(coords_p.numel() * 4 + mask_p.numel() + tokens_p.numel() * 8) * world,
+                   "d2h_bytes_per_step": int(out_host.numel() * 2) * world}}
+    if world == 1:
+        # the two HBM-bound row kernels of the block, timed alone on this batch's shapes, with their ncu DRAM traffic
+        from proteusai_b200.utils.model_utils.base_modules import fused_ops
+        rows = (b1 - b0) * EN_N
+        x = torch.randn(rows, 512, device=dev).to(torch.bfloat16)
+        w = torch.ones(512, device=dev, dtype=torch.bfloat16)
+        hbuf = torch.randn(rows, 2048, device=dev).to(torch.bfloat16)
+        ln_ms = device_ms(lambda: fused_ops.add_layernorm(x, x, w, w, 1e-5), steps)
+        ge_ms = device_ms(lambda: fused_ops.gelu(hbuf, inplace=True), steps)
+        peak, src = hbm_peak()
+        ln_bytes, ge_bytes = rows * 512 * 2 * 3, rows * 2048 * 2 * 2
+        res["row_kernels"] = [
+            {"kernel": "add_layernorm_bf16_kernel", "ms": ln_ms, "roofline": {
+                "bound": "hbm", "achieved": ln_bytes / (ln_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_source": src,
+                "frac": ln_bytes / (ln_ms * 1e-3) / 1e9 / peak, "traffic": NCU_TRAFFIC_BYTES["add_layernorm_bf16_kernel"] * rows / 65536}},
+            {"kernel": "gelu_bf16_kernel", "ms": ge_ms, "roofline": {
+                "bound": "hbm", "achieved": ge_bytes / (ge_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s", "peak_source": src,
+                "frac": ge_bytes / (ge_ms * 1e-3) / 1e9 / peak, "traffic": NCU_TRAFFIC_BYTES["gelu_bf16_kernel"] * rows / 65536}}]
+    if cpu_baseline and rank == 0:
+        res["cpu_baseline"] = encoder_cpu_baseline(model.float().cpu(), lengths)
+        model.to(dev).to_compute_dtype_(torch.bfloat16)
     if graphed:
         # The same forward captured once into a CUDA graph and replayed: inputs are copied into static device buffers,
         # the graph runs, the logits are copied out.  Removes the host's per-kernel launch work from the step.
@@ -310,7 +435,8 @@ def bench_graph(dev, steps, cpu_baseline):
            "knn_ms": knn_ms, "edge_rbf_ms": rbf_ms, "edge_rbf_layernorm_ms": rbf_ln_ms, "dtype": "f32",
            "config": {"workload": f"one chain, N={n}, K={k}, 4 atoms per node, 16 RBF centres, seed {SEED}", "sharding": "rank 0 only"},
            "roofline": {"bound": "hbm", "kernel": "edge_rbf_4x4x16_kernel", "achieved": out_bytes / (rbf_ms * 1e-3) / 1e9, "peak": peak,
-                        "unit": "GB/s", "frac": out_bytes / (rbf_ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None},
+                        "unit": "GB/s", "frac": out_bytes / (rbf_ms * 1e-3) / 1e9 / peak, "peak_source": src,
+                        "traffic": NCU_TRAFFIC_BYTES["edge_rbf_4x4x16_kernel"]},
            "gpu_launches": 2 * steps}
     if cpu_baseline:
         from oracle.gnn_ref import edge_rbf_ref, get_neighbors_ref
@@ -324,6 +450,49 @@ def bench_graph(dev, steps, cpu_baseline):
         res["cpu_baseline"] = {"value": ns / dt, "unit": "nodes/s", "cores": torch.get_num_threads(), "kind": "port",
                                "sample": f"first {ns} nodes of the chain as a chain of their own (dense N x N formulation), {dt:.2f} s"}
     return res
+
+
+def bench_we_aniso(dev, steps, sfu_rate, nominal, flush):
+    """Anisotropic WE (per-wavenumber C-beta scaling, the variant the reference's model calls) forward at the headline
+    shape: one chain, N = 16384, 256 wavenumbers.  SFU-bound like the isotropic kernel: one sin + one cos per evaluation."""
+    from proteusai_b200.utils.model_utils.wf_embedding.anisotropic.cb_scaling.learnable_wavenumbers.cuda.wf_embedding import \
+        we_aniso_forward_rows
+    coords_h, wn_h = workload()
+    g = torch.Generator().manual_seed(SEED)
+    cb = torch.randn(coords_h.shape, generator=g)
+    cb = (cb / torch.linalg.vector_norm(cb, dim=2, keepdim=True)).to(dev)
+    cbm = torch.rand(wn_h.shape, generator=g).to(dev)
+    c, wn = coords_h.to(dev), wn_h.to(dev)
+    ms = device_ms(lambda: we_aniso_forward_rows(c, cb, cbm, wn, None, 0, N_SEQ), steps, flush=flush)
+    achieved = EVALS_PER_STEP / (ms * 1e-3)
+    return {"metric": f"anisotropic WE pair*wavenumber evals/s @N={N_SEQ},d=512", "value": achieved, "unit": "evals/s", "ms_per_step": ms,
+            "dtype": "f32", "config": {"workload": f"anisotropic (C-beta scaling) WE forward, Z=1, N={N_SEQ}, 256 wavenumbers, seed {SEED}",
+                                       "sharding": "rank 0 only"},
+            "roofline": {"bound": "sfu", "kernel": "we_aniso_fwd_kernel", "achieved": achieved / 1e9, "peak": nominal / 1e9,
+                         "unit": "Geval/s", "frac": achieved / nominal, "peak_source": "nominal: 8 sin+cos pairs per clock per SM at the maximum SM clock",
+                         "peak_measured": sfu_rate / 1e9, "frac_of_measured": achieved / sfu_rate, "traffic": None},
+            "gpu_launches": steps}
+
+
+def bench_we_bwd(dev, steps, flush):
+    """WE backward (wavenumber gradient from the stored sums) at Z = 8, N = 16384, K = 256: 16 bytes read per (z, n, k),
+    537 MB per call, HBM-bound."""
+    from proteusai_b200.utils.model_utils.wf_embedding.isotropic.cuda.wf_embedding import we_backward_dk
+    z, n, k = 8, 16384, K_WN
+    g = torch.Generator(device=dev).manual_seed(SEED)
+    d_out = torch.randn(z, n, 2 * k, device=dev, generator=g)
+    cs, sn = torch.randn(z, n, k, device=dev, generator=g), torch.randn(z, n, k, device=dev, generator=g)
+    ms = device_ms(lambda: we_backward_dk(d_out, cs, sn), steps, flush=flush)
+    nbytes = z * n * k * 16
+    peak, src = hbm_peak()
+    return {"metric": "WE backward (z,n,k) triples/s @Z=8,N=16384,K=256", "value": z * n * k / (ms * 1e-3), "unit": "triples/s",
+            "ms_per_step": ms, "dtype": "f32",
+            "config": {"workload": "WE backward dk, Z=8, N=16384, K=256, N(0,1) inputs", "sharding": "rank 0 only",
+                       "l2": "flushed between timed calls; inputs 537 MB"},
+            "roofline": {"bound": "hbm", "kernel": "we_bwd_partial_kernel", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None,
+                         "note": "through the public call: the two kernels plus the workspace allocation"},
+            "gpu_launches": 2 * steps}
 
 
 def cpu_port_rate(coords, wn, target_s=12.0, chunk=32):
@@ -486,6 +655,19 @@ def main():
         step_e2e()
     e2e_ms = timed(step_e2e, args.steps, use_events=False)
 
+    # Outside the timed region: rows that ANOTHER rank computed, as they arrived through the all-gather, against the CPU
+    # oracle (64 rows from the middle of the next rank's shard); the largest error over the ranks goes into the line.
+    gather_check = None
+    if world > 1:
+        from oracle.we_ref import rel_l2, wf_embedding_ref
+        step_resident()
+        o0, o1 = sharding.shard_range(N_SEQ, world, (rank + 1) % world)
+        a = (o0 + o1) // 2
+        ref = wf_embedding_ref(coords_h, wn_h, 1, rows=(a, a + 64), chunk=32)
+        err = torch.tensor([rel_l2(ref, out[:, a:a + 64].cpu())], device=dev, dtype=torch.float64)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        gather_check = float(err.item())
+
     value = EVALS_PER_STEP * args.steps / (total_ms * 1e-3)
     e2e_value = EVALS_PER_STEP * args.steps / (e2e_ms * 1e-3)
     line = None
@@ -495,6 +677,7 @@ def main():
         evals_per_launch = (r1 - r0) * (N_SEQ - 1) * K_WN
         achieved = evals_per_launch / (kern_ms * 1e-3)
         nominal = SFU_NOMINAL_PAIRS_PER_CLK_SM * sms * (clocks["sm_max_mhz"] or 1965) * 1e6
+        balanced = BALANCED_PIPE_PAIRS_PER_CLK_SM * sms * (clocks["sm_max_mhz"] or 1965) * 1e6
         line = {
             "metric": f"WE pair*wavenumber evals/s @N={N_SEQ},d=512", "value": value, "unit": "evals/s",
             "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": total_ms / args.steps,
@@ -508,10 +691,16 @@ def main():
                     "h2d_bytes_per_step": int(coords_pin.numel() * 4 + wn_pin.numel() * 4) * world,
                     "d2h_bytes_per_step": int(N_SEQ * 2 * K_WN * 4), "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": args.steps,
-            "roofline": {"bound": "sfu", "achieved": achieved / 1e9, "peak": sfu_rate / 1e9, "unit": "Geval/s",
-                         "frac": achieved / sfu_rate, "traffic": None,
-                         "peak_source": "measured live: register-only sin+cos loop on this GPU (pai_measure_sfu_peak)",
-                         "peak_nominal": nominal / 1e9, "frac_of_nominal": achieved / nominal,
+            "gather_check": gather_check,
+            "roofline": {"bound": "sfu", "achieved": achieved / 1e9, "peak": nominal / 1e9, "unit": "Geval/s",
+                         "frac": achieved / nominal, "traffic": None,
+                         "peak_source": "nominal: 16 SFU results = 8 sin+cos pairs per clock per SM x SMs x the maximum SM clock "
+                                        "(MEASURED_PEAKS.json holds no SFU figure; HBM and tensor peaks do not bound this kernel)",
+                         "peak_measured": sfu_rate / 1e9, "frac_of_measured": achieved / sfu_rate,
+                         "peak_measured_source": "live: register-only sin+cos loop on this GPU (pai_measure_sfu_peak)",
+                         "balanced_pipe_peak": balanced / 1e9, "frac_of_balanced": achieved / balanced,
+                         "balanced_pipe_note": "bound with SFU and fp32 pipes both busy (12.2 evaluations per clock per SM): applies "
+                                               "because one pair in eight per lane is evaluated by an FMA-pipe polynomial",
                          "kernel": "we_fwd_kernel", "kernel_ms": kern_ms,
                          "evals_per_launch": evals_per_launch},
         }
@@ -521,15 +710,21 @@ def main():
             line["cpu_baseline"] = {"value": rate, "unit": "evals/s", "cores": torch.get_num_threads(), "kind": "port",
                                     "sample": f"{rows} of {N_SEQ} observer rows x all sources x {K_WN} wavenumbers, {secs:.1f} s"}
     ga = None
-    if N_SEQ == 16384 or args.geoattn:
-        ga = bench_geoattn(dev, world, rank, args.steps, dist)
+    full = N_SEQ == 16384 or args.geoattn
+    want_cpu = world == 1 and not args.no_cpu_baseline
+    if full:
+        ga = bench_geoattn(dev, world, rank, max(args.steps, 20), dist, cpu_baseline=want_cpu)
     enc = None
-    if N_SEQ == 16384 or args.geoattn:
-        enc = bench_encoder(dev, world, rank, args.steps, dist, graphed=args.graph_encoder)
+    if full:
+        enc = bench_encoder(dev, world, rank, args.steps, dist, graphed=args.graph_encoder, cpu_baseline=want_cpu)
     if rank == 0:
         line["geoattn"] = ga
         line["encoder"] = enc
-        line["graph"] = bench_graph(dev, args.steps, world == 1 and not args.no_cpu_baseline) if (N_SEQ == 16384 or args.geoattn) else None
+        line["graph"] = bench_graph(dev, args.steps, want_cpu) if full else None
+        if N_SEQ == 16384:
+            del out, cs, sn
+            line["we_aniso"] = bench_we_aniso(dev, args.steps, sfu_rate, nominal, flush)
+            line["we_bwd"] = bench_we_bwd(dev, args.steps, flush)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

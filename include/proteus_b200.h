@@ -336,7 +336,8 @@ enum pai_tune_key {
     PAI_TUNE_WE_NO_TMA = 5,       /* 1: plain loads instead of bulk copies for the source tiles */
     PAI_TUNE_GA_NO_FAR_SKIP = 6,  /* 1: evaluate the RBF of every key group, however far */
     PAI_TUNE_GA_NO_ORDER = 7,     /* 1: issue the samples in natural order instead of longest first */
-    PAI_TUNE_COUNT = 8
+    PAI_TUNE_WE_NO_MIXED = 8,     /* 1: every warp evaluates on both pipes instead of separate SFU and polynomial warps */
+    PAI_TUNE_COUNT = 9
 };
 int pai_tune_set(int key, int value);
 int pai_selftest_wait_timeout(void *stream);

@@ -243,7 +243,12 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_aniso_fwd_kerne
     cur_item = -1;
     if (!p.counter) break;
     }
-    if (timed_out && tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
+    if (timed_out && tid == 0) {
+        atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
+        // the copies that may still be in flight target this CTA's shared memory: give them a bounded chance to land
+        mbar_wait_bounded(&sm.bar[0], (uint32_t)((n >> 1) & 1), 1u << 12);
+        mbar_wait_bounded(&sm.bar[1], (uint32_t)((n >> 1) & 1), 1u << 12);
+    }
 }
 
 static int we_aniso_fwd_launch(WeAnisoParams p, int Z, int sms, unsigned *counter, cudaStream_t stream) {

@@ -61,7 +61,7 @@ struct __align__(16) WeSmem {
     float stage[2][3][WE_TJ_MAX];  // x/y/z planes, two stages
     float4 tile[WE_TJ_MAX];        // repacked {x,y,z,valid}
     uint64_t bar[2];
-    int hi[2][WE_WARPS];
+    int hi[2][8];
     unsigned run;
 };
 
@@ -89,10 +89,12 @@ __device__ __forceinline__ uint32_t we_hash_mix(uint32_t h) {
 //     hash of (batch element, observer, source, wavenumber index, seed) is mapped to [0, 1] and the evaluation is
 //     kept when that is >= p; kept real and imaginary parts (and with them the stored sums) are scaled by 1/(1-p).
 //     The comparison (float)h / 2^32 >= p is done on the integer: the host passes the smallest h that passes.
-template <int KS, bool MAG1, bool RR, int NP, bool DROP = false>
-__global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(const WeFwdParams p) {
-    __shared__ WeSmem sm;
+// The body of a warp: KS wavenumbers per lane starting `kslice0` wavenumbers into the CTA's group of `GROUP`; the CTA has
+// THREADS threads, all of which walk the same runs, units and barriers whatever their KS and NP.
+template <int KS, bool MAG1, bool RR, int NP, bool DROP, int THREADS, int GROUP>
+__device__ __forceinline__ void we_fwd_body(const WeFwdParams &p, WeSmem &sm, const int kslice0) {
     constexpr int KP = KS / 2;
+    constexpr int NWARPS = THREADS / 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int N = p.N, K = p.K;
     const bool tma = p.use_tma != 0;
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
             const int ob = (int)(rest % p.obs_blocks);
             z = (int)(rest / p.obs_blocks);
             row = p.row_begin + ob * 32 + lane;
-            k0 = (kg * WE_WARPS + warp) * KS;
+            k0 = kg * GROUP + kslice0;
             row_in = row < p.row_end;
             const float *czi = p.coords + (size_t)z * 3 * N;
             ov = false;
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
         }
         // repack to {x,y,z,valid}; find the end of the valid sources of this tile
         int mine = 0;
-        for (int j = tid; j < cnt; j += WE_THREADS) {
+        for (int j = tid; j < cnt; j += THREADS) {
             float4 s;
             if (tma) {
                 s.x = sm.stage[st][0][j];
@@ -253,7 +255,9 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
         if (lane == 0) sm.hi[st][warp] = mine;
         __syncthreads();  // also publishes sm.tile (sm.hi[st] is next written two units later, after two more barriers)
         // sources past the last valid one of the tile (the padded tail of a sample) are not looped over
-        const int hi = max(max(sm.hi[st][0], sm.hi[st][1]), max(sm.hi[st][2], sm.hi[st][3]));
+        int hi = 0;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) hi = max(hi, sm.hi[st][w]);
         if (hi == 0 || !item_live) continue;
 
 #pragma unroll 2
@@ -324,8 +328,33 @@ __global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(cons
     cur_item = -1;
     if (!p.counter) break;
     }
-    if (timed_out && tid == 0) atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
-    // (after a time-out the one copy that may still be in flight targets this CTA's own shared memory)
+    if (timed_out && tid == 0) {
+        atomicExch(&g_device_status, (int)PAI_ERR_DEVICE_WAIT_TIMEOUT);
+        // the one copy that may still be in flight targets this CTA's shared memory: give it a bounded chance to land
+        mbar_wait_bounded(&sm.bar[0], (uint32_t)((n >> 1) & 1), 1u << 12);
+        mbar_wait_bounded(&sm.bar[1], (uint32_t)((n >> 1) & 1), 1u << 12);
+    }
+}
+
+template <int KS, bool MAG1, bool RR, int NP, bool DROP = false>
+__global__ void __launch_bounds__(WE_THREADS, WE_CTAS_PER_SM) we_fwd_kernel(const WeFwdParams p) {
+    __shared__ WeSmem sm;
+    we_fwd_body<KS, MAG1, RR, NP, DROP, WE_THREADS, WE_WARPS * KS>(p, sm, (int)(threadIdx.x >> 5) * KS);
+}
+
+// The fast path (1/r magnitude, no dropout) with the two pipes fed by DIFFERENT warps: eight warps per CTA, warp w and
+// warp w + 4 sit on the same scheduler and share 16 wavenumbers of the CTA's group of 64; warp w evaluates WE_MIX_SFU of
+// them with sin.approx / cos.approx (SFU pipe), warp w + 4 the other WE_MIX_POLY with the polynomial (FMA pipe).  Mixed
+// inside one warp the long Horner chains and the SFU instructions queue behind each other in the warp's in-order issue;
+// in separate warps the scheduler interleaves them and both pipes stay busy.
+constexpr int WE_MIX_SFU = 10, WE_MIX_POLY = 6, WE_MIX_THREADS = 256, WE_MIX_CTAS_PER_SM = 2;
+static_assert(WE_MIX_SFU + WE_MIX_POLY == 16, "a warp pair covers 16 wavenumbers");
+
+__global__ void __launch_bounds__(WE_MIX_THREADS, WE_MIX_CTAS_PER_SM) we_fwd_mixed_kernel(const WeFwdParams p) {
+    __shared__ WeSmem sm;
+    const int warp = threadIdx.x >> 5;
+    if (warp < 4) we_fwd_body<WE_MIX_SFU, true, false, 0, false, WE_MIX_THREADS, 64>(p, sm, warp * 16);
+    else we_fwd_body<WE_MIX_POLY, true, false, WE_MIX_POLY / 2, false, WE_MIX_THREADS, 64>(p, sm, (warp - 4) * 16 + WE_MIX_SFU);
 }
 
 template <int KS, int NP>
@@ -347,12 +376,12 @@ static void we_fwd_launch_np(const WeFwdParams &p, bool rr, unsigned grid, cudaS
 
 template <int KS>
 static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint, int waves, bool reproducible, int npoly,
-                            unsigned *counter, cudaStream_t stream) {
+                            bool mixed, unsigned *counter, cudaStream_t stream) {
     const int rows = p.row_end - p.row_begin;
     p.obs_blocks = (rows + 31) / 32;
-    p.k_groups = (p.K + WE_WARPS * KS - 1) / (WE_WARPS * KS);
+    p.k_groups = (p.K + WE_WARPS * KS - 1) / (WE_WARPS * KS);  // (the mixed kernel's groups are 64 wide like those of KS = 16)
     const long long items = (long long)Z * p.obs_blocks * p.k_groups;
-    const long long resident = (long long)sms * WE_CTAS_PER_SM;
+    const long long resident = (long long)sms * (mixed ? WE_MIX_CTAS_PER_SM : WE_CTAS_PER_SM);
     // tile size: as large as possible while every resident CTA still gets several units
     int tj = WE_TJ_MAX;
     if (tj_hint > 0) {
@@ -393,6 +422,10 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
         cudaError_t ce = cudaMemsetAsync(p.counter, 0, sizeof(unsigned), stream);
         if (ce != cudaSuccess) return (int)ce;
     }
+    if (mixed) {
+        we_fwd_mixed_kernel<<<grid, WE_MIX_THREADS, 0, stream>>>(p);
+        return (int)cudaPeekAtLastError();
+    }
     // pairs evaluated on the FMA pipe (KS = 16 has 8 pairs per lane)
     if (KS == 16) {
         switch (npoly) {
@@ -409,15 +442,18 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
 
 // ks_hint: 0 = choose; otherwise 2, 8 or 16.  tj_hint: 0 = choose; otherwise a multiple of 4 in
 // [4, 512].  waves: 0 = choose; otherwise CTAs launched per resident CTA slot.  rr: explicit range reduction.  The three outputs must already be zero over the row range.
+// `mixed_ok`: the caller allows the kernel with separate SFU and polynomial warps (it is used for the 1/r magnitude without
+// dropout or explicit range reduction, when the lane width is the default 16 and npoly is the default 1).
 static int we_fwd_launch(const WeFwdParams &p, int Z, int ks_hint, int tj_hint, int waves, bool reproducible, bool rr,
-                         int npoly, int sms, unsigned *counter, cudaStream_t stream) {
+                         int npoly, bool mixed_ok, int sms, unsigned *counter, cudaStream_t stream) {
     int ks = ks_hint;
     if (ks == 0) ks = p.K >= 64 ? 16 : (p.K >= 32 ? 8 : 2);
     if (tj_hint < 0 || tj_hint > WE_TJ_MAX || (tj_hint & 3) || waves < 0 || waves > 64) return (int)PAI_ERR_UNSUPPORTED;
+    const bool mixed = mixed_ok && ks == 16 && ks_hint == 0 && p.mag_type == 1 && !rr && p.drop_scale == 0.f && npoly == 1;
     switch (ks) {
-        case 16: return we_fwd_launch_ks<16>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
-        case 8: return we_fwd_launch_ks<8>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
-        case 2: return we_fwd_launch_ks<2>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, counter, stream);
+        case 16: return we_fwd_launch_ks<16>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, mixed, counter, stream);
+        case 8: return we_fwd_launch_ks<8>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, false, counter, stream);
+        case 2: return we_fwd_launch_ks<2>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, false, counter, stream);
         default: return (int)PAI_ERR_UNSUPPORTED;
     }
 }
