@@ -147,11 +147,14 @@ __device__ __forceinline__ void ga_stage_rows(GaQueryRows &rw, int tid, bool ok,
 // MASKED: the key tile or the query tile holds a padded token (validity is then applied by selection, so whatever
 // the padding holds, Inf or NaN included, never reaches a result).  `far` (warp-uniform): the 16 queries are too far
 // from the warp's keys for R to count.
-template <bool MASKED, int FORM, int OFF>
-__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], bool far, const GaQueryRows &rw, int p0,
+// FAR: 0 = near (R evaluated), 1 = far, 2 = decided at run time by `far_rt`; with 0 or 1 the body is branch-free, so the two
+// groups of a pass form one straight-line block.
+template <bool MASKED, int FORM, int OFF, int FAR>
+__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], bool far_rt, const GaQueryRows &rw, int p0,
                                              const GaBwdKey &key, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
                                              f2_t &dbeta2, uint32_t (&pw)[16], uint32_t (&dw)[16]) {
     constexpr int POFF = OFF / 2;
+    const bool far = FAR == 2 ? far_rt : (FAR == 1);
     const f2_t one2 = f2_pack(1.f, 1.f);
     if (far && FORM == 1 && fm.far_masked) {  // every pair of the group is outside the RBF window: P = 0
 #pragma unroll
@@ -352,19 +355,19 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     // per-query inputs of a tile: thread tid < 128 loads query tile*128 + tid
     auto row_inputs = [&](int tile, bool &ok, float &x, float &y, float &zc, float &l2, float &dsum) {
-        const int i = tile * GA_BM + tid;
-        ok = i < N && (vz ? vz[i] != 0 : true);
-        x = y = zc = 0.f;
-        l2 = INFINITY;  // +inf: P = 0 for a padded query
-        dsum = 0.f;
-        if (ok) {
-            x = cz[i * 3] - orx;
-            y = cz[i * 3 + 1] - ory;
-            zc = cz[i * 3 + 2] - orz;
-            const float lse = p.lse[(size_t)zh * N + i];
-            l2 = lse == -INFINITY ? INFINITY : lse * 1.4426950408889634f;  // a row without any valid pair: P = 0
-            dsum = p.dsum[(size_t)zh_local * N + i];
-        }
+        // (all loads issued at once from a clamped index: none waits for the validity byte)
+        const int i = tile * GA_BM + tid, ic = min(i, N - 1);
+        const uint8_t vb = vz ? vz[ic] : (uint8_t)1;
+        const float gx = cz[ic * 3], gy = cz[ic * 3 + 1], gz = cz[ic * 3 + 2];
+        const float lse = p.lse[(size_t)zh * N + ic];
+        const float dsv = p.dsum[(size_t)zh_local * N + ic];
+        ok = i < N && vb != 0;
+        x = ok ? gx - orx : 0.f;
+        y = ok ? gy - ory : 0.f;
+        zc = ok ? gz - orz : 0.f;
+        // +inf: P = 0 for a padded query and for a row without any valid pair
+        l2 = (ok && lse != -INFINITY) ? lse * 1.4426950408889634f : INFINITY;
+        dsum = ok ? dsv : 0.f;
     };
     if (tid < GA_BM) {
         bool ok;
@@ -395,36 +398,42 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
                 tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
             };
-            auto issue_s_dp = [&](int b) {  // S^T = K Q^T, dP^T = V dO^T: 4 + 4 MMAs of K = 16 over d = 64
-                const uint32_t q_addr = smem_u32(sm.q[b]), do_addr = smem_u32(sm.dout[b]);
+            // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
+            const uint64_t k_km = umma_desc_sw128(k_addr, 16, 1024), v_km = umma_desc_sw128(v_addr, 16, 1024);  // K-major operands
+            const uint64_t k_mn = umma_desc_sw128(k_addr, 0, 1024);                                              // B of dQ
+            uint64_t q_km[2], do_km[2], q_mn[2], do_mn[2], ds_km[2], ds_mn[2];
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                q_km[b] = umma_desc_sw128(smem_u32(sm.q[b]), 16, 1024);
+                do_km[b] = umma_desc_sw128(smem_u32(sm.dout[b]), 16, 1024);
+                q_mn[b] = umma_desc_sw128(smem_u32(sm.q[b]), 0, 1024);
+                do_mn[b] = umma_desc_sw128(smem_u32(sm.dout[b]), 0, 1024);
+                ds_km[b] = umma_desc_sw128(smem_u32(sm.ds[b]), 16, 1024);
+                ds_mn[b] = umma_desc_sw128(smem_u32(sm.ds[b]), GA_TILE_BYTES, 1024);
+            }
+            auto issue_s_dp = [&](int b) {  // S^T = K Q^T, dP^T = V dO^T: 4 + 4 MMAs of K = 16 over d = 64 (32 B per step)
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_s, umma_desc_sw128(k_addr + kk * 32, 16, 1024), umma_desc_sw128(q_addr + kk * 32, 16, 1024),
-                            IDESC_SP, kk > 0 ? 1u : 0u);
+                    umma_ss(tm_s, k_km + (uint64_t)(kk * 2), q_km[b] + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_dp, umma_desc_sw128(v_addr + kk * 32, 16, 1024), umma_desc_sw128(do_addr + kk * 32, 16, 1024),
-                            IDESC_SP, kk > 0 ? 1u : 0u);
+                    umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), do_km[b] + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_sp);
             };
             auto issue_dv_dk = [&](int b, bool first_tile) {  // K = 16 queries per step
-                const uint32_t q_addr = smem_u32(sm.q[b]), do_addr = smem_u32(sm.dout[b]), ds_addr = smem_u32(sm.ds[b]);
 #pragma unroll
                 for (int kk = 0; kk < GA_BM / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
-                    umma_ts(tm_dv, tm_p + kk * 8, umma_desc_sw128(do_addr + kk * 2048, 0, 1024), IDESC_KN,
-                            (first_tile && kk == 0) ? 0u : 1u);
+                    umma_ts(tm_dv, tm_p + kk * 8, do_mn[b] + (uint64_t)(kk * 128), IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
 #pragma unroll
-                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dK += dS^T Q: dS^T advances 32 B inside the swizzled row
-                    umma_ss(tm_dk, umma_desc_sw128(ds_addr + (kk >> 2) * GA_TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                            umma_desc_sw128(q_addr + kk * 2048, 0, 1024), IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
+                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dK += dS^T Q: dS^T advances 32 B inside the swizzled row, second sub-tile after 64
+                    umma_ss(tm_dk, ds_km[b] + (uint64_t)((kk >> 2) * (GA_TILE_BYTES >> 4) + (kk & 3) * 2), q_mn[b] + (uint64_t)(kk * 128),
+                            IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
                 umma_commit(&sm.bar_vk);
             };
             auto issue_dq = [&](int b) {  // dQ = dS K: K = 16 keys per step, 2 KiB down the dS^T tile (M = queries: two sub-tiles)
-                const uint32_t ds_addr = smem_u32(sm.ds[b]);
 #pragma unroll
                 for (int kk = 0; kk < GA_BN / 16; ++kk)
-                    umma_ss(tm_dq, umma_desc_sw128(ds_addr + kk * 2048, GA_TILE_BYTES, 1024),
-                            umma_desc_sw128(k_addr + kk * 2048, 0, 1024), IDESC_NN, kk > 0 ? 1u : 0u);
+                    umma_ss(tm_dq, ds_mn[b] + (uint64_t)(kk * 128), k_mn + (uint64_t)(kk * 128), IDESC_NN, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_dq);
             };
             bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag);
@@ -557,15 +566,21 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 }
                 uint32_t pw[16], dw[16];
                 const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
-#define PAI_GA_BWD2(MASKED, FORM)                                                                                          \
-    do {                                                                                                                   \
-        ga_bwd_chunk<MASKED, FORM, 0>(sv, dpv, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);      \
-        ga_bwd_chunk<MASKED, FORM, 16>(sv, dpv, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
+#define PAI_GA_BWD2(MASKED, FORM, MODE)                                                                                          \
+    do {                                                                                                                         \
+        ga_bwd_chunk<MASKED, FORM, 0, MODE>(sv, dpv, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);      \
+        ga_bwd_chunk<MASKED, FORM, 16, MODE>(sv, dpv, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
     } while (0)
                 if (p.form == 0) {
-                    if (masked) PAI_GA_BWD2(true, 0); else PAI_GA_BWD2(false, 0);
+                    if (!far0 && !far1) {
+                        if (masked) PAI_GA_BWD2(true, 0, 0); else PAI_GA_BWD2(false, 0, 0);
+                    } else if (far0 && far1) {
+                        if (masked) PAI_GA_BWD2(true, 0, 1); else PAI_GA_BWD2(false, 0, 1);
+                    } else {
+                        if (masked) PAI_GA_BWD2(true, 0, 2); else PAI_GA_BWD2(false, 0, 2);
+                    }
                 } else {
-                    if (masked) PAI_GA_BWD2(true, 1); else PAI_GA_BWD2(false, 1);
+                    if (masked) PAI_GA_BWD2(true, 1, 2); else PAI_GA_BWD2(false, 1, 2);
                 }
 #undef PAI_GA_BWD2
                 // P^T(t-1) is read by dV(t-1), the dS^T buffer of tile t-2 by dK / dQ(t-2): no store before dV, dK(t-1)

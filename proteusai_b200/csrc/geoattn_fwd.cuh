@@ -10,17 +10,22 @@
 // Query row r = TMEM lane r is shared by two math threads: warp w (0..3) takes key columns 0..63 of a
 // tile and output columns 0..31, warp w + 4 takes key columns 64..127 and output columns 32..63 (both
 // may touch TMEM lanes 32 (w % 4) ..).  Lane 0 of the producer warp issues every TMA load and MMA.
-// Tensor memory (256 columns): S [0,128) fp32, O [128,192) fp32, P [192,256) bf16 pairs.
+// Tensor memory: S [0,128) fp32, O [128,192) fp32, P [192,256) bf16 pairs, G [256,384) fp32.
 //   S  = Q K^T : tcgen05.mma, A = Q tile, B = K tile (both K-major, 128-byte swizzle, via TMA);
-//   softmax    : each math thread reads its 64 logits ONCE into registers (tcgen05.ld) and releases the S
-//                columns at once, so the tensor core computes S of the next key tile underneath the
-//                softmax of this one.  scale * (1 + R) in packed fp32x2 arithmetic; |r_i - r_j|^2 comes
-//                from three FMAs on coordinates centred on the tile's first valid query.  A group of
-//                16 keys whose bounding sphere lies farther than 5.9 sigma_h from the bounding sphere of
-//                the warp's 32 queries has R < 2^-25 for every pair, where S (1 + R) == S in fp32: there
-//                the exponential and the distance arithmetic are skipped (most of the off-diagonal
-//                work of the narrow heads).  The two halves of a row exchange their maxima through shared
-//                memory; P is written as bf16 straight into tensor memory;
+//   G          : the geometry of the tile comes from the tensor core as well: G_ij = |k_j|^2 - 2 q_i . k_j
+//                (coordinates centred on the tile's first valid query) is a product of two narrow operand tiles
+//                that the threads write themselves, each fp32 coordinate split into three bf16 terms
+//                (ga_write_geo_row), so that |r_i - r_j|^2 = G_ij + |q_i|^2 to fp32 accuracy.  Reading key
+//                coordinates from shared memory instead costs every warp a broadcast load per key pair, which
+//                made the shared-memory pipe, not the SFU, the limiter of this stage;
+//   softmax    : each math thread reads its 64 G values and 64 logits ONCE into registers (tcgen05.ld) and
+//                releases the columns, so the tensor core computes the next key tile underneath the
+//                softmax of this one.  R = 2^(c G + c |q|^2), SR = S scale (1 + R) in packed fp32x2 arithmetic.
+//                A group of 16 keys whose bounding sphere lies farther than 5.9 sigma_h from the bounding sphere
+//                of the warp's 32 queries has R < 2^-25 for every pair, where S (1 + R) == S in fp32: there
+//                the exponential is skipped (most of the off-diagonal work of the narrow heads).  The two
+//                halves of a row exchange their maxima through shared memory; P is written as bf16 straight
+//                into tensor memory;
 //   O += P V   : tcgen05.mma with the A operand (P) read from tensor memory, B = V tile (MN-major: keys
 //                are the K dimension), accumulated in TMEM [128 x 64] across the key tiles.  The running
 //                maximum is only raised when a tile exceeds it by more than 2^8 (then the accumulator and
@@ -42,14 +47,14 @@ constexpr int GA_MAX_TILES = GA_PLAN_MAX_TILES;
 constexpr int GA_FWD_MATH_THREADS = 256;
 constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 32;  // + the producer warp
 constexpr float GA_RESCALE_THRESHOLD = 8.f;                 // log2 units
-constexpr uint32_t GA_TMEM_COLS = 256;
+constexpr uint32_t GA_TMEM_COLS = 512;
 constexpr uint32_t GA_TILE_BYTES = GA_BN * GA_D * 2;  // 16 KiB
 constexpr int GA_KC_BUFS = 3;                           // key-coordinate buffers (see the tile loop)
 constexpr float GA_FAR_SIGMAS = 5.9f;                   // exp(-d^2 / 2 sigma^2) < 2^-25 beyond 5.887 sigma
 
-struct GaKeyCoords {                  // centred key coordinates of one tile, two keys per entry
-    float4 ka[GA_BN / 2];             // {x_j, x_j+1, y_j, y_j+1}
-    float4 kc[GA_BN / 2];             // {z_j, z_j+1, |k_j|^2, |k_j+1|^2}
+constexpr int GA_GEO_K = 32;                            // bf16 columns of the geometry operands (21 used)
+
+struct GaKeyCoords {                  // per-key side data of one tile
     alignas(16) float kb[GA_BN];      // 0 for a valid key, -inf for a padded one
     float4 sph[GA_BN / 16];           // bounding sphere of each group of 16 keys: centre, radius (< 0: no valid key)
 };
@@ -58,6 +63,8 @@ struct GaFwdSmem {
     alignas(1024) uint8_t q[GA_TILE_BYTES];
     alignas(1024) uint8_t k[2][GA_TILE_BYTES];
     alignas(1024) uint8_t v[2][GA_TILE_BYTES];
+    alignas(1024) uint8_t qg[GA_TILE_BYTES];              // geometry operand of the queries (rows of 128 B, 64 B used)
+    alignas(1024) uint8_t kg[GA_KC_BUFS][GA_TILE_BYTES];  // geometry operand of the keys, one per staged tile
     GaKeyCoords kc[GA_KC_BUFS];
     float xch[2][2][GA_BM];                       // row maxima exchanged between the two halves, by tile parity
     float lsum[2][GA_BM];                         // row sums exchanged at the end
@@ -159,15 +166,50 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     return r;
 }
 
-// Stages the centred coordinates, the mask and the 16-key bounding spheres of one key tile.  Executed by
+// fp32 -> three bf16 terms whose sum reproduces the value to about 2^-24 relative
+__device__ __forceinline__ void ga_split3(float a, uint32_t &h, uint32_t &m, uint32_t &l) {
+    const __nv_bfloat16 bh = __float2bfloat16_rn(a);
+    const float r1 = a - __bfloat162float(bh);
+    const __nv_bfloat16 bm = __float2bfloat16_rn(r1);
+    const __nv_bfloat16 bl = __float2bfloat16_rn(r1 - __bfloat162float(bm));
+    h = (uint32_t)__bfloat16_as_ushort(bh);
+    m = (uint32_t)__bfloat16_as_ushort(bm);
+    l = (uint32_t)__bfloat16_as_ushort(bl);
+}
+
+// One row (GA_GEO_K bf16 values) of a geometry operand tile, in the 128-byte-swizzled K-major layout the tensor core
+// reads.  The product of a LEFT row (a, e) and a RIGHT row (b, n) is  a.b + e n  to fp32 accuracy: every fp32 factor
+// is split into bf16 terms h + m + l and the six products of combined order <= 2 are laid out side by side,
+//     LEFT  per coordinate: a_h a_h a_m a_h a_l a_m        then e_h e_h e_m e_h e_l e_m   (zeros after that)
+//     RIGHT per coordinate: b_h b_m b_h b_l b_h b_m        then n_h n_m n_h n_l n_h n_m
+// (dropped terms are below 2^-24 of |a||b|).  In the forward LEFT = (-2 q, 1), RIGHT = (k, |k|^2): G = |k|^2 - 2 q.k.
+template <bool LEFT>
+__device__ __forceinline__ void ga_write_geo_row(uint8_t *tile, int row, float x, float y, float z, float e) {
+    uint32_t w[16];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t h, m, l;
+        ga_split3(c == 0 ? x : c == 1 ? y : c == 2 ? z : e, h, m, l);
+        if (LEFT) {
+            w[3 * c + 0] = h | (h << 16);
+            w[3 * c + 1] = m | (h << 16);
+            w[3 * c + 2] = l | (m << 16);
+        } else {
+            w[3 * c + 0] = h | (m << 16);
+            w[3 * c + 1] = h | (l << 16);
+            w[3 * c + 2] = h | (m << 16);
+        }
+    }
+    w[12] = w[13] = w[14] = w[15] = 0u;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4 *>(tile + sw128_offset(row, c)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+}
+
+// Stages one key tile: the geometry operand row of the key, the mask and the 16-key bounding spheres.  Executed by
 // the 128 threads of warps 0..3 (thread = key); `x, y, z` are the centred coordinates (0 for a padded key).
-__device__ __forceinline__ void ga_stage_keys(GaKeyCoords &kc, int tid, bool ok, float x, float y, float z) {
-    float *a = reinterpret_cast<float *>(&kc.ka[tid >> 1]);
-    float *c = reinterpret_cast<float *>(&kc.kc[tid >> 1]);
-    a[tid & 1] = x;
-    a[2 + (tid & 1)] = y;
-    c[tid & 1] = z;
-    c[2 + (tid & 1)] = x * x + y * y + z * z;
+__device__ __forceinline__ void ga_stage_keys(GaKeyCoords &kc, uint8_t *kg, int tid, bool ok, float x, float y, float z) {
+    ga_write_geo_row<false>(kg, tid, x, y, z, x * x + y * y + z * z);
     kc.kb[tid] = ok ? 0.f : -INFINITY;
     // bounding sphere of the 16 keys of this half-warp (valid keys only): centre = mean, radius = largest distance
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded keys carry 0
@@ -184,77 +226,54 @@ __device__ __forceinline__ void ga_stage_keys(GaKeyCoords &kc, int tid, bool ok,
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) d2 = fmaxf(d2, __shfl_xor_sync(0xffffffffu, d2, off));
     if ((tid & 15) == 0) kc.sph[tid >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
+    fence_proxy_async();  // the geometry row (generic-proxy stores) must be visible to the tensor core
 }
 
-// 16 logits (8 key pairs) of one row, held in registers: v[] holds raw S on entry and SR on return;
-// returns the running maximum.  SR = (S * c_s) * (1 + R) with R = 2^(c_rbf * d^2), d^2 = |q|^2 + |k|^2 - 2 q.k
-// from the centred coordinates; `far`: the key group is too far for R to count (warp-uniform).
-template <bool MASKED, int FORM, int OFF>
-__device__ __forceinline__ float ga_sr_chunk(uint32_t (&w)[32], bool far, const float4 *ka, const float4 *kc, const float *kb, f2_t qx2,
-                                             f2_t qy2, f2_t qz2, f2_t crbf2, f2_t cqn2, f2_t cs2, const GaForm &fm, float m_loc) {
+// 16 logits (8 key pairs) of one row, held in registers: v[] holds raw S on entry and SR on return, g[] the matching
+// G values; returns the maximum.  SR = (S * c_s) * (1 + R) with R = 2^(c_rbf * (G + |q|^2)).
+// FAR: 0 = the group is near (R evaluated), 1 = far (R does not count), 2 = decided at run time by `far_rt`
+// (warp-uniform).  With 0 or 1 the body has no branch, so the four groups of a row form one straight-line block.
+template <bool MASKED, int FORM, int OFF, int FAR>
+__device__ __forceinline__ float ga_sr_chunk(uint32_t (&w)[32], uint32_t g_taddr, bool far_rt, const float *kb, f2_t crbf2,
+                                             f2_t cqn2, f2_t cs2, const GaForm &fm) {
 #define v(i) w[OFF + (i)]
-    if (far) {
+    const bool far = FAR == 2 ? far_rt : (FAR == 1);
+    float m_loc = -INFINITY;
+    f2_t rb[8];
+    if (!far) {
+        uint32_t gw[16];  // the 16 G values of the group, straight from tensor memory
+        tmem_ld16(g_taddr + OFF, gw);
+        tmem_wait_ld();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            f2_t sr = f2_mul(f2_pack(__uint_as_float(v(2 * e)), __uint_as_float(v(2 * e + 1))), cs2);
-            if (FORM == 1) {
-                if (fm.far_masked) {
-                    sr = f2_pack(-INFINITY, -INFINITY);
-                } else {  // R = 0: inside the window (min_rbf <= 0), Rn = rn_b
-                    float t0, t1;
-                    f2_unpack(sr, t0, t1);
-                    sr = f2_pack(fmaf(fm.beta * fm.rn_b, fabsf(t0), t0), fmaf(fm.beta * fm.rn_b, fabsf(t1), t1));
-                }
+            float a0, a1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(gw[2 * e]), __uint_as_float(gw[2 * e + 1])), crbf2, cqn2), a0, a1);
+            if (FORM == 1) {  // keep R <= 1 exactly (the d^2 of a coincident pair can round below zero)
+                a0 = fminf(a0, 0.f);
+                a1 = fminf(a1, 0.f);
             }
-            float v0, v1;
-            f2_unpack(sr, v0, v1);
-            if (MASKED) {  // select, do not add: a padded key may hold Inf / NaN
-                const float2 b = *reinterpret_cast<const float2 *>(kb + 2 * e);
-                v0 = b.x == 0.f ? v0 : -INFINITY;
-                v1 = b.y == 0.f ? v1 : -INFINITY;
-            }
-            v(2 * e) = __float_as_uint(v0);
-            v(2 * e + 1) = __float_as_uint(v1);
-            m_loc = max3(m_loc, v0, v1);
+            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
         }
-        return m_loc;
-    }
-    f2_t arg[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {  // exponent arguments, independent of S
-        const float4 a = ka[e], k4 = kc[e];
-        f2_t d2 = f2_fma(qz2, f2_pack(k4.x, k4.y), f2_pack(k4.z, k4.w));
-        d2 = f2_fma(qy2, f2_pack(a.z, a.w), d2);
-        d2 = f2_fma(qx2, f2_pack(a.x, a.y), d2);
-        arg[e] = f2_fma(d2, crbf2, cqn2);
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        float a0, a1;
-        f2_unpack(arg[e], a0, a1);
-        if (FORM == 1) {  // keep R <= 1 exactly (the centred d^2 of a coincident pair can round below zero)
-            a0 = fminf(a0, 0.f);
-            a1 = fminf(a1, 0.f);
-        }
-        arg[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         const f2_t t2 = f2_mul(f2_pack(__uint_as_float(v(2 * e)), __uint_as_float(v(2 * e + 1))), cs2);
         f2_t sr;
         if (FORM == 0) {
-            sr = f2_fma(t2, arg[e], t2);
+            sr = far ? t2 : f2_fma(t2, rb[e], t2);
+        } else if (far && fm.far_masked) {
+            sr = f2_pack(-INFINITY, -INFINITY);
         } else {
-            float t0, t1, r0, r1;
+            float t0, t1, r0 = 0.f, r1 = 0.f;  // a far group inside the window (min_rbf <= 0): R counts as 0
             f2_unpack(t2, t0, t1);
-            f2_unpack(arg[e], r0, r1);
+            if (!far) f2_unpack(rb[e], r0, r1);
             const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
             const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
             sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
         }
         float v0, v1;
         f2_unpack(sr, v0, v1);
-        if (MASKED) {
+        if (MASKED) {  // select, do not add: a padded key may hold Inf / NaN
             const float2 b = *reinterpret_cast<const float2 *>(kb + 2 * e);
             v0 = b.x == 0.f ? v0 : -INFINITY;
             v1 = b.y == 0.f ? v1 : -INFINITY;
@@ -267,27 +286,14 @@ __device__ __forceinline__ float ga_sr_chunk(uint32_t (&w)[32], bool far, const 
 #undef v
 }
 
-// The 64 logits of one thread: four groups of 16 keys, each with its own far test.
-template <bool MASKED, int FORM>
-__device__ __forceinline__ float ga_sr_row(uint32_t (&s0)[32], uint32_t (&s1)[32], const GaKeyCoords &kc, int half, float wqx, float wqy,
-                                           float wqz, float wq_reach, f2_t qx2, f2_t qy2, f2_t qz2, f2_t crbf2, f2_t cqn2, f2_t cs2,
-                                           const GaForm &fm) {
-    float m_loc = -INFINITY;
-    auto far_of = [&](int c) -> bool {
-        const float4 sp = kc.sph[half * 4 + c];
-        const float dx = sp.x - wqx, dy = sp.y - wqy, dz = sp.z - wqz;
-        const float reach = wq_reach + sp.w;  // wq_reach = cut + radius of the query sphere (-inf: test off)
-        return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-    };
-#define PAI_GA_CHUNK(ARR, C, OFF)                                                                                               \
-    m_loc = ga_sr_chunk<MASKED, FORM, OFF>(ARR, far_of(C), &kc.ka[half * 32 + (C) * 8], &kc.kc[half * 32 + (C) * 8],             \
-                                           &kc.kb[half * 64 + (C) * 16], qx2, qy2, qz2, crbf2, cqn2, cs2, fm, m_loc)
-    PAI_GA_CHUNK(s0, 0, 0);
-    PAI_GA_CHUNK(s0, 1, 16);
-    PAI_GA_CHUNK(s1, 2, 0);
-    PAI_GA_CHUNK(s1, 3, 16);
-#undef PAI_GA_CHUNK
-    return m_loc;
+// 32 logits of one thread (two groups of 16 keys; H = which 32 of the thread's 64).  MODE 0: every group of the row is
+// near, 1: every group is far, 2: per group (`far`).  Each group keeps its own running maximum.
+template <bool MASKED, int FORM, int MODE, int H>
+__device__ __forceinline__ float ga_sr_half(uint32_t (&sv)[32], uint32_t gv, const GaKeyCoords &kc, int half,
+                                            const bool (&far)[4], f2_t crbf2, f2_t cqn2, f2_t cs2, const GaForm &fm) {
+    const float m0 = ga_sr_chunk<MASKED, FORM, 0, MODE>(sv, gv, far[2 * H], &kc.kb[half * 64 + (2 * H) * 16], crbf2, cqn2, cs2, fm);
+    const float m1 = ga_sr_chunk<MASKED, FORM, 16, MODE>(sv, gv, far[2 * H + 1], &kc.kb[half * 64 + (2 * H + 1) * 16], crbf2, cqn2, cs2, fm);
+    return fmaxf(m0, m1);
 }
 
 __global__ void __launch_bounds__(GA_FWD_THREADS, 1)
@@ -367,21 +373,38 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     volatile int *abort_flag = &sm.abort;
 
     // ---- set-up: first key coordinates --------------------------------------------------------------
-    auto key_coords = [&](int tile, bool &ok, float &x, float &y, float &zc) {  // thread tid < 128: key tile*128 + tid, centred
-        const int j = tile * GA_BN + tid;
-        ok = j < N && (vz ? vz[j] != 0 : true);
-        x = y = zc = 0.f;
-        if (ok) {
-            x = cz[j * 3] - orx;
-            y = cz[j * 3 + 1] - ory;
-            zc = cz[j * 3 + 2] - orz;
-        }
+    // Coordinates of a key: the loads are issued at once from a clamped index (none waits for the validity byte) and
+    // only turned into centred coordinates where they are used, so the thread does not stall on them in between.
+    struct KeyLoad {
+        float gx, gy, gz;
+        uint8_t vb;
+        bool in_range;
     };
+    auto key_load = [&](int tile) -> KeyLoad {  // thread tid < 128: key tile*128 + tid
+        const int j = tile * GA_BN + tid, jc = min(j, N - 1);
+        KeyLoad k;
+        k.vb = vz ? vz[jc] : (uint8_t)1;
+        k.gx = cz[jc * 3];
+        k.gy = cz[jc * 3 + 1];
+        k.gz = cz[jc * 3 + 2];
+        k.in_range = j < N;
+        return k;
+    };
+    auto key_stage = [&](int buf, const KeyLoad &k) {
+        const bool ok = k.in_range && k.vb != 0;
+        ga_stage_keys(sm.kc[buf], sm.kg[buf], tid, ok, ok ? k.gx - orx : 0.f, ok ? k.gy - ory : 0.f, ok ? k.gz - orz : 0.f);
+    };
+    // this thread's query, centred
+    float qcx = 0.f, qcy = 0.f, qcz = 0.f;
+    if (q_ok) {
+        qcx = cz[row * 3] - orx;
+        qcy = cz[row * 3 + 1] - ory;
+        qcz = cz[row * 3 + 2] - orz;
+    }
     if (tid < GA_BN) {
-        bool ok;
-        float x, y, zc;
-        key_coords(tile_word_g(0) & 0x7fff, ok, x, y, zc);
-        ga_stage_keys(sm.kc[0], tid, ok, x, y, zc);
+        key_stage(0, key_load(tile_word_g(0) & 0x7fff));
+        ga_write_geo_row<true>(sm.qg, tid, -2.f * qcx, -2.f * qcy, -2.f * qcz, 1.f);  // (tid < 128: r == tid, half == 0)
+        fence_proxy_async();
     }
     tc_fence_before();
     __syncthreads();  // barriers initialised, TMEM allocated, tile list and first key coordinates in place
@@ -391,6 +414,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem_s = tmem;          // columns [0,128): S
     const uint32_t tmem_o = tmem + 128;    // columns [128,192): O accumulator
     const uint32_t tmem_p = tmem + 192;    // columns [192,256): P as bf16 pairs (A operand of P V)
+    const uint32_t tmem_g = tmem + 256;    // columns [256,384): G = |k|^2 - 2 q.k
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
     if (!is_math) {
@@ -399,20 +423,29 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint32_t q_addr = smem_u32(sm.q);
             constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_BN, false, false);  // Q K^T: both K-major
             constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);    // P V: V is MN-major
-            auto issue_s = [&](int b) {  // 4 MMAs of K = 16 over d = 64: advance 32 B inside the swizzled row
-                const uint32_t k_addr = smem_u32(sm.k[b]);
+            // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
+            const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024);
+            const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
+            const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
+            const uint64_t qg_desc = umma_desc_sw128(smem_u32(sm.qg), 16, 1024);
+            const uint64_t kg_desc[GA_KC_BUFS] = {umma_desc_sw128(smem_u32(sm.kg[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.kg[1]), 16, 1024),
+                                                  umma_desc_sw128(smem_u32(sm.kg[2]), 16, 1024)};
+            // S(t) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(t): 2 more over the
+            // geometry operands of the staged key tile t
+            auto issue_s = [&](int b, int t) {
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tmem_s, umma_desc_sw128(q_addr + kk * 32, 16, 1024), umma_desc_sw128(k_addr + kk * 32, 16, 1024),
-                            IDESC_S, kk > 0 ? 1u : 0u);
+                    umma_ss(tmem_s, q_desc + (uint64_t)(kk * 2), k_desc[b] + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
+                const uint64_t kg = kg_desc[t % GA_KC_BUFS];
+#pragma unroll
+                for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
+                    umma_ss(tmem_g, qg_desc + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_s);
             };
             auto issue_pv = [&](int b, bool first) {  // 8 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
-                const uint32_t v_addr = smem_u32(sm.v[b]);
 #pragma unroll
                 for (int kk = 0; kk < GA_BN / 16; ++kk)
-                    umma_ts(tmem_o, tmem_p + kk * 8, umma_desc_sw128(v_addr + kk * 2048, 0, 1024), IDESC_O,
-                            (first && kk == 0) ? 0u : 1u);
+                    umma_ts(tmem_o, tmem_p + kk * 8, v_desc[b] + (uint64_t)(kk * 128), IDESC_O, (first && kk == 0) ? 0u : 1u);
                 umma_commit(&sm.bar_o);
             };
             auto load_k = [&](int t) {
@@ -425,10 +458,11 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 mbar_expect_tx(&sm.bar_v[b], GA_TILE_BYTES);
                 tma_load_4d(sm.v[b], &map_v, 0, (tile_word(t) & 0x7fff) * GA_BN, h, z, &sm.bar_v[b]);
             };
-            bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag) && mbar_wait_abortable(&sm.bar_k[0], 0, abort_flag);
+            bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag) && mbar_wait_abortable(&sm.bar_k[0], 0, abort_flag) &&
+                      mbar_wait_abortable(&sm.bar_kc[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_s(0);
+                issue_s(0, 0);
             }
             for (int t = 0; ok && t < nt; ++t) {
                 const uint32_t par = (uint32_t)(t & 1);
@@ -438,8 +472,9 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (!(ok = mbar_wait_abortable(&sm.bar_sfree, par, abort_flag))) break;
                     if (t + 2 < nt) load_k(t + 2);
                     if (!(ok = mbar_wait_abortable(&sm.bar_k[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
+                    if (!(ok = mbar_wait_abortable(&sm.bar_kc[(t + 1) % GA_KC_BUFS], (uint32_t)(((t + 1) / GA_KC_BUFS) & 1), abort_flag))) break;
                     tc_fence_after();
-                    issue_s(b ^ 1);  // S(t+1) runs underneath the softmax of tile t
+                    issue_s(b ^ 1, t + 1);  // S, G(t+1) run underneath the softmax of tile t
                 }
                 if (!(ok = mbar_wait_abortable(&sm.bar_p, par, abort_flag))) break;  // P(t) in TMEM, O rescaled if need be
                 if (!(ok = mbar_wait_abortable(&sm.bar_v[b], (uint32_t)((t >> 1) & 1), abort_flag))) break;
@@ -466,14 +501,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float sig = p.sigma[h];
         const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);  // R = 2^(c_rbf * d^2)
         const float c_s = p.scale * 1.4426950408889634f;               // logits in base-2 units
-        float qcx = 0.f, qcy = 0.f, qcz = 0.f;
-        if (q_ok) {
-            qcx = cz[row * 3] - orx;
-            qcy = cz[row * 3 + 1] - ory;
-            qcz = cz[row * 3 + 2] - orz;
-        }
-        // d^2 = |q|^2 + |k|^2 - 2 q.k  ->  c_rbf * d^2 = fma(|k|^2 + (-2q).k, c_rbf, c_rbf |q|^2)
-        const f2_t qx2 = f2_pack(-2.f * qcx, -2.f * qcx), qy2 = f2_pack(-2.f * qcy, -2.f * qcy), qz2 = f2_pack(-2.f * qcz, -2.f * qcz);
+        // R = 2^(c_rbf d^2) with d^2 = G + |q|^2
         const float cqn = c_rbf * (qcx * qcx + qcy * qcy + qcz * qcz);
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cqn2 = f2_pack(cqn, cqn), cs2 = f2_pack(c_s, c_s);
         GaForm fm;
@@ -513,35 +541,58 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const bool has_hole = (tile_word(t) & 0x8000) != 0;
             uint32_t s0[32], s1[32];
             float m_loc = -INFINITY;
-            if (ok) ok = wait_w(&sm.bar_s, par);  // S(t) has landed in TMEM
+            // key coordinates of the next tile: issue the global loads now, stage them after the first pass
+            const bool stage_next = t + 1 < nt && tid < GA_BN;
+            KeyLoad nk = {0.f, 0.f, 0.f, 0, false};
+            if (stage_next) nk = key_load(tile_word(t + 1) & 0x7fff);
+            if (ok) ok = wait_w(&sm.bar_s, par);  // S(t), G(t) have landed in TMEM
+            if (ok) ok = wait_w(&sm.bar_kc[cb], (uint32_t)((t / GA_KC_BUFS) & 1));  // (long complete: the producer waited for it)
             if (ok) {
                 tc_fence_after();
+                const GaKeyCoords &kc = sm.kc[cb];
+                bool far[4];
+                int nfar = 0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {  // far test of the four key groups against this warp's queries (warp-uniform)
+                    const float4 sp = kc.sph[half * 4 + c];
+                    const float dx = sp.x - wqx, dy = sp.y - wqy, dz = sp.z - wqz;
+                    const float reach = wq_reach + sp.w;  // wq_reach = cut + radius of the query sphere (-inf: test off)
+                    far[c] = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+                    nfar += far[c] ? 1 : 0;
+                }
+                // two halves of 32 logits: S of the half into registers, G group by group, SR in place (it stays for the P phase)
+                uint32_t gv = tmem_g + lane_base + half * 64;
+                float m_a, m_b;
+#define PAI_GA_HALF(H, SV, MASKED, FORM, MODE) ga_sr_half<MASKED, FORM, MODE, H>(SV, gv, kc, half, far, crbf2, cqn2, cs2, fm)
+#define PAI_GA_DISPATCH(H, SV, OUT)                                                                             \
+    if (p.form == 0) {                                                                                          \
+        if (nfar == 0) {                                                                                        \
+            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 0); else OUT = PAI_GA_HALF(H, SV, false, 0, 0);     \
+        } else if (nfar == 4) {                                                                                 \
+            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 1); else OUT = PAI_GA_HALF(H, SV, false, 0, 1);     \
+        } else {                                                                                                \
+            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 2); else OUT = PAI_GA_HALF(H, SV, false, 0, 2);     \
+        }                                                                                                       \
+    } else {                                                                                                    \
+        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 1, 2); else OUT = PAI_GA_HALF(H, SV, false, 1, 2);         \
+    }
                 tmem_ld32(tmem_s + lane_base + half * 64, s0);
-                tmem_ld32(tmem_s + lane_base + half * 64 + 32, s1);
-                // key coordinates of the next tile: issue the global loads now, stage them after the first pass
-                float nx = 0.f, ny = 0.f, nz = 0.f;
-                bool nok = false;
-                const bool stage_next = t + 1 < nt && tid < GA_BN;
-                if (stage_next) key_coords(tile_word(t + 1) & 0x7fff, nok, nx, ny, nz);
                 tmem_wait_ld();
+                PAI_GA_DISPATCH(0, s0, m_a)
+                gv += 32;
+                tmem_ld32(tmem_s + lane_base + half * 64 + 32, s1);
+                tmem_wait_ld();
+                PAI_GA_DISPATCH(1, s1, m_b)
                 tc_fence_before();
-                mbar_arrive(&sm.bar_sfree);  // the tensor core may overwrite S with the next tile's
-                ok = wait_w(&sm.bar_kc[cb], (uint32_t)((t / GA_KC_BUFS) & 1));
-                if (ok) {
-                    const GaKeyCoords &kc = sm.kc[cb];
-                    if (p.form == 0) {
-                        m_loc = has_hole ? ga_sr_row<true, 0>(s0, s1, kc, half, wqx, wqy, wqz, wq_reach, qx2, qy2, qz2, crbf2, cqn2, cs2, fm)
-                                         : ga_sr_row<false, 0>(s0, s1, kc, half, wqx, wqy, wqz, wq_reach, qx2, qy2, qz2, crbf2, cqn2, cs2, fm);
-                    } else {
-                        m_loc = has_hole ? ga_sr_row<true, 1>(s0, s1, kc, half, wqx, wqy, wqz, wq_reach, qx2, qy2, qz2, crbf2, cqn2, cs2, fm)
-                                         : ga_sr_row<false, 1>(s0, s1, kc, half, wqx, wqy, wqz, wq_reach, qx2, qy2, qz2, crbf2, cqn2, cs2, fm);
-                    }
-                    // Buffer (t+1) % 3 was last read during tile t-2, which every thread has left: S(t) was only issued
-                    // after all of them had read S(t-1), that is after they had finished tile t-2.
-                    if (stage_next) {
-                        ga_stage_keys(sm.kc[(t + 1) % GA_KC_BUFS], tid, nok, nx, ny, nz);
-                        mbar_arrive(&sm.bar_kc[(t + 1) % GA_KC_BUFS]);
-                    }
+                mbar_arrive(&sm.bar_sfree);  // S and G are in registers: the tensor core may overwrite them with the next tile's
+#undef PAI_GA_DISPATCH
+#undef PAI_GA_HALF
+                m_loc = fmaxf(m_a, m_b);
+                // Buffer (t+1) % 3 was last read during tile t-2 (by these threads and by the G MMA of that tile), which every
+                // thread has left: S(t) was only issued after all of them had read S(t-1), that is after they had finished tile t-2.
+                if (stage_next) {
+                    key_stage((t + 1) % GA_KC_BUFS, nk);
+                    mbar_arrive(&sm.bar_kc[(t + 1) % GA_KC_BUFS]);
                 }
             }
             sm.xch[par][half][r] = m_loc;
@@ -561,7 +612,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // P = 2^(SR - m), row sum, bf16 pairs
             const float m_safe = m_run == -INFINITY ? 0.f : m_run;  // a row without any valid pair so far: P = 2^(-inf) = 0
             const f2_t mn2 = f2_pack(m_safe, m_safe);
-            f2_t l2 = 0ull;
+            f2_t l2 = 0ull, l2b = 0ull;
             uint32_t pw[32];
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
@@ -570,11 +621,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                                         : f2_pack(__uint_as_float(s1[2 * e - 32]), __uint_as_float(s1[2 * e - 31]));
                 f2_unpack(f2_sub(sr2, mn2), a0, a1);
                 const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
-                l2 = f2_add(l2, f2_pack(p0, p1));
+                if (e & 1) l2b = f2_add(l2b, f2_pack(p0, p1));
+                else l2 = f2_add(l2, f2_pack(p0, p1));
                 pw[e] = pack_bf16x2(p0, p1);
             }
             float l0, l1;
-            f2_unpack(l2, l0, l1);
+            f2_unpack(f2_add(l2, l2b), l0, l1);
             l_run = l_run * alpha + (l0 + l1);
             if (t > 0) {  // P V(t-1) has completed: the P columns are free and the O accumulator is at rest
                 if (!(ok = wait_w(&sm.bar_o, par ^ 1))) continue;
