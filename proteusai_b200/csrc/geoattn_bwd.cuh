@@ -36,12 +36,11 @@ namespace pai {
 
 constexpr uint32_t GA_BWD_TMEM_COLS = 512;
 constexpr int GA_BWD_MATH_THREADS = 256;
-constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 32;  // + the producer warp
+constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 64;  // + the producer warp and the stager warp
 constexpr int GA_ROW_BUFS = 3;
+constexpr int GA_SUB = 64;  // queries per sub-tile (two sub-tiles per 128-row query tile)
 
 struct GaQueryRows {                  // per-query inputs of one query tile, two queries per entry
-    float4 qa[GA_BM / 2];             // {x_i, x_i+1, y_i, y_i+1}   centred on the key tile's first valid key
-    float4 qc[GA_BM / 2];             // {z_i, z_i+1, |q_i|^2, |q_i+1|^2}
     float2 l2[GA_BM / 2];             // log-sum-exp in base-2 units (+inf: padded query or row without a valid pair)
     float2 dsum[GA_BM / 2];           // D_i
     alignas(16) float qb[GA_BM];      // 0 for a valid query, -inf for a padded one
@@ -54,9 +53,11 @@ struct GaBwdSmem {
     alignas(1024) uint8_t q[2][GA_TILE_BYTES];
     alignas(1024) uint8_t dout[2][GA_TILE_BYTES];
     alignas(1024) uint8_t ds[2][2 * GA_TILE_BYTES];  // dS^T [128 keys x 128 queries] bf16: two [128 x 64] swizzled sub-tiles
+    // Geometry operands (see ga_write_geo_row): slot 0 = the keys (-2 k, 1), slots 1..3 = the ring of staged query tiles (q, |q|^2)
+    alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaQueryRows rows[GA_ROW_BUFS];
     uint16_t tiles[GA_MAX_TILES];          // live query tiles of the range; bit 15: the tile also holds a padded query
-    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_spfree, bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS];
+    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_spfree, bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS], bar_rowsfree[GA_ROW_BUFS];
     uint32_t tmem_base;
     int abort;
     float dsig[GA_BWD_MATH_THREADS / 32];
@@ -108,22 +109,19 @@ __device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-struct GaBwdKey {  // per-thread constants of the thread's key, packed for fp32x2 arithmetic
-    f2_t kx2, ky2, kz2, ckn2;  // -2 k (centred), c_rbf |k|^2
+struct GaBwdKey {  // per-thread constants of the thread's key
+    f2_t ckn2;  // c_rbf |k|^2 (centred)
     bool k_ok;
 };
 
-// Stages the per-query inputs of one query tile.  Executed by the 128 threads of warps 0..3 (thread = query).
-__device__ __forceinline__ void ga_stage_rows(GaQueryRows &rw, int tid, bool ok, float x, float y, float z, float l2, float dsum) {
-    float *a = reinterpret_cast<float *>(&rw.qa[tid >> 1]);
-    float *c = reinterpret_cast<float *>(&rw.qc[tid >> 1]);
-    a[tid & 1] = x;
-    a[2 + (tid & 1)] = y;
-    c[tid & 1] = z;
-    c[2 + (tid & 1)] = x * x + y * y + z * z;
-    reinterpret_cast<float *>(&rw.l2[tid >> 1])[tid & 1] = l2;
-    reinterpret_cast<float *>(&rw.dsum[tid >> 1])[tid & 1] = dsum;
-    rw.qb[tid] = ok ? 0.f : -INFINITY;
+// Stages one query of a query tile: its geometry operand row (q, |q|^2), log-sum-exp, D, validity and, with the other 15
+// queries of its half-warp, the bounding sphere of the group of 16.  Executed by whole warps with query = lane + 32 m.
+__device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile, int geo_block, int i, bool ok, float x, float y, float z,
+                                             float l2, float dsum) {
+    ga_write_geo_row<false>(geo_tile, geo_block, i, x, y, z, x * x + y * y + z * z);
+    reinterpret_cast<float *>(&rw.l2[i >> 1])[i & 1] = l2;
+    reinterpret_cast<float *>(&rw.dsum[i >> 1])[i & 1] = dsum;
+    rw.qb[i] = ok ? 0.f : -INFINITY;
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded queries carry 0
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) {
@@ -137,12 +135,13 @@ __device__ __forceinline__ void ga_stage_rows(GaQueryRows &rw, int tid, bool ok,
     float d2 = ok ? (x - cx) * (x - cx) + (y - cy) * (y - cy) + (z - cz) * (z - cz) : 0.f;
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) d2 = fmaxf(d2, __shfl_xor_sync(0xffffffffu, d2, off));
-    if ((tid & 15) == 0) rw.sph[tid >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
+    if ((i & 15) == 0) rw.sph[i >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
 }
 
 // 16 query columns (8 pairs) of one key row: recompute P, form dS and the spread-gradient term.  sv / dpv hold the
-// raw S^T and dP^T values of the thread's 32 columns of this pass, of which this call takes OFF .. OFF + 15; the
-// results come back as bf16 pairs in pw / dw [POFF .. POFF + 7].  `p0` is the index of the first of the 8 query
+// raw S^T and dP^T values of the thread's 32 columns of this sub-tile, of which this call takes OFF .. OFF + 15; the
+// matching 16 values of G^T = |q|^2 - 2 k.q are read from tensor memory at g_taddr + OFF (|r_k - r_q|^2 = G^T + |k|^2);
+// the results come back as bf16 pairs in pw / dw [POFF .. POFF + 7].  `p0` is the index of the first of the 8 query
 // pairs inside the tile's row arrays.
 // MASKED: the key tile or the query tile holds a padded token (validity is then applied by selection, so whatever
 // the padding holds, Inf or NaN included, never reaches a result).  `far` (warp-uniform): the 16 queries are too far
@@ -150,7 +149,8 @@ __device__ __forceinline__ void ga_stage_rows(GaQueryRows &rw, int tid, bool ok,
 // FAR: 0 = near (R evaluated), 1 = far, 2 = decided at run time by `far_rt`; with 0 or 1 the body is branch-free, so the two
 // groups of a pass form one straight-line block.
 template <bool MASKED, int FORM, int OFF, int FAR>
-__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], bool far_rt, const GaQueryRows &rw, int p0,
+__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], uint32_t g_taddr, bool far_rt,
+                                             const GaQueryRows &rw, int p0,
                                              const GaBwdKey &key, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
                                              f2_t &dbeta2, uint32_t (&pw)[16], uint32_t (&dw)[16]) {
     constexpr int POFF = OFF / 2;
@@ -165,14 +165,12 @@ __device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uin
 #pragma unroll
     for (int e = 0; e < 8; ++e) arg[e] = rb[e] = 0ull;
     if (!far) {
+        uint32_t gw[16];
+        tmem_ld16(g_taddr + OFF, gw);
+        tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const float4 a = rw.qa[p0 + e], q4 = rw.qc[p0 + e];
-            f2_t d2 = f2_fma(key.kz2, f2_pack(q4.x, q4.y), f2_pack(q4.z, q4.w));
-            d2 = f2_fma(key.ky2, f2_pack(a.z, a.w), d2);
-            d2 = f2_fma(key.kx2, f2_pack(a.x, a.y), d2);
-            arg[e] = f2_fma(d2, crbf2, key.ckn2);  // c_rbf * d^2
-        }
+        for (int e = 0; e < 8; ++e)  // c_rbf * d^2
+            arg[e] = f2_fma(f2_pack(__uint_as_float(gw[2 * e]), __uint_as_float(gw[2 * e + 1])), crbf2, key.ckn2);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             float a0, a1;
@@ -276,7 +274,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     GaBwdSmem &sm = *reinterpret_cast<GaBwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
-    const int half = (warp >> 2) & 1;             // which 64 query columns / which 32 output columns
+    const bool is_producer = warp == GA_BWD_MATH_THREADS / 32, is_stager = warp == GA_BWD_MATH_THREADS / 32 + 1;
+    const int half = (warp >> 2) & 1;             // which 32 query columns of a sub-tile / which 32 output columns
     const int r = (warp & 3) * 32 + lane;         // key row inside the tile = TMEM lane
     const int N = p.N;
     const int tiles_all = (N + GA_BM - 1) / GA_BM;
@@ -315,14 +314,16 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         return;
     }
     for (int t = tid; t < nt; t += GA_BWD_THREADS) sm.tiles[t] = (uint16_t)word_g(first + t);
+    auto tile_word = [&](int t) -> int { return (int)sm.tiles[t]; };  // (published by the barrier below)
     const bool key_hole = (k_info & 0x8000) != 0;
     // origin of the centred coordinates: the first valid key of this tile
     const int ok_row = j0 + (k_info & 0x7f);
     const float orx = cz[ok_row * 3], ory = cz[ok_row * 3 + 1], orz = cz[ok_row * 3 + 2];
     volatile int *abort_flag = &sm.abort;
+    const int nsub = 2 * nt;  // sub-tiles of 64 queries: u = 2 t + s
 
     // ---- set-up ------------------------------------------------------------------------------------
-    if (!is_math) {
+    if (is_producer) {
         if (lane == 0) {
             mbar_init(&sm.bar_kv, 1);
             mbar_init(&sm.bar_qdo[0], 1);
@@ -334,7 +335,10 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&sm.bar_pds, GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_dqr, GA_BWD_MATH_THREADS);
 #pragma unroll
-            for (int b = 0; b < GA_ROW_BUFS; ++b) mbar_init(&sm.bar_rows[b], GA_BM);
+            for (int b = 0; b < GA_ROW_BUFS; ++b) {
+                mbar_init(&sm.bar_rows[b], 32);
+                mbar_init(&sm.bar_rowsfree[b], GA_BWD_MATH_THREADS);
+            }
             mbar_fence_init();
             fence_proxy_async();
             // the first loads leave before anything else is set up
@@ -353,55 +357,80 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
         tmem_relinquish();
     }
-    // per-query inputs of a tile: thread tid < 128 loads query tile*128 + tid
-    auto row_inputs = [&](int tile, bool &ok, float &x, float &y, float &zc, float &l2, float &dsum) {
-        // (all loads issued at once from a clamped index: none waits for the validity byte)
-        const int i = tile * GA_BM + tid, ic = min(i, N - 1);
-        const uint8_t vb = vz ? vz[ic] : (uint8_t)1;
-        const float gx = cz[ic * 3], gy = cz[ic * 3 + 1], gz = cz[ic * 3 + 2];
-        const float lse = p.lse[(size_t)zh * N + ic];
-        const float dsv = p.dsum[(size_t)zh_local * N + ic];
-        ok = i < N && vb != 0;
-        x = ok ? gx - orx : 0.f;
-        y = ok ? gy - ory : 0.f;
-        zc = ok ? gz - orz : 0.f;
-        // +inf: P = 0 for a padded query and for a row without any valid pair
-        l2 = (ok && lse != -INFINITY) ? lse * 1.4426950408889634f : INFINITY;
-        dsum = ok ? dsv : 0.f;
+    // Per-query inputs of four queries per stager lane (queries lane + 32 m of a tile): the loads are issued at once
+    // from clamped indices, none waits for the validity bytes.
+    struct RowLoad {
+        float gx[4], gy[4], gz[4], lse[4], ds[4];
+        uint8_t vb[4];
     };
-    if (tid < GA_BM) {
-        bool ok;
-        float x, y, zc, l2, dsum;
-        row_inputs(word_g(first) & 0x7fff, ok, x, y, zc, l2, dsum);
-        ga_stage_rows(sm.rows[0], tid, ok, x, y, zc, l2, dsum);
+    auto row_load = [&](int tile, RowLoad &q) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int ic = min(tile * GA_BM + lane + 32 * m, N - 1);
+            q.vb[m] = vz ? vz[ic] : (uint8_t)1;
+            q.gx[m] = cz[ic * 3];
+            q.gy[m] = cz[ic * 3 + 1];
+            q.gz[m] = cz[ic * 3 + 2];
+            q.lse[m] = p.lse[(size_t)zh * N + ic];
+            q.ds[m] = p.dsum[(size_t)zh_local * N + ic];
+        }
+    };
+    auto row_stage = [&](int tile, int buf, const RowLoad &q) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int i = tile * GA_BM + lane + 32 * m;
+            const bool ok = i < N && q.vb[m] != 0;
+            // +inf: P = 0 for a padded query and for a row without any valid pair
+            const float l2 = (ok && q.lse[m] != -INFINITY) ? q.lse[m] * 1.4426950408889634f : INFINITY;
+            ga_stage_row(sm.rows[buf], ga_geo_tile(sm, 1 + buf), ga_geo_block(1 + buf), lane + 32 * m, ok, ok ? q.gx[m] - orx : 0.f,
+                         ok ? q.gy[m] - ory : 0.f, ok ? q.gz[m] - orz : 0.f, l2, ok ? q.ds[m] : 0.f);
+        }
+        fence_proxy_async();  // the geometry rows (generic-proxy stores) must be visible to the tensor core
+    };
+    // this thread's key, centred; the keys' geometry operand: (-2 k, 1)
+    float kcx = 0.f, kcy = 0.f, kcz = 0.f;
+    if (k_ok) {
+        kcx = cz[jrow * 3] - orx;
+        kcy = cz[jrow * 3 + 1] - ory;
+        kcz = cz[jrow * 3 + 2] - orz;
     }
+    if (tid < GA_BN) {  // (tid < 128: r == tid, half == 0)
+        ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), tid, -2.f * kcx, -2.f * kcy, -2.f * kcz, 1.f);
+        fence_proxy_async();
+    }
+    RowLoad rl;
+    if (is_stager) row_load(word_g(first) & 0x7fff, rl);  // in flight across the barrier
     tc_fence_before();
-    __syncthreads();  // barriers initialised, TMEM allocated, tile list and the first tile's row inputs in place
+    __syncthreads();  // barriers initialised, TMEM allocated, tile list and the keys' geometry operand in place
     tc_fence_after();
-    if (tid < GA_BM) mbar_arrive(&sm.bar_rows[0]);
-    auto tile_word = [&](int t) -> int { return (int)sm.tiles[t]; };
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_p = tmem + 256, tm_dv = tmem + 320, tm_dk = tmem + 384, tm_dq = tmem + 448;
+    // S^T [0,64), dP^T [64,128), G^T two buffers [128,192) [192,256), P^T [256,288), dV [320,384), dK [384,448), dQ [448,512)
+    const uint32_t tm_s = tmem, tm_dp = tmem + 64, tm_g = tmem + 128, tm_p = tmem + 256, tm_dv = tmem + 320, tm_dk = tmem + 384,
+                   tm_dq = tmem + 448;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-    if (!is_math) {
+    if (is_stager) {
+        // ================================ stager warp ================================================
+        // Runs up to GA_ROW_BUFS query tiles ahead of the math warps.
+        for (int t = 0; t < nt; ++t) {
+            const int b = t % GA_ROW_BUFS;
+            if (t > 0) row_load(tile_word(t) & 0x7fff, rl);
+            // buffer b was last used by tile t - GA_ROW_BUFS: every math thread has left it (and its G MMAs have completed)
+            if (t >= GA_ROW_BUFS && !mbar_wait_abortable(&sm.bar_rowsfree[b], (uint32_t)((t / GA_ROW_BUFS - 1) & 1), abort_flag)) break;
+            row_stage(tile_word(t) & 0x7fff, b, rl);
+            mbar_arrive(&sm.bar_rows[b]);
+        }
+    } else if (is_producer) {
         // ================================ producer warp ==============================================
         if (lane == 0) {
             const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
-            constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, 128, false, false);
-            constexpr uint32_t IDESC_KN = umma_idesc_bf16(128, GA_D, false, true);  // dV (A in TMEM), dK: A K-major, B MN-major
-            constexpr uint32_t IDESC_NN = umma_idesc_bf16(128, GA_D, true, true);   // dQ: A MN-major, B MN-major
-            auto load_qdo = [&](int t) {
-                const int b = t & 1;
-                const int i0 = (tile_word(t) & 0x7fff) * GA_BM;
-                mbar_expect_tx(&sm.bar_qdo[b], 2 * GA_TILE_BYTES);
-                tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
-                tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
-            };
+            constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, GA_SUB, false, false);  // S^T, dP^T, G^T of a sub-tile: [128 x 64]
+            constexpr uint32_t IDESC_KN = umma_idesc_bf16(128, GA_D, false, true);     // dV (A in TMEM), dK: A K-major, B MN-major
+            constexpr uint32_t IDESC_NN = umma_idesc_bf16(128, GA_D, true, true);      // dQ: A MN-major, B MN-major
             // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
             const uint64_t k_km = umma_desc_sw128(k_addr, 16, 1024), v_km = umma_desc_sw128(v_addr, 16, 1024);  // K-major operands
             const uint64_t k_mn = umma_desc_sw128(k_addr, 0, 1024);                                              // B of dQ
-            uint64_t q_km[2], do_km[2], q_mn[2], do_mn[2], ds_km[2], ds_mn[2];
+            uint64_t q_km[2], do_km[2], q_mn[2], do_mn[2], ds_km[2], ds_mn[2], geo_desc[2];
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
                 q_km[b] = umma_desc_sw128(smem_u32(sm.q[b]), 16, 1024);
@@ -410,24 +439,41 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 do_mn[b] = umma_desc_sw128(smem_u32(sm.dout[b]), 0, 1024);
                 ds_km[b] = umma_desc_sw128(smem_u32(sm.ds[b]), 16, 1024);
                 ds_mn[b] = umma_desc_sw128(smem_u32(sm.ds[b]), GA_TILE_BYTES, 1024);
+                geo_desc[b] = umma_desc_sw128(smem_u32(sm.geo[b]), 16, 1024);
             }
-            auto issue_s_dp = [&](int b) {  // S^T = K Q^T, dP^T = V dO^T: 4 + 4 MMAs of K = 16 over d = 64 (32 B per step)
+            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
+            constexpr uint64_t SUB_ROWS = (uint64_t)(GA_SUB * 128) >> 4;  // 64 rows of a swizzled tile, in 16-byte units
+            auto load_qdo = [&](int t) {
+                const int b = t & 1;
+                const int i0 = (tile_word(t) & 0x7fff) * GA_BM;
+                mbar_expect_tx(&sm.bar_qdo[b], 2 * GA_TILE_BYTES);
+                tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
+                tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
+            };
+            // Sub-tile u = 2 t + s (queries 64 s .. 64 s + 63 of tile t): S^T = K Q^T and dP^T = V dO^T, 4 + 4 MMAs of K = 16
+            // over d = 64; G^T over the geometry operands, 2 MMAs.  B operands start 64 rows into their tiles for s = 1.
+            auto issue_sdg = [&](int u) {
+                const int t = u >> 1, sub = u & 1, b = t & 1;
+                const uint64_t qd = q_km[b] + sub * SUB_ROWS, dd = do_km[b] + sub * SUB_ROWS;
 #pragma unroll
-                for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_s, k_km + (uint64_t)(kk * 2), q_km[b] + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_s, k_km + (uint64_t)(kk * 2), qd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), do_km[b] + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), dd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                const uint64_t kg = geo_slot_desc(0), qg = geo_slot_desc(1 + t % GA_ROW_BUFS) + sub * SUB_ROWS;
+#pragma unroll
+                for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
+                    umma_ss(tm_g + (u & 1) * GA_SUB, kg + (uint64_t)(kk * 2), qg + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_sp);
             };
-            auto issue_dv_dk = [&](int b, bool first_tile) {  // K = 16 queries per step
+            auto issue_dv_dk = [&](int u) {  // K = 16 queries per step, 4 steps per sub-tile
+                const int t = u >> 1, sub = u & 1, b = t & 1;
 #pragma unroll
-                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
-                    umma_ts(tm_dv, tm_p + kk * 8, do_mn[b] + (uint64_t)(kk * 128), IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
+                for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
+                    umma_ts(tm_dv, tm_p + kk * 8, do_mn[b] + sub * SUB_ROWS + (uint64_t)(kk * 128), IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
 #pragma unroll
-                for (int kk = 0; kk < GA_BM / 16; ++kk)  // dK += dS^T Q: dS^T advances 32 B inside the swizzled row, second sub-tile after 64
-                    umma_ss(tm_dk, ds_km[b] + (uint64_t)((kk >> 2) * (GA_TILE_BYTES >> 4) + (kk & 3) * 2), q_mn[b] + (uint64_t)(kk * 128),
-                            IDESC_KN, (first_tile && kk == 0) ? 0u : 1u);
+                for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dK += dS^T Q: the sub-tile of dS^T, 32 B per step inside the swizzled row
+                    umma_ss(tm_dk, ds_km[b] + (uint64_t)(sub * (GA_TILE_BYTES >> 4) + kk * 2), q_mn[b] + sub * SUB_ROWS + (uint64_t)(kk * 128),
+                            IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
                 umma_commit(&sm.bar_vk);
             };
             auto issue_dq = [&](int b) {  // dQ = dS K: K = 16 keys per step, 2 KiB down the dS^T tile (M = queries: two sub-tiles)
@@ -436,29 +482,35 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     umma_ss(tm_dq, ds_mn[b] + (uint64_t)(kk * 128), k_mn + (uint64_t)(kk * 128), IDESC_NN, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_dq);
             };
-            bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag);
+            bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag) &&
+                      mbar_wait_abortable(&sm.bar_rows[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_s_dp(0);
+                issue_sdg(0);
             }
-            for (int t = 0; ok && t < nt; ++t) {
-                const int b = t & 1;
-                const uint32_t par = (uint32_t)(t & 1);
-                if (t + 1 < nt) {  // every math thread holds its S^T, dP^T(t) in registers: compute the next tile's
+            for (int u = 0; ok && u < nsub; ++u) {
+                const int t = u >> 1, sub = u & 1, b = t & 1;
+                const uint32_t par = (uint32_t)(u & 1);
+                if (u + 1 < nsub) {  // every math thread holds its S^T, dP^T(u) in registers: compute the next sub-tile's
                     if (!(ok = mbar_wait_abortable(&sm.bar_spfree, par, abort_flag))) break;
-                    if (!(ok = mbar_wait_abortable(&sm.bar_qdo[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
+                    if (sub == 1) {  // the next sub-tile opens query tile t + 1
+                        if (!(ok = mbar_wait_abortable(&sm.bar_qdo[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
+                        if (!(ok = mbar_wait_abortable(&sm.bar_rows[(t + 1) % GA_ROW_BUFS], (uint32_t)(((t + 1) / GA_ROW_BUFS) & 1), abort_flag))) break;
+                    }
                     tc_fence_after();
-                    issue_s_dp(b ^ 1);
+                    issue_sdg(u + 1);  // (its G^T buffer was last read for sub-tile u - 1, which has handed over P^T and dS^T)
                 }
-                if (!(ok = mbar_wait_abortable(&sm.bar_pds, par, abort_flag))) break;  // P^T(t) in TMEM, dS^T(t) in shared memory
+                if (!(ok = mbar_wait_abortable(&sm.bar_pds, par, abort_flag))) break;  // P^T(u) in TMEM, dS^T(u) in shared memory
                 tc_fence_after();
-                issue_dv_dk(b, t == 0);
-                if (t > 0 && !(ok = mbar_wait_abortable(&sm.bar_dqr, par ^ 1, abort_flag))) break;  // dQ(t-1) read out of TMEM
-                tc_fence_after();
-                issue_dq(b);
-                if (t + 2 < nt) {  // Q / dO buffer b is free once S^T, dP^T(t) and dV, dK(t) are done
-                    if (!(ok = mbar_wait_abortable(&sm.bar_vk, par, abort_flag))) break;
-                    load_qdo(t + 2);
+                issue_dv_dk(u);
+                if (sub == 1) {
+                    if (t > 0 && !(ok = mbar_wait_abortable(&sm.bar_dqr, (uint32_t)((t - 1) & 1), abort_flag))) break;  // dQ(t-1) read out
+                    tc_fence_after();
+                    issue_dq(b);
+                    if (t + 2 < nt) {  // Q / dO buffer b is free once the sub-tile MMAs of tile t are done
+                        if (!(ok = mbar_wait_abortable(&sm.bar_vk, par, abort_flag))) break;
+                        load_qdo(t + 2);
+                    }
                 }
             }
             if (!ok) {  // gave up: let the copies already issued land before the CTA exits (bounded)
@@ -478,15 +530,6 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         GaForm fm;
         ga_form_setup(fm, p.form, p.form == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
         GaBwdKey key;
-        float kcx = 0.f, kcy = 0.f, kcz = 0.f;
-        if (k_ok) {
-            kcx = cz[jrow * 3] - orx;
-            kcy = cz[jrow * 3 + 1] - ory;
-            kcz = cz[jrow * 3 + 2] - orz;
-        }
-        key.kx2 = f2_pack(-2.f * kcx, -2.f * kcx);
-        key.ky2 = f2_pack(-2.f * kcy, -2.f * kcy);
-        key.kz2 = f2_pack(-2.f * kcz, -2.f * kcz);
         const float ckn = c_rbf * (kcx * kcx + kcy * kcy + kcz * kcz);
         key.ckn2 = f2_pack(ckn, ckn);
         key.k_ok = k_ok;
@@ -533,43 +576,36 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         };
 
         for (int t = 0; ok && t < nt; ++t) {
-            const uint32_t par = (uint32_t)(t & 1);
             const int rbuf = t % GA_ROW_BUFS;
             const bool masked = key_hole || (tile_word(t) & 0x8000) != 0;
-            // per-query inputs of the next tile: issue the global loads now, stage them after the first pass
-            bool n_ok = false;
-            float nx = 0.f, ny = 0.f, nz = 0.f, nl2 = INFINITY, nds = 0.f;
-            const bool stage_next = t + 1 < nt && tid < GA_BM;
-            if (stage_next) row_inputs(tile_word(t + 1) & 0x7fff, n_ok, nx, ny, nz, nl2, nds);
-            if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T(t) have landed in TMEM
-            tc_fence_after();
             const GaQueryRows &rw = sm.rows[rbuf];
             uint8_t *ds_tile = sm.ds[t & 1];
-            auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
-                const float4 sp = rw.sph[g];
-                const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
-                const float reach = wk_reach + sp.w;
-                return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-            };
 #pragma unroll
-            for (int pass = 0; pass < 2; ++pass) {
-                const int col0 = half * 64 + pass * 32;  // first query column of this pass
+            for (int sub = 0; sub < 2; ++sub) {
+                const int u = 2 * t + sub;
+                const uint32_t par = (uint32_t)(u & 1);
+                if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T, G^T(u) have landed in TMEM (the producer waited for the rows)
+                tc_fence_after();
                 uint32_t sv[32], dpv[32];
-                tmem_ld32(tm_s + lane_base + col0, sv);
-                tmem_ld32(tm_dp + lane_base + col0, dpv);
+                tmem_ld32(tm_s + lane_base + half * 32, sv);
+                tmem_ld32(tm_dp + lane_base + half * 32, dpv);
                 tmem_wait_ld();
-                if (pass == 1) {  // both passes are in registers: the accumulators may be overwritten
-                    tc_fence_before();
-                    mbar_arrive(&sm.bar_spfree);
-                } else {
-                    if (!(ok = wait_w(&sm.bar_rows[rbuf], (uint32_t)((t / GA_ROW_BUFS) & 1)))) break;
-                }
+                tc_fence_before();
+                mbar_arrive(&sm.bar_spfree);  // the accumulators may be overwritten with the next sub-tile's
+                const int col0 = sub * GA_SUB + half * 32;  // first query column (inside the tile) of this thread's 32
+                const uint32_t g_taddr = tm_g + (u & 1) * GA_SUB + lane_base + half * 32;
+                auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
+                    const float4 sp = rw.sph[g];
+                    const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
+                    const float reach = wk_reach + sp.w;
+                    return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+                };
                 uint32_t pw[16], dw[16];
                 const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
-#define PAI_GA_BWD2(MASKED, FORM, MODE)                                                                                          \
-    do {                                                                                                                         \
-        ga_bwd_chunk<MASKED, FORM, 0, MODE>(sv, dpv, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);      \
-        ga_bwd_chunk<MASKED, FORM, 16, MODE>(sv, dpv, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
+#define PAI_GA_BWD2(MASKED, FORM, MODE)                                                                                            \
+    do {                                                                                                                           \
+        ga_bwd_chunk<MASKED, FORM, 0, MODE>(sv, dpv, g_taddr, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);   \
+        ga_bwd_chunk<MASKED, FORM, 16, MODE>(sv, dpv, g_taddr, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
     } while (0)
                 if (p.form == 0) {
                     if (!far0 && !far1) {
@@ -583,30 +619,23 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     if (masked) PAI_GA_BWD2(true, 1, 2); else PAI_GA_BWD2(false, 1, 2);
                 }
 #undef PAI_GA_BWD2
-                // P^T(t-1) is read by dV(t-1), the dS^T buffer of tile t-2 by dK / dQ(t-2): no store before dV, dK(t-1)
-                // have completed (dQ(t-2) was read out by these very threads during tile t-1)
-                if (pass == 0 && t > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
-                tmem_st16(tm_p + lane_base + col0 / 2, pw);
+                // P^T(u-1) is read by dV(u-1): no store before it has completed (the dS^T buffer of this tile was last read
+                // by dK / dQ two query tiles ago)
+                if (u > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
+                tmem_st16(tm_p + lane_base + half * 16, pw);
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // 8 queries = one 16-byte chunk of the swizzled key row
-                    const int chunk = col0 / 8 + c;
-                    *reinterpret_cast<uint4 *>(ds_tile + (chunk >> 3) * GA_TILE_BYTES + sw128_offset(r, chunk & 7)) =
+                for (int c = 0; c < 4; ++c)  // 8 queries = one 16-byte chunk of the swizzled key row, sub-tile `sub`
+                    *reinterpret_cast<uint4 *>(ds_tile + sub * GA_TILE_BYTES + sw128_offset(r, half * 4 + c)) =
                         make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
-                }
-                if (pass == 0 && stage_next) {
-                    // buffer (t+1) % 3 was last read during tile t-2, which every thread has left (S^T(t) was only issued
-                    // after all of them had loaded the second pass of tile t-1)
-                    ga_stage_rows(sm.rows[(t + 1) % GA_ROW_BUFS], tid, n_ok, nx, ny, nz, nl2, nds);
-                    mbar_arrive(&sm.bar_rows[(t + 1) % GA_ROW_BUFS]);
-                }
+                tmem_wait_st();
+                fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
+                tc_fence_before();
+                mbar_arrive(&sm.bar_pds);
             }
             if (!ok) break;
-            tmem_wait_st();
-            fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
-            tc_fence_before();
-            mbar_arrive(&sm.bar_pds);
+            mbar_arrive(&sm.bar_rowsfree[rbuf]);  // the stager may reuse this tile's row buffer
             if (t > 0) {  // dQ(t-1) completed long ago: read it out now, off the tensor core's critical path
-                if (!(ok = wait_w(&sm.bar_dq, par ^ 1))) break;
+                if (!(ok = wait_w(&sm.bar_dq, (uint32_t)((t - 1) & 1)))) break;
                 tc_fence_after();
                 read_dq(t - 1);
             }
@@ -617,7 +646,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         if (ok) {
             tc_fence_after();
             read_dq(nt - 1);
-            ok = wait_w(&sm.bar_vk, (uint32_t)((nt - 1) & 1));  // the last dV / dK accumulation has completed
+            ok = wait_w(&sm.bar_vk, (uint32_t)((nsub - 1) & 1));  // the last dV / dK accumulation has completed
         }
         if (ok) {
             tc_fence_after();
@@ -667,7 +696,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (p.dbeta) atomicAdd(p.dbeta + h, totb * p.scale);
         }
     }
-    if (warp == GA_BWD_MATH_THREADS / 32) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
+    if (is_producer) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
 }
 
 }  // namespace pai

@@ -45,7 +45,7 @@ constexpr int GA_BN = 128;  // keys per tile
 constexpr int GA_D = 64;    // head dimension
 constexpr int GA_MAX_TILES = GA_PLAN_MAX_TILES;
 constexpr int GA_FWD_MATH_THREADS = 256;
-constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 32;  // + the producer warp
+constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 64;  // + the producer warp and the stager warp
 constexpr float GA_RESCALE_THRESHOLD = 8.f;                 // log2 units
 constexpr uint32_t GA_TMEM_COLS = 512;
 constexpr uint32_t GA_TILE_BYTES = GA_BN * GA_D * 2;  // 16 KiB
@@ -63,12 +63,13 @@ struct GaFwdSmem {
     alignas(1024) uint8_t q[GA_TILE_BYTES];
     alignas(1024) uint8_t k[2][GA_TILE_BYTES];
     alignas(1024) uint8_t v[2][GA_TILE_BYTES];
-    alignas(1024) uint8_t qg[GA_TILE_BYTES];              // geometry operand of the queries (rows of 128 B, 64 B used)
-    alignas(1024) uint8_t kg[GA_KC_BUFS][GA_TILE_BYTES];  // geometry operand of the keys, one per staged tile
+    // Geometry operands: rows of 128 B of which an operand uses 64 (GA_GEO_K bf16), so one buffer holds two of them side by
+    // side (column blocks 0 and 1).  Slot 0: the queries; slots 1..3: the ring of staged key tiles.
+    alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaKeyCoords kc[GA_KC_BUFS];
     float xch[2][2][GA_BM];                       // row maxima exchanged between the two halves, by tile parity
     float lsum[2][GA_BM];                         // row sums exchanged at the end
-    uint64_t bar_q, bar_k[2], bar_v[2], bar_s, bar_sfree, bar_p, bar_o, bar_kc[GA_KC_BUFS];
+    uint64_t bar_q, bar_k[2], bar_v[2], bar_s, bar_sfree, bar_p, bar_o, bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
     uint16_t tiles[GA_MAX_TILES];                 // key tiles with a valid key; bit 15: the tile also has a padded key
     uint32_t tmem_base;
     int abort;                                    // raised by the first wait that expires
@@ -184,7 +185,7 @@ __device__ __forceinline__ void ga_split3(float a, uint32_t &h, uint32_t &m, uin
 //     RIGHT per coordinate: b_h b_m b_h b_l b_h b_m        then n_h n_m n_h n_l n_h n_m
 // (dropped terms are below 2^-24 of |a||b|).  In the forward LEFT = (-2 q, 1), RIGHT = (k, |k|^2): G = |k|^2 - 2 q.k.
 template <bool LEFT>
-__device__ __forceinline__ void ga_write_geo_row(uint8_t *tile, int row, float x, float y, float z, float e) {
+__device__ __forceinline__ void ga_write_geo_row(uint8_t *tile, int block, int row, float x, float y, float z, float e) {
     uint32_t w[16];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -202,15 +203,20 @@ __device__ __forceinline__ void ga_write_geo_row(uint8_t *tile, int row, float x
     }
     w[12] = w[13] = w[14] = w[15] = 0u;
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4 *>(tile + sw128_offset(row, c)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+    for (int c = 0; c < 4; ++c)  // `block` selects the half of the 128-byte row (16-byte chunks 0..3 or 4..7)
+        *reinterpret_cast<uint4 *>(tile + sw128_offset(row, 4 * block + c)) = make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
 }
+// geometry slot -> buffer and column block (two slots share a buffer)
+template <typename Smem>
+__device__ __forceinline__ uint8_t *ga_geo_tile(Smem &sm, int slot) { return sm.geo[slot >> 1]; }
+__device__ __forceinline__ int ga_geo_block(int slot) { return slot & 1; }
 
-// Stages one key tile: the geometry operand row of the key, the mask and the 16-key bounding spheres.  Executed by
-// the 128 threads of warps 0..3 (thread = key); `x, y, z` are the centred coordinates (0 for a padded key).
-__device__ __forceinline__ void ga_stage_keys(GaKeyCoords &kc, uint8_t *kg, int tid, bool ok, float x, float y, float z) {
-    ga_write_geo_row<false>(kg, tid, x, y, z, x * x + y * y + z * z);
-    kc.kb[tid] = ok ? 0.f : -INFINITY;
+// Stages one key of a key tile: its geometry operand row, its mask entry and, with the other 15 keys of its half-warp,
+// the bounding sphere of the group of 16.  Executed by whole warps with key = (lane + 32 m): the 16 lanes of a half-warp
+// hold 16 consecutive keys.  `x, y, z` are the centred coordinates (0 for a padded key).
+__device__ __forceinline__ void ga_stage_key(GaKeyCoords &kc, uint8_t *geo_tile, int geo_block, int key, bool ok, float x, float y, float z) {
+    ga_write_geo_row<false>(geo_tile, geo_block, key, x, y, z, x * x + y * y + z * z);
+    kc.kb[key] = ok ? 0.f : -INFINITY;
     // bounding sphere of the 16 keys of this half-warp (valid keys only): centre = mean, radius = largest distance
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded keys carry 0
 #pragma unroll
@@ -225,8 +231,7 @@ __device__ __forceinline__ void ga_stage_keys(GaKeyCoords &kc, uint8_t *kg, int 
     float d2 = ok ? (x - cx) * (x - cx) + (y - cy) * (y - cy) + (z - cz) * (z - cz) : 0.f;
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) d2 = fmaxf(d2, __shfl_xor_sync(0xffffffffu, d2, off));
-    if ((tid & 15) == 0) kc.sph[tid >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
-    fence_proxy_async();  // the geometry row (generic-proxy stores) must be visible to the tensor core
+    if ((key & 15) == 0) kc.sph[key >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
 }
 
 // 16 logits (8 key pairs) of one row, held in registers: v[] holds raw S on entry and SR on return, g[] the matching
@@ -303,6 +308,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     GaFwdSmem &sm = *reinterpret_cast<GaFwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_FWD_MATH_THREADS / 32;
+    const bool is_producer = warp == GA_FWD_MATH_THREADS / 32, is_stager = warp == GA_FWD_MATH_THREADS / 32 + 1;
     const int half = (warp >> 2) & 1;             // 0: key columns 0..63, 1: 64..127
     const int r = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
     const int N = p.N;
@@ -334,7 +340,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         return;
     }
-    if (warp == 8) {
+    if (is_producer) {
         if (lane == 0) {
             mbar_init(&sm.bar_q, 1);
             mbar_init(&sm.bar_k[0], 1);
@@ -346,7 +352,10 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&sm.bar_sfree, GA_FWD_MATH_THREADS);
             mbar_init(&sm.bar_p, GA_FWD_MATH_THREADS);
 #pragma unroll
-            for (int b = 0; b < GA_KC_BUFS; ++b) mbar_init(&sm.bar_kc[b], GA_BN);
+            for (int b = 0; b < GA_KC_BUFS; ++b) {
+                mbar_init(&sm.bar_kc[b], 32);
+                mbar_init(&sm.bar_kcfree[b], GA_FWD_MATH_THREADS);
+            }
             mbar_fence_init();
             fence_proxy_async();
             // the first loads leave before anything else is set up
@@ -372,27 +381,31 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const float orx = cz[oq * 3], ory = cz[oq * 3 + 1], orz = cz[oq * 3 + 2];
     volatile int *abort_flag = &sm.abort;
 
-    // ---- set-up: first key coordinates --------------------------------------------------------------
-    // Coordinates of a key: the loads are issued at once from a clamped index (none waits for the validity byte) and
-    // only turned into centred coordinates where they are used, so the thread does not stall on them in between.
+    // Coordinates of four keys per stager lane (keys lane, lane + 32, lane + 64, lane + 96 of a tile): the loads are
+    // issued at once from clamped indices, none waits for the validity bytes.
     struct KeyLoad {
-        float gx, gy, gz;
-        uint8_t vb;
-        bool in_range;
+        float gx[4], gy[4], gz[4];
+        uint8_t vb[4];
     };
-    auto key_load = [&](int tile) -> KeyLoad {  // thread tid < 128: key tile*128 + tid
-        const int j = tile * GA_BN + tid, jc = min(j, N - 1);
-        KeyLoad k;
-        k.vb = vz ? vz[jc] : (uint8_t)1;
-        k.gx = cz[jc * 3];
-        k.gy = cz[jc * 3 + 1];
-        k.gz = cz[jc * 3 + 2];
-        k.in_range = j < N;
-        return k;
+    auto key_load = [&](int tile, KeyLoad &k) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int jc = min(tile * GA_BN + lane + 32 * m, N - 1);
+            k.vb[m] = vz ? vz[jc] : (uint8_t)1;
+            k.gx[m] = cz[jc * 3];
+            k.gy[m] = cz[jc * 3 + 1];
+            k.gz[m] = cz[jc * 3 + 2];
+        }
     };
-    auto key_stage = [&](int buf, const KeyLoad &k) {
-        const bool ok = k.in_range && k.vb != 0;
-        ga_stage_keys(sm.kc[buf], sm.kg[buf], tid, ok, ok ? k.gx - orx : 0.f, ok ? k.gy - ory : 0.f, ok ? k.gz - orz : 0.f);
+    auto key_stage = [&](int tile, int buf, const KeyLoad &k) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            const int j = tile * GA_BN + lane + 32 * m;
+            const bool ok = j < N && k.vb[m] != 0;
+            ga_stage_key(sm.kc[buf], ga_geo_tile(sm, 1 + buf), ga_geo_block(1 + buf), lane + 32 * m, ok, ok ? k.gx[m] - orx : 0.f,
+                         ok ? k.gy[m] - ory : 0.f, ok ? k.gz[m] - orz : 0.f);
+        }
+        fence_proxy_async();  // the geometry rows (generic-proxy stores) must be visible to the tensor core
     };
     // this thread's query, centred
     float qcx = 0.f, qcy = 0.f, qcz = 0.f;
@@ -401,15 +414,15 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         qcy = cz[row * 3 + 1] - ory;
         qcz = cz[row * 3 + 2] - orz;
     }
-    if (tid < GA_BN) {
-        key_stage(0, key_load(tile_word_g(0) & 0x7fff));
-        ga_write_geo_row<true>(sm.qg, tid, -2.f * qcx, -2.f * qcy, -2.f * qcz, 1.f);  // (tid < 128: r == tid, half == 0)
+    if (tid < GA_BM) {  // (tid < 128: r == tid, half == 0) the queries' geometry operand: (-2 q, 1)
+        ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), tid, -2.f * qcx, -2.f * qcy, -2.f * qcz, 1.f);
         fence_proxy_async();
     }
+    KeyLoad kl;
+    if (is_stager) key_load(tile_word_g(0) & 0x7fff, kl);  // in flight across the barrier
     tc_fence_before();
-    __syncthreads();  // barriers initialised, TMEM allocated, tile list and first key coordinates in place
+    __syncthreads();  // barriers initialised, TMEM allocated, tile list and the queries' geometry operand in place
     tc_fence_after();
-    if (tid < GA_BN) mbar_arrive(&sm.bar_kc[0]);
     const uint32_t tmem = sm.tmem_base;
     const uint32_t tmem_s = tmem;          // columns [0,128): S
     const uint32_t tmem_o = tmem + 128;    // columns [128,192): O accumulator
@@ -417,7 +430,18 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem_g = tmem + 256;    // columns [256,384): G = |k|^2 - 2 q.k
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
-    if (!is_math) {
+    if (is_stager) {
+        // ================================ stager warp ================================================
+        // Runs up to GA_KC_BUFS key tiles ahead of the math warps: geometry operand rows, masks and bounding spheres.
+        for (int t = 0; t < nt; ++t) {
+            const int b = t % GA_KC_BUFS;
+            if (t > 0) key_load(tile_word(t) & 0x7fff, kl);
+            // buffer b was last used by tile t - GA_KC_BUFS: every math thread has left it (and its G MMA has completed)
+            if (t >= GA_KC_BUFS && !mbar_wait_abortable(&sm.bar_kcfree[b], (uint32_t)((t / GA_KC_BUFS - 1) & 1), abort_flag)) break;
+            key_stage(tile_word(t) & 0x7fff, b, kl);
+            mbar_arrive(&sm.bar_kc[b]);
+        }
+    } else if (is_producer) {
         // ================================ producer warp ==============================================
         if (lane == 0) {
             const uint32_t q_addr = smem_u32(sm.q);
@@ -427,19 +451,18 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024);
             const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
             const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
-            const uint64_t qg_desc = umma_desc_sw128(smem_u32(sm.qg), 16, 1024);
-            const uint64_t kg_desc[GA_KC_BUFS] = {umma_desc_sw128(smem_u32(sm.kg[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.kg[1]), 16, 1024),
-                                                  umma_desc_sw128(smem_u32(sm.kg[2]), 16, 1024)};
+            const uint64_t geo_desc[2] = {umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.geo[1]), 16, 1024)};
+            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
             // S(t) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(t): 2 more over the
             // geometry operands of the staged key tile t
             auto issue_s = [&](int b, int t) {
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
                     umma_ss(tmem_s, q_desc + (uint64_t)(kk * 2), k_desc[b] + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
-                const uint64_t kg = kg_desc[t % GA_KC_BUFS];
+                const uint64_t qg = geo_slot_desc(0), kg = geo_slot_desc(1 + t % GA_KC_BUFS);
 #pragma unroll
                 for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
-                    umma_ss(tmem_g, qg_desc + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
+                    umma_ss(tmem_g, qg + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_s);
             };
             auto issue_pv = [&](int b, bool first) {  // 8 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
@@ -468,7 +491,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 const uint32_t par = (uint32_t)(t & 1);
                 const int b = t & 1;
                 if (t + 1 < nt) {
-                    // every math thread holds S(t) in registers: the S columns and K buffer b are free
+                    // every math thread holds S(t), G(t) in registers: their columns and K buffer b are free
                     if (!(ok = mbar_wait_abortable(&sm.bar_sfree, par, abort_flag))) break;
                     if (t + 2 < nt) load_k(t + 2);
                     if (!(ok = mbar_wait_abortable(&sm.bar_k[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
@@ -541,12 +564,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const bool has_hole = (tile_word(t) & 0x8000) != 0;
             uint32_t s0[32], s1[32];
             float m_loc = -INFINITY;
-            // key coordinates of the next tile: issue the global loads now, stage them after the first pass
-            const bool stage_next = t + 1 < nt && tid < GA_BN;
-            KeyLoad nk = {0.f, 0.f, 0.f, 0, false};
-            if (stage_next) nk = key_load(tile_word(t + 1) & 0x7fff);
-            if (ok) ok = wait_w(&sm.bar_s, par);  // S(t), G(t) have landed in TMEM
-            if (ok) ok = wait_w(&sm.bar_kc[cb], (uint32_t)((t / GA_KC_BUFS) & 1));  // (long complete: the producer waited for it)
+            if (ok) ok = wait_w(&sm.bar_s, par);  // S(t), G(t) have landed in TMEM (the producer waited for the staged key tile)
             if (ok) {
                 tc_fence_after();
                 const GaKeyCoords &kc = sm.kc[cb];
@@ -583,17 +601,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tmem_ld32(tmem_s + lane_base + half * 64 + 32, s1);
                 tmem_wait_ld();
                 PAI_GA_DISPATCH(1, s1, m_b)
-                tc_fence_before();
-                mbar_arrive(&sm.bar_sfree);  // S and G are in registers: the tensor core may overwrite them with the next tile's
 #undef PAI_GA_DISPATCH
 #undef PAI_GA_HALF
+                tc_fence_before();
+                mbar_arrive(&sm.bar_sfree);       // S and G are in registers: the tensor core may overwrite them with the next tile's
+                mbar_arrive(&sm.bar_kcfree[cb]);  // ... and the stager may reuse this key buffer
                 m_loc = fmaxf(m_a, m_b);
-                // Buffer (t+1) % 3 was last read during tile t-2 (by these threads and by the G MMA of that tile), which every
-                // thread has left: S(t) was only issued after all of them had read S(t-1), that is after they had finished tile t-2.
-                if (stage_next) {
-                    key_stage((t + 1) % GA_KC_BUFS, nk);
-                    mbar_arrive(&sm.bar_kc[(t + 1) % GA_KC_BUFS]);
-                }
             }
             sm.xch[par][half][r] = m_loc;
             pair_bar_sync(warp & 3);  // the two warps that share these 32 rows
@@ -675,7 +688,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) tmem_dealloc(tmem, GA_TMEM_COLS);
+    if (is_producer) tmem_dealloc(tmem, GA_TMEM_COLS);
 }
 
 }  // namespace pai
