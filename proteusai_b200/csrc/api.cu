@@ -308,17 +308,19 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
                                         stride_of(q_strides, 2, N), pai::GA_BM))
         return e;
     if (int e = pai::make_map_bf16_zhnd(&mk, K, Z, H, N, d, stride_of(k_strides, 0, Z), stride_of(k_strides, 1, H),
-                                        stride_of(k_strides, 2, N), pai::GA_BN))
+                                        stride_of(k_strides, 2, N), pai::GA_BS))
         return e;
     if (int e = pai::make_map_bf16_zhnd(&mv, V, Z, H, N, d, stride_of(v_strides, 0, Z), stride_of(v_strides, 1, H),
-                                        stride_of(v_strides, 2, N), pai::GA_BN))
+                                        stride_of(v_strides, 2, N), pai::GA_BS))
         return e;
     const int smem = (int)sizeof(pai::GaFwdSmem) + 1024;
     static bool attr_done[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(pai::geoattn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(pai::geoattn_fwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(pai::geoattn_fwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -345,7 +347,8 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
     dim3 grid((q_end - q_begin + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
-    pai::geoattn_fwd_kernel<<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    if (logit_form == 0) pai::geoattn_fwd_kernel<0><<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
+    else pai::geoattn_fwd_kernel<1><<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
 }
 

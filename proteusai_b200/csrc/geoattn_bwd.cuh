@@ -416,7 +416,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int b = t % GA_ROW_BUFS;
             if (t > 0) row_load(tile_word(t) & 0x7fff, rl);
             // buffer b was last used by tile t - GA_ROW_BUFS: every math thread has left it (and its G MMAs have completed)
-            if (t >= GA_ROW_BUFS && !mbar_wait_abortable(&sm.bar_rowsfree[b], (uint32_t)((t / GA_ROW_BUFS - 1) & 1), abort_flag)) break;
+            if (t >= GA_ROW_BUFS && !__all_sync(0xffffffffu, mbar_wait_abortable(&sm.bar_rowsfree[b], (uint32_t)((t / GA_ROW_BUFS - 1) & 1), abort_flag) ? 1 : 0))
+                break;  // (decided by the whole warp: the staging below shuffles across all 32 lanes)
             row_stage(tile_word(t) & 0x7fff, b, rl);
             mbar_arrive(&sm.bar_rows[b]);
         }

@@ -6,34 +6,35 @@
 // README states (README.md:40); the form the reference tree's kernel implements is the second
 // instantiation (FORM = 1).
 //
-// One CTA = 128 query rows of one (batch, head): 8 math warps and one producer warp; two CTAs share an SM.
-// Query row r = TMEM lane r is shared by two math threads: warp w (0..3) takes key columns 0..63 of a
-// tile and output columns 0..31, warp w + 4 takes key columns 64..127 and output columns 32..63 (both
-// may touch TMEM lanes 32 (w % 4) ..).  Lane 0 of the producer warp issues every TMA load and MMA.
-// Tensor memory: S [0,128) fp32, O [128,192) fp32, P [192,256) bf16 pairs, G [256,384) fp32.
-//   S  = Q K^T : tcgen05.mma, A = Q tile, B = K tile (both K-major, 128-byte swizzle, via TMA);
-//   G          : the geometry of the tile comes from the tensor core as well: G_ij = |k_j|^2 - 2 q_i . k_j
+// One CTA = 128 query rows of one (batch, head): four math warps (one thread per query row = TMEM lane, so a row
+// needs no exchange between threads), a producer warp (lane 0 issues every TMA load and MMA) and a stager warp.  Two
+// CTAs share an SM: their phases drift apart, so the SFU-heavy and FMA-heavy stretches of one overlap the waits of
+// the other, and a CTA's set-up hides behind its neighbour's work.  Keys are taken 64 at a time (a "step"; two steps
+// per 128-key tile of the batch plan).
+// Tensor memory (256 columns): S [0,64) fp32, G [64,128) fp32, O [128,192) fp32, P [192,224) bf16 pairs.
+//   S  = Q K^T : tcgen05.mma, A = Q tile, B = K step (both K-major, 128-byte swizzle, via TMA);
+//   G          : the geometry of the step comes from the tensor core as well: G_ij = |k_j|^2 - 2 q_i . k_j
 //                (coordinates centred on the tile's first valid query) is a product of two narrow operand tiles
 //                that the threads write themselves, each fp32 coordinate split into three bf16 terms
 //                (ga_write_geo_row), so that |r_i - r_j|^2 = G_ij + |q_i|^2 to fp32 accuracy.  Reading key
 //                coordinates from shared memory instead costs every warp a broadcast load per key pair, which
 //                made the shared-memory pipe, not the SFU, the limiter of this stage;
-//   softmax    : each math thread reads its 64 G values and 64 logits ONCE into registers (tcgen05.ld) and
-//                releases the columns, so the tensor core computes the next key tile underneath the
-//                softmax of this one.  R = 2^(c G + c |q|^2), SR = S scale (1 + R) in packed fp32x2 arithmetic.
+//   softmax    : a math thread reads the 64 logits of its row ONCE into registers (tcgen05.ld), G group by group,
+//                and releases the columns, so the tensor core computes the next step underneath the softmax of
+//                this one.  R = 2^(c G + c |q|^2), SR = S scale (1 + R) in packed fp32x2 arithmetic.
 //                A group of 16 keys whose bounding sphere lies farther than 5.9 sigma_h from the bounding sphere
 //                of the warp's 32 queries has R < 2^-25 for every pair, where S (1 + R) == S in fp32: there
-//                the exponential is skipped (most of the off-diagonal work of the narrow heads).  The two
-//                halves of a row exchange their maxima through shared memory; P is written as bf16 straight
-//                into tensor memory;
-//   O += P V   : tcgen05.mma with the A operand (P) read from tensor memory, B = V tile (MN-major: keys
-//                are the K dimension), accumulated in TMEM [128 x 64] across the key tiles.  The running
-//                maximum is only raised when a tile exceeds it by more than 2^8 (then the accumulator and
+//                the exponential is skipped (most of the off-diagonal work of the narrow heads).  P is written
+//                as bf16 straight into tensor memory;
+//   O += P V   : tcgen05.mma with the A operand (P) read from tensor memory, B = V step (MN-major: keys
+//                are the K dimension), accumulated in TMEM [128 x 64] across the steps.  The running
+//                maximum is only raised when a step exceeds it by more than 2^8 (then the accumulator and
 //                the row sum are rescaled); otherwise P is computed against the slightly stale maximum,
 //                which is exact after the final normalisation.
-// K and V are double-buffered.  Key tiles without any valid key are never loaded (list from the batch plan,
-// geoattn_plan.cuh); tiles without a padded key take a path without the mask; CTAs without any valid query
-// only write zeros.  Every wait is bounded and abortable (tc.cuh).
+// K and V are double-buffered.  The stager warp runs up to three key tiles ahead: geometry operand rows, masks and
+// bounding spheres.  Key tiles without any valid key are never loaded (list from the batch plan, geoattn_plan.cuh);
+// tiles without a padded key take a path without the mask; CTAs without any valid query only write zeros.  Every
+// wait is bounded and abortable (tc.cuh).
 #pragma once
 #include "geoattn_plan.cuh"
 #include "tc.cuh"
@@ -41,18 +42,20 @@
 namespace pai {
 
 constexpr int GA_BM = 128;  // query rows per CTA
-constexpr int GA_BN = 128;  // keys per tile
+constexpr int GA_BN = 128;  // tokens per tile of the batch plan (and per query / key tile of the backward)
+constexpr int GA_BS = 64;   // keys per step of the forward
 constexpr int GA_D = 64;    // head dimension
 constexpr int GA_MAX_TILES = GA_PLAN_MAX_TILES;
-constexpr int GA_FWD_MATH_THREADS = 256;
+constexpr int GA_FWD_MATH_THREADS = 128;
 constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 64;  // + the producer warp and the stager warp
 constexpr float GA_RESCALE_THRESHOLD = 8.f;                 // log2 units
-constexpr uint32_t GA_TMEM_COLS = 512;
+constexpr uint32_t GA_TMEM_COLS = 256;
 constexpr uint32_t GA_TILE_BYTES = GA_BN * GA_D * 2;  // 16 KiB
-constexpr int GA_KC_BUFS = 3;                           // key-coordinate buffers (see the tile loop)
+constexpr uint32_t GA_STEP_BYTES = GA_BS * GA_D * 2;  // 8 KiB
+constexpr int GA_KC_BUFS = 3;                           // staged key tiles in flight
 constexpr float GA_FAR_SIGMAS = 5.9f;                   // exp(-d^2 / 2 sigma^2) < 2^-25 beyond 5.887 sigma
 
-constexpr int GA_GEO_K = 32;                            // bf16 columns of the geometry operands (21 used)
+constexpr int GA_GEO_K = 32;                            // bf16 columns of the geometry operands (24 used)
 
 struct GaKeyCoords {                  // per-key side data of one tile
     alignas(16) float kb[GA_BN];      // 0 for a valid key, -inf for a padded one
@@ -61,14 +64,12 @@ struct GaKeyCoords {                  // per-key side data of one tile
 
 struct GaFwdSmem {
     alignas(1024) uint8_t q[GA_TILE_BYTES];
-    alignas(1024) uint8_t k[2][GA_TILE_BYTES];
-    alignas(1024) uint8_t v[2][GA_TILE_BYTES];
+    alignas(1024) uint8_t k[2][GA_STEP_BYTES];
+    alignas(1024) uint8_t v[2][GA_STEP_BYTES];
     // Geometry operands: rows of 128 B of which an operand uses 64 (GA_GEO_K bf16), so one buffer holds two of them side by
     // side (column blocks 0 and 1).  Slot 0: the queries; slots 1..3: the ring of staged key tiles.
     alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaKeyCoords kc[GA_KC_BUFS];
-    float xch[2][2][GA_BM];                       // row maxima exchanged between the two halves, by tile parity
-    float lsum[2][GA_BM];                         // row sums exchanged at the end
     uint64_t bar_q, bar_k[2], bar_v[2], bar_s, bar_sfree, bar_p, bar_o, bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
     uint16_t tiles[GA_MAX_TILES];                 // key tiles with a valid key; bit 15: the tile also has a padded key
     uint32_t tmem_base;
@@ -144,23 +145,6 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-// Barrier among a subset of the CTA's warps.  The id is an immediate so that the compiler counts the
-// barriers the kernel really uses: an SM has 16, and a kernel that indexes them with a register is
-// charged all 16, which limits it to one CTA per SM.
-template <int ID>
-__device__ __forceinline__ void named_bar_sync(int count) {
-    asm volatile("bar.sync %0, %1;" ::"n"(ID), "r"(count) : "memory");
-}
-// the two warps w and w + 4 that share 32 query rows
-__device__ __forceinline__ void pair_bar_sync(int quarter) {
-    switch (quarter) {
-        case 0: named_bar_sync<1>(64); break;
-        case 1: named_bar_sync<2>(64); break;
-        case 2: named_bar_sync<3>(64); break;
-        default: named_bar_sync<4>(64); break;
-    }
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -291,17 +275,18 @@ __device__ __forceinline__ float ga_sr_chunk(uint32_t (&w)[32], uint32_t g_taddr
 #undef v
 }
 
-// 32 logits of one thread (two groups of 16 keys; H = which 32 of the thread's 64).  MODE 0: every group of the row is
-// near, 1: every group is far, 2: per group (`far`).  Each group keeps its own running maximum.
+// 32 logits of one thread (two groups of 16 keys; H = which 32 of the thread's 64 = of the step's keys).  MODE 0: every
+// group of the step is near, 1: every group is far, 2: per group (`far`).  `kb`: the mask entries of the step's 64 keys.
 template <bool MASKED, int FORM, int MODE, int H>
-__device__ __forceinline__ float ga_sr_half(uint32_t (&sv)[32], uint32_t gv, const GaKeyCoords &kc, int half,
-                                            const bool (&far)[4], f2_t crbf2, f2_t cqn2, f2_t cs2, const GaForm &fm) {
-    const float m0 = ga_sr_chunk<MASKED, FORM, 0, MODE>(sv, gv, far[2 * H], &kc.kb[half * 64 + (2 * H) * 16], crbf2, cqn2, cs2, fm);
-    const float m1 = ga_sr_chunk<MASKED, FORM, 16, MODE>(sv, gv, far[2 * H + 1], &kc.kb[half * 64 + (2 * H + 1) * 16], crbf2, cqn2, cs2, fm);
+__device__ __forceinline__ float ga_sr_half(uint32_t (&sv)[32], uint32_t gv, const float *kb, const bool (&far)[4], f2_t crbf2, f2_t cqn2,
+                                            f2_t cs2, const GaForm &fm) {
+    const float m0 = ga_sr_chunk<MASKED, FORM, 0, MODE>(sv, gv, far[2 * H], kb + (2 * H) * 16, crbf2, cqn2, cs2, fm);
+    const float m1 = ga_sr_chunk<MASKED, FORM, 16, MODE>(sv, gv, far[2 * H + 1], kb + (2 * H + 1) * 16, crbf2, cqn2, cs2, fm);
     return fmaxf(m0, m1);
 }
 
-__global__ void __launch_bounds__(GA_FWD_THREADS, 1)
+template <int FORM>
+__global__ void __launch_bounds__(GA_FWD_THREADS, 2)
 geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const GaFwdParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -309,8 +294,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_FWD_MATH_THREADS / 32;
     const bool is_producer = warp == GA_FWD_MATH_THREADS / 32, is_stager = warp == GA_FWD_MATH_THREADS / 32 + 1;
-    const int half = (warp >> 2) & 1;             // 0: key columns 0..63, 1: 64..127
-    const int r = (warp & 3) * 32 + lane;         // query row inside the tile = TMEM lane
+    const int r = tid & (GA_BM - 1);              // math threads: query row inside the tile = TMEM lane
     const int N = p.N;
     const int tiles_all = (N + GA_BN - 1) / GA_BN;
     int zh_local = blockIdx.y;                    // index into the shard of (batch, head) pairs
@@ -331,15 +315,17 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // this CTA's query tile: dead (no valid query) or the offset of its first valid query
     const int q_info = p.plan ? ga_plan_info(p.plan, p.Z, N, z)[i0 / GA_BM] : ga_plan_info_unmasked(N, i0 / GA_BM);
     const bool q_ok = is_math && row < N && (vz ? vz[row] != 0 : true);
-    __nv_bfloat16 *orow = p.out + (long long)z * p.so_z + (long long)h * p.so_h + (long long)row * p.so_n + half * 32;
+    __nv_bfloat16 *orow = p.out + (long long)z * p.so_z + (long long)h * p.so_h + (long long)row * p.so_n;
     if (q_info < 0 || nt == 0) {  // nothing to attend from / to: zeros and -inf
         if (is_math && row < N) {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) reinterpret_cast<uint4 *>(orow)[c] = make_uint4(0, 0, 0, 0);
-            if (half == 0) p.lse[(size_t)zh * N + row] = -INFINITY;
+            for (int c = 0; c < 8; ++c) reinterpret_cast<uint4 *>(orow)[c] = make_uint4(0, 0, 0, 0);
+            p.lse[(size_t)zh * N + row] = -INFINITY;
         }
         return;
     }
+    // steps of 64 keys: u = 2 t + sub; the second half of the sequence's last tile may lie entirely past N
+    const int nu = 2 * nt - (((tile_word_g(nt - 1) & 0x7fff) * GA_BN + GA_BS >= N) ? 1 : 0);
     if (is_producer) {
         if (lane == 0) {
             mbar_init(&sm.bar_q, 1);
@@ -361,12 +347,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // the first loads leave before anything else is set up
             mbar_expect_tx(&sm.bar_q, GA_TILE_BYTES);
             tma_load_4d(sm.q, &map_q, 0, i0, h, z, &sm.bar_q);
-            for (int t = 0; t < 2 && t < nt; ++t) {
-                const int j0 = (tile_word_g(t) & 0x7fff) * GA_BN;
-                mbar_expect_tx(&sm.bar_k[t], GA_TILE_BYTES);
-                tma_load_4d(sm.k[t], &map_k, 0, j0, h, z, &sm.bar_k[t]);
-                mbar_expect_tx(&sm.bar_v[t], GA_TILE_BYTES);
-                tma_load_4d(sm.v[t], &map_v, 0, j0, h, z, &sm.bar_v[t]);
+            for (int u = 0; u < 2 && u < nu; ++u) {
+                const int j0 = (tile_word_g(u >> 1) & 0x7fff) * GA_BN + (u & 1) * GA_BS;
+                mbar_expect_tx(&sm.bar_k[u], GA_STEP_BYTES);
+                tma_load_4d(sm.k[u], &map_k, 0, j0, h, z, &sm.bar_k[u]);
+                mbar_expect_tx(&sm.bar_v[u], GA_STEP_BYTES);
+                tma_load_4d(sm.v[u], &map_v, 0, j0, h, z, &sm.bar_v[u]);
             }
             sm.abort = 0;
         }
@@ -414,8 +400,8 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         qcy = cz[row * 3 + 1] - ory;
         qcz = cz[row * 3 + 2] - orz;
     }
-    if (tid < GA_BM) {  // (tid < 128: r == tid, half == 0) the queries' geometry operand: (-2 q, 1)
-        ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), tid, -2.f * qcx, -2.f * qcy, -2.f * qcz, 1.f);
+    if (is_math) {  // the queries' geometry operand: (-2 q, 1)
+        ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), r, -2.f * qcx, -2.f * qcy, -2.f * qcz, 1.f);
         fence_proxy_async();
     }
     KeyLoad kl;
@@ -424,10 +410,10 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();  // barriers initialised, TMEM allocated, tile list and the queries' geometry operand in place
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t tmem_s = tmem;          // columns [0,128): S
+    const uint32_t tmem_s = tmem;          // columns [0,64): S
+    const uint32_t tmem_g = tmem + 64;     // columns [64,128): G = |k|^2 - 2 q.k
     const uint32_t tmem_o = tmem + 128;    // columns [128,192): O accumulator
-    const uint32_t tmem_p = tmem + 192;    // columns [192,256): P as bf16 pairs (A operand of P V)
-    const uint32_t tmem_g = tmem + 256;    // columns [256,384): G = |k|^2 - 2 q.k
+    const uint32_t tmem_p = tmem + 192;    // columns [192,224): P as bf16 pairs (A operand of P V)
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
     if (is_stager) {
@@ -436,76 +422,83 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int t = 0; t < nt; ++t) {
             const int b = t % GA_KC_BUFS;
             if (t > 0) key_load(tile_word(t) & 0x7fff, kl);
-            // buffer b was last used by tile t - GA_KC_BUFS: every math thread has left it (and its G MMA has completed)
-            if (t >= GA_KC_BUFS && !mbar_wait_abortable(&sm.bar_kcfree[b], (uint32_t)((t / GA_KC_BUFS - 1) & 1), abort_flag)) break;
+            // buffer b was last used by tile t - GA_KC_BUFS: every math thread has left it (and its G MMAs have completed)
+            if (t >= GA_KC_BUFS && !__all_sync(0xffffffffu, mbar_wait_abortable(&sm.bar_kcfree[b], (uint32_t)((t / GA_KC_BUFS - 1) & 1), abort_flag) ? 1 : 0))
+                break;  // (decided by the whole warp: the staging below shuffles across all 32 lanes)
             key_stage(tile_word(t) & 0x7fff, b, kl);
             mbar_arrive(&sm.bar_kc[b]);
         }
     } else if (is_producer) {
         // ================================ producer warp ==============================================
         if (lane == 0) {
-            const uint32_t q_addr = smem_u32(sm.q);
-            constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_BN, false, false);  // Q K^T: both K-major
+            constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_BS, false, false);  // Q K^T and G: both K-major, N = 64
             constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);    // P V: V is MN-major
             // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
-            const uint64_t q_desc = umma_desc_sw128(q_addr, 16, 1024);
+            const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
             const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
             const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
             const uint64_t geo_desc[2] = {umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.geo[1]), 16, 1024)};
             auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
-            // S(t) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(t): 2 more over the
-            // geometry operands of the staged key tile t
-            auto issue_s = [&](int b, int t) {
+            constexpr uint64_t STEP_ROWS = (uint64_t)(GA_BS * 128) >> 4;  // 64 rows of a swizzled tile, in 16-byte units
+            // S(u) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(u): 2 more over the
+            // geometry operands (the keys' rows start 64 rows into the staged tile for the second step of a tile)
+            auto issue_s = [&](int u) {
+                const int b = u & 1, t = u >> 1;
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
                     umma_ss(tmem_s, q_desc + (uint64_t)(kk * 2), k_desc[b] + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
-                const uint64_t qg = geo_slot_desc(0), kg = geo_slot_desc(1 + t % GA_KC_BUFS);
+                const uint64_t qg = geo_slot_desc(0), kg = geo_slot_desc(1 + t % GA_KC_BUFS) + (uint64_t)(u & 1) * STEP_ROWS;
 #pragma unroll
                 for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
                     umma_ss(tmem_g, qg + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
                 umma_commit(&sm.bar_s);
             };
-            auto issue_pv = [&](int b, bool first) {  // 8 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
+            auto issue_pv = [&](int u) {  // 4 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
+                const int b = u & 1;
 #pragma unroll
-                for (int kk = 0; kk < GA_BN / 16; ++kk)
-                    umma_ts(tmem_o, tmem_p + kk * 8, v_desc[b] + (uint64_t)(kk * 128), IDESC_O, (first && kk == 0) ? 0u : 1u);
+                for (int kk = 0; kk < GA_BS / 16; ++kk)
+                    umma_ts(tmem_o, tmem_p + kk * 8, v_desc[b] + (uint64_t)(kk * 128), IDESC_O, (u == 0 && kk == 0) ? 0u : 1u);
                 umma_commit(&sm.bar_o);
             };
-            auto load_k = [&](int t) {
-                const int b = t & 1;
-                mbar_expect_tx(&sm.bar_k[b], GA_TILE_BYTES);
-                tma_load_4d(sm.k[b], &map_k, 0, (tile_word(t) & 0x7fff) * GA_BN, h, z, &sm.bar_k[b]);
+            auto key0 = [&](int u) -> int { return (tile_word(u >> 1) & 0x7fff) * GA_BN + (u & 1) * GA_BS; };
+            auto load_k = [&](int u) {
+                const int b = u & 1;
+                mbar_expect_tx(&sm.bar_k[b], GA_STEP_BYTES);
+                tma_load_4d(sm.k[b], &map_k, 0, key0(u), h, z, &sm.bar_k[b]);
             };
-            auto load_v = [&](int t) {
-                const int b = t & 1;
-                mbar_expect_tx(&sm.bar_v[b], GA_TILE_BYTES);
-                tma_load_4d(sm.v[b], &map_v, 0, (tile_word(t) & 0x7fff) * GA_BN, h, z, &sm.bar_v[b]);
+            auto load_v = [&](int u) {
+                const int b = u & 1;
+                mbar_expect_tx(&sm.bar_v[b], GA_STEP_BYTES);
+                tma_load_4d(sm.v[b], &map_v, 0, key0(u), h, z, &sm.bar_v[b]);
             };
             bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag) && mbar_wait_abortable(&sm.bar_k[0], 0, abort_flag) &&
                       mbar_wait_abortable(&sm.bar_kc[0], 0, abort_flag);
             if (ok) {
                 tc_fence_after();
-                issue_s(0, 0);
+                issue_s(0);
             }
-            for (int t = 0; ok && t < nt; ++t) {
-                const uint32_t par = (uint32_t)(t & 1);
-                const int b = t & 1;
-                if (t + 1 < nt) {
-                    // every math thread holds S(t), G(t) in registers: their columns and K buffer b are free
+            for (int u = 0; ok && u < nu; ++u) {
+                const uint32_t par = (uint32_t)(u & 1);
+                const int b = u & 1;
+                if (u + 1 < nu) {
+                    // every math thread holds S(u), G(u) in registers: their columns and K buffer b are free
                     if (!(ok = mbar_wait_abortable(&sm.bar_sfree, par, abort_flag))) break;
-                    if (t + 2 < nt) load_k(t + 2);
-                    if (!(ok = mbar_wait_abortable(&sm.bar_k[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
-                    if (!(ok = mbar_wait_abortable(&sm.bar_kc[(t + 1) % GA_KC_BUFS], (uint32_t)(((t + 1) / GA_KC_BUFS) & 1), abort_flag))) break;
+                    if (u + 2 < nu) load_k(u + 2);
+                    if (!(ok = mbar_wait_abortable(&sm.bar_k[b ^ 1], (uint32_t)(((u + 1) >> 1) & 1), abort_flag))) break;
+                    if (b == 1) {  // the next step opens key tile t + 1: its staged geometry operand
+                        const int t1 = (u + 1) >> 1;
+                        if (!(ok = mbar_wait_abortable(&sm.bar_kc[t1 % GA_KC_BUFS], (uint32_t)((t1 / GA_KC_BUFS) & 1), abort_flag))) break;
+                    }
                     tc_fence_after();
-                    issue_s(b ^ 1, t + 1);  // S, G(t+1) run underneath the softmax of tile t
+                    issue_s(u + 1);  // S, G(u+1) run underneath the softmax of step u
                 }
-                if (!(ok = mbar_wait_abortable(&sm.bar_p, par, abort_flag))) break;  // P(t) in TMEM, O rescaled if need be
-                if (!(ok = mbar_wait_abortable(&sm.bar_v[b], (uint32_t)((t >> 1) & 1), abort_flag))) break;
+                if (!(ok = mbar_wait_abortable(&sm.bar_p, par, abort_flag))) break;  // P(u) in TMEM, O rescaled if need be
+                if (!(ok = mbar_wait_abortable(&sm.bar_v[b], (uint32_t)((u >> 1) & 1), abort_flag))) break;
                 tc_fence_after();
-                issue_pv(b, t == 0);
-                if (t + 2 < nt) {  // V buffer b is free once P V(t) has completed
+                issue_pv(u);
+                if (u + 2 < nu) {  // V buffer b is free once P V(u) has completed
                     if (!(ok = mbar_wait_abortable(&sm.bar_o, par, abort_flag))) break;
-                    load_v(t + 2);
+                    load_v(u + 2);
                 }
             }
             if (!ok) {
@@ -528,7 +521,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const float cqn = c_rbf * (qcx * qcx + qcy * qcy + qcz * qcz);
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cqn2 = f2_pack(cqn, cqn), cs2 = f2_pack(c_s, c_s);
         GaForm fm;
-        ga_form_setup(fm, p.form, p.form == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
+        ga_form_setup(fm, FORM, FORM == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
         // bounding sphere of the warp's valid queries; wq_reach = (distance beyond which R does not count) + radius
         float wqx, wqy, wqz, wq_reach;
         {
@@ -550,72 +543,61 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             wq_reach = fm.far_cut * sig + sqrtf(d2) * 1.0001f + 1e-4f;
             if (!p.far_skip || !(fm.far_cut < INFINITY)) wq_reach = -INFINITY;  // test off
         }
-        float m_run = -INFINITY, l_run = 0.f;  // l_run: this thread's half of the row sum
-        // `ok` is kept uniform across the warp (tcgen05.ld / st and the votes below need all 32 lanes), and a warp
-        // that has given up still meets its partner at every pair barrier: the loop only gets cheap, never shorter.
+        float m_run = -INFINITY, l_run = 0.f;
+        // `ok` is kept uniform across the warp (tcgen05.ld / st and the votes below need all 32 lanes)
         bool ok = true;
         auto wait_w = [&](uint64_t *bar, uint32_t parity) -> bool {
             return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
         };
 
-        for (int t = 0; t < nt; ++t) {
-            const uint32_t par = (uint32_t)(t & 1);
-            const int cb = t % GA_KC_BUFS;
+        for (int u = 0; ok && u < nu; ++u) {
+            const uint32_t par = (uint32_t)(u & 1);
+            const int t = u >> 1, sub = u & 1, cb = t % GA_KC_BUFS;
             const bool has_hole = (tile_word(t) & 0x8000) != 0;
             uint32_t s0[32], s1[32];
-            float m_loc = -INFINITY;
-            if (ok) ok = wait_w(&sm.bar_s, par);  // S(t), G(t) have landed in TMEM (the producer waited for the staged key tile)
-            if (ok) {
-                tc_fence_after();
-                const GaKeyCoords &kc = sm.kc[cb];
-                bool far[4];
-                int nfar = 0;
+            if (!(ok = wait_w(&sm.bar_s, par))) break;  // S(u), G(u) have landed in TMEM (the producer waited for the staged key tile)
+            tc_fence_after();
+            const GaKeyCoords &kc = sm.kc[cb];
+            const float *kb = kc.kb + sub * GA_BS;
+            bool far[4];
+            int nfar = 0;
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {  // far test of the four key groups against this warp's queries (warp-uniform)
-                    const float4 sp = kc.sph[half * 4 + c];
-                    const float dx = sp.x - wqx, dy = sp.y - wqy, dz = sp.z - wqz;
-                    const float reach = wq_reach + sp.w;  // wq_reach = cut + radius of the query sphere (-inf: test off)
-                    far[c] = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-                    nfar += far[c] ? 1 : 0;
-                }
-                // two halves of 32 logits: S of the half into registers, G group by group, SR in place (it stays for the P phase)
-                uint32_t gv = tmem_g + lane_base + half * 64;
-                float m_a, m_b;
-#define PAI_GA_HALF(H, SV, MASKED, FORM, MODE) ga_sr_half<MASKED, FORM, MODE, H>(SV, gv, kc, half, far, crbf2, cqn2, cs2, fm)
-#define PAI_GA_DISPATCH(H, SV, OUT)                                                                             \
-    if (p.form == 0) {                                                                                          \
-        if (nfar == 0) {                                                                                        \
-            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 0); else OUT = PAI_GA_HALF(H, SV, false, 0, 0);     \
-        } else if (nfar == 4) {                                                                                 \
-            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 1); else OUT = PAI_GA_HALF(H, SV, false, 0, 1);     \
-        } else {                                                                                                \
-            if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0, 2); else OUT = PAI_GA_HALF(H, SV, false, 0, 2);     \
-        }                                                                                                       \
-    } else {                                                                                                    \
-        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 1, 2); else OUT = PAI_GA_HALF(H, SV, false, 1, 2);         \
+            for (int c = 0; c < 4; ++c) {  // far test of the step's four key groups against this warp's queries (warp-uniform)
+                const float4 sp = kc.sph[sub * 4 + c];
+                const float dx = sp.x - wqx, dy = sp.y - wqy, dz = sp.z - wqz;
+                const float reach = wq_reach + sp.w;  // wq_reach = cut + radius of the query sphere (-inf: test off)
+                far[c] = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+                nfar += far[c] ? 1 : 0;
+            }
+            // S of the row into registers, G group by group, SR in place (it stays for the P phase)
+            uint32_t gv = tmem_g + lane_base;
+            float m_a, m_b;
+#define PAI_GA_HALF(H, SV, MASKED, MODE) ga_sr_half<MASKED, FORM, MODE, H>(SV, gv, kb, far, crbf2, cqn2, cs2, fm)
+#define PAI_GA_DISPATCH(H, SV, OUT)                                                                       \
+    if (FORM == 0 && nfar == 0) {                                                                         \
+        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0); else OUT = PAI_GA_HALF(H, SV, false, 0);         \
+    } else if (FORM == 0 && nfar == 4) {                                                                  \
+        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 1); else OUT = PAI_GA_HALF(H, SV, false, 1);         \
+    } else {                                                                                              \
+        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 2); else OUT = PAI_GA_HALF(H, SV, false, 2);         \
     }
-                tmem_ld32(tmem_s + lane_base + half * 64, s0);
-                tmem_wait_ld();
-                PAI_GA_DISPATCH(0, s0, m_a)
-                gv += 32;
-                tmem_ld32(tmem_s + lane_base + half * 64 + 32, s1);
-                tmem_wait_ld();
-                PAI_GA_DISPATCH(1, s1, m_b)
+            tmem_ld32(tmem_s + lane_base, s0);
+            tmem_ld32(tmem_s + lane_base + 32, s1);
+            tmem_wait_ld();
+            PAI_GA_DISPATCH(0, s0, m_a)
+            gv += 32;
+            PAI_GA_DISPATCH(1, s1, m_b)
 #undef PAI_GA_DISPATCH
 #undef PAI_GA_HALF
-                tc_fence_before();
-                mbar_arrive(&sm.bar_sfree);       // S and G are in registers: the tensor core may overwrite them with the next tile's
-                mbar_arrive(&sm.bar_kcfree[cb]);  // ... and the stager may reuse this key buffer
-                m_loc = fmaxf(m_a, m_b);
-            }
-            sm.xch[par][half][r] = m_loc;
-            pair_bar_sync(warp & 3);  // the two warps that share these 32 rows
-            if (!ok) continue;
-            // the tile maximum is finite for form 0 (every listed tile holds a valid key); form 1 can mask a whole row of a tile
-            const float m_tile = fmaxf(m_loc, sm.xch[par][half ^ 1][r]);
+            tc_fence_before();
+            mbar_arrive(&sm.bar_sfree);  // S and G are in registers: the tensor core may overwrite them with the next step's
+            if (sub == 1 || u + 1 == nu) mbar_arrive(&sm.bar_kcfree[cb]);  // ... and the stager may reuse this key tile's buffer
+            // the row maximum of the step (finite for form 0: every listed tile holds a valid key, though a step of it may
+            // not; form 1 can mask a whole row)
+            const float m_tile = fmaxf(m_a, m_b);
             float alpha = 1.f;
             bool raise = false;
-            if (t == 0) {
+            if (m_run == -INFINITY) {
                 m_run = m_tile;
             } else if (m_tile > m_run + GA_RESCALE_THRESHOLD) {
                 raise = true;
@@ -641,49 +623,52 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             float l0, l1;
             f2_unpack(f2_add(l2, l2b), l0, l1);
             l_run = l_run * alpha + (l0 + l1);
-            if (t > 0) {  // P V(t-1) has completed: the P columns are free and the O accumulator is at rest
-                if (!(ok = wait_w(&sm.bar_o, par ^ 1))) continue;
+            if (u > 0) {  // P V(u-1) has completed: the P columns are free and the O accumulator is at rest
+                if (!(ok = wait_w(&sm.bar_o, par ^ 1))) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, raise)) {  // same rows, hence the same decision, in the partner warp
-                    uint32_t v[32];
-                    tmem_ld32(tmem_o + lane_base + half * 32, v);
-                    tmem_wait_ld();
+                if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                    tmem_st32(tmem_o + lane_base + half * 32, v);
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_o + lane_base + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                        tmem_st32(tmem_o + lane_base + c * 32, v);
+                    }
                 }
             }
-            tmem_st32(tmem_p + lane_base + half * 32, pw);
+            tmem_st32(tmem_p + lane_base, pw);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sm.bar_p);
         }
 
         // ---- epilogue ----------------------------------------------------------------------------------
-        if (ok) ok = wait_w(&sm.bar_o, (uint32_t)((nt - 1) & 1));
-        uint32_t ov[32];
-        if (ok) {
+        if (ok) ok = wait_w(&sm.bar_o, (uint32_t)((nu - 1) & 1));
+        if (ok) {  // (warp-uniform: tcgen05.ld needs all 32 lanes, rows past N included; only the stores are per row)
             tc_fence_after();
-            tmem_ld32(tmem_o + lane_base + half * 32, ov);
-            tmem_wait_ld();
-        }
-        sm.lsum[half][r] = l_run;
-        pair_bar_sync(warp & 3);
-        if (ok && row < N) {
-            const float l_tot = l_run + sm.lsum[half ^ 1][r];
             // select, do not multiply by 0: padding may hold Inf / NaN in Q, K or V
-            const bool live = q_ok && l_tot > 0.f;
-            const float inv = live ? 1.f / l_tot : 0.f;
+            const bool live = q_ok && l_run > 0.f;
+            const float inv = live ? 1.f / l_run : 0.f;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint4 pk;
-                pk.x = pack_bf16x2(__uint_as_float(ov[c * 8 + 0]) * inv, __uint_as_float(ov[c * 8 + 1]) * inv);
-                pk.y = pack_bf16x2(__uint_as_float(ov[c * 8 + 2]) * inv, __uint_as_float(ov[c * 8 + 3]) * inv);
-                pk.z = pack_bf16x2(__uint_as_float(ov[c * 8 + 4]) * inv, __uint_as_float(ov[c * 8 + 5]) * inv);
-                pk.w = pack_bf16x2(__uint_as_float(ov[c * 8 + 6]) * inv, __uint_as_float(ov[c * 8 + 7]) * inv);
-                reinterpret_cast<uint4 *>(orow)[c] = live ? pk : make_uint4(0, 0, 0, 0);
+            for (int hh = 0; hh < 2; ++hh) {
+                uint32_t ov[32];
+                tmem_ld32(tmem_o + lane_base + hh * 32, ov);
+                tmem_wait_ld();
+                if (row < N) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(__uint_as_float(ov[c * 8 + 0]) * inv, __uint_as_float(ov[c * 8 + 1]) * inv);
+                        pk.y = pack_bf16x2(__uint_as_float(ov[c * 8 + 2]) * inv, __uint_as_float(ov[c * 8 + 3]) * inv);
+                        pk.z = pack_bf16x2(__uint_as_float(ov[c * 8 + 4]) * inv, __uint_as_float(ov[c * 8 + 5]) * inv);
+                        pk.w = pack_bf16x2(__uint_as_float(ov[c * 8 + 6]) * inv, __uint_as_float(ov[c * 8 + 7]) * inv);
+                        reinterpret_cast<uint4 *>(orow)[hh * 4 + c] = live ? pk : make_uint4(0, 0, 0, 0);
+                    }
+                }
             }
-            if (half == 0) p.lse[(size_t)zh * N + row] = live ? (m_run + lg2_approx(l_tot)) * 0.6931471805599453f : -INFINITY;
+            if (row < N) p.lse[(size_t)zh * N + row] = live ? (m_run + lg2_approx(l_run)) * 0.6931471805599453f : -INFINITY;
         }
     }
     tc_fence_before();
