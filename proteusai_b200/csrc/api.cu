@@ -404,7 +404,9 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-        ce = cudaFuncSetAttribute(pai::geoattn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        ce = cudaFuncSetAttribute(pai::geoattn_bwd_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (ce != cudaSuccess) return (int)ce;
+        ce = cudaFuncSetAttribute(pai::geoattn_bwd_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (ce != cudaSuccess) return (int)ce;
         if (dev >= 0 && dev < 64) attr_done[dev] = true;
     }
@@ -442,7 +444,8 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.zh_begin = zh_begin;
     p.scale = scale;
     dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
-    pai::geoattn_bwd_kernel<<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+    if (p.form == 0) pai::geoattn_bwd_kernel<0><<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
+    else pai::geoattn_bwd_kernel<1><<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();
 }
 

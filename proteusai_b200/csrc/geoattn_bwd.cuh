@@ -43,7 +43,7 @@ constexpr int GA_SUB = 64;  // queries per sub-tile (two sub-tiles per 128-row q
 struct GaQueryRows {                  // per-query inputs of one query tile, two queries per entry
     float2 l2[GA_BM / 2];             // log-sum-exp in base-2 units (+inf: padded query or row without a valid pair)
     float2 dsum[GA_BM / 2];           // D_i
-    alignas(16) float qb[GA_BM];      // 0 for a valid query, -inf for a padded one
+    uint32_t qbits[GA_BM / 32];       // bit i of word u: query 32 u + i is valid
     float4 sph[GA_BM / 16];           // bounding sphere of each group of 16 queries (radius < 0: no valid query)
 };
 
@@ -121,7 +121,8 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile,
     ga_write_geo_row<false>(geo_tile, geo_block, i, x, y, z, x * x + y * y + z * z);
     reinterpret_cast<float *>(&rw.l2[i >> 1])[i & 1] = l2;
     reinterpret_cast<float *>(&rw.dsum[i >> 1])[i & 1] = dsum;
-    rw.qb[i] = ok ? 0.f : -INFINITY;
+    const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+    if ((i & 31) == 0) rw.qbits[i >> 5] = bits;
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded queries carry 0
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) {
@@ -138,50 +139,52 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile,
     if ((i & 15) == 0) rw.sph[i >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
 }
 
-// 16 query columns (8 pairs) of one key row: recompute P, form dS and the spread-gradient term.  sv / dpv hold the
-// raw S^T and dP^T values of the thread's 32 columns of this sub-tile, of which this call takes OFF .. OFF + 15; the
-// matching 16 values of G^T = |q|^2 - 2 k.q are read from tensor memory at g_taddr + OFF (|r_k - r_q|^2 = G^T + |k|^2);
-// the results come back as bf16 pairs in pw / dw [POFF .. POFF + 7].  `p0` is the index of the first of the 8 query
-// pairs inside the tile's row arrays.
-// MASKED: the key tile or the query tile holds a padded token (validity is then applied by selection, so whatever
-// the padding holds, Inf or NaN included, never reaches a result).  `far` (warp-uniform): the 16 queries are too far
-// from the warp's keys for R to count.
-// FAR: 0 = near (R evaluated), 1 = far, 2 = decided at run time by `far_rt`; with 0 or 1 the body is branch-free, so the two
-// groups of a pass form one straight-line block.
-template <bool MASKED, int FORM, int OFF, int FAR>
-__device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uint32_t (&dpv)[32], uint32_t g_taddr, bool far_rt,
-                                             const GaQueryRows &rw, int p0,
-                                             const GaBwdKey &key, f2_t crbf2, f2_t cs2, f2_t scale2, const GaForm &fm, f2_t &dsig2,
-                                             f2_t &dbeta2, uint32_t (&pw)[16], uint32_t (&dw)[16]) {
+// 16 query columns (8 pairs) of one key row: recompute P, form dS and the spread-gradient term.  sv / dpv / gv hold the
+// raw S^T, dP^T and G^T = |q|^2 - 2 k.q values of the thread's 32 columns of this sub-tile (|r_k - r_q|^2 = G^T + |k|^2),
+// of which this call takes OFF .. OFF + 15; the results come back as bf16 pairs in pw / dw [OFF/2 .. OFF/2 + 7].  `p0` is
+// the index of the first of the 8 query pairs inside the tile's row arrays.
+// `masked` (warp-uniform): the key tile or the query tile holds a padded token; `qbits`: validity of the 16 queries.
+// S^T and dP^T of a padded pair are then replaced by 0 and its P by 0, so whatever the padding holds, Inf or NaN
+// included, never reaches a result.  `far` (warp-uniform): the 16 queries are too far from the warp's keys for R to
+// count; R = 0 then goes through the same arithmetic.  One body serves every case: the loop that calls it is not
+// unrolled, which keeps the instruction footprint of the kernel small.
+template <int FORM, int OFF>
+__device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[32], uint32_t (&dpv)[32], const uint32_t (&gv)[32], bool far, bool masked,
+                                             uint32_t qbits, const GaQueryRows &rw, int p0, const GaBwdKey &key, f2_t crbf2, f2_t cs2,
+                                             f2_t scale2, const GaForm &fm, f2_t &dsig2, f2_t &dbeta2, uint32_t (&pw)[16],
+                                             uint32_t (&dw)[16]) {
     constexpr int POFF = OFF / 2;
-    const bool far = FAR == 2 ? far_rt : (FAR == 1);
     const f2_t one2 = f2_pack(1.f, 1.f);
     if (far && FORM == 1 && fm.far_masked) {  // every pair of the group is outside the RBF window: P = 0
 #pragma unroll
         for (int e = 0; e < 8; ++e) pw[POFF + e] = dw[POFF + e] = 0u;
         return;
     }
+    if (masked) {
+        const uint32_t ok_bits = key.k_ok ? qbits : 0u;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const bool ok = (ok_bits >> i) & 1u;
+            sv[OFF + i] = ok ? sv[OFF + i] : 0u;
+            dpv[OFF + i] = ok ? dpv[OFF + i] : 0u;
+        }
+    }
     f2_t arg[8], rb[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) arg[e] = rb[e] = 0ull;
     if (!far) {
-        uint32_t gw[16];
-        tmem_ld16(g_taddr + OFF, gw);
-        tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 8; ++e)  // c_rbf * d^2
-            arg[e] = f2_fma(f2_pack(__uint_as_float(gw[2 * e]), __uint_as_float(gw[2 * e + 1])), crbf2, key.ckn2);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 8; ++e) {  // c_rbf * d^2 and R
             float a0, a1;
-            f2_unpack(arg[e], a0, a1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(gv[OFF + 2 * e]), __uint_as_float(gv[OFF + 2 * e + 1])), crbf2, key.ckn2), a0, a1);
             if (FORM == 1) {
                 a0 = fminf(a0, 0.f);
                 a1 = fminf(a1, 0.f);
-                arg[e] = f2_pack(a0, a1);
             }
-            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
+            arg[e] = f2_pack(a0, a1);
+            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));
         }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) arg[e] = rb[e] = 0ull;
     }
     f2_t x[8];
 #pragma unroll
@@ -190,7 +193,7 @@ __device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uin
         const f2_t t2 = f2_mul(s_raw, cs2);
         f2_t sr;
         if (FORM == 0) {
-            sr = far ? t2 : f2_fma(t2, rb[e], t2);
+            sr = f2_fma(t2, rb[e], t2);
         } else {
             float t0, t1, r0, r1;
             f2_unpack(t2, t0, t1);
@@ -200,57 +203,37 @@ __device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uin
             sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
         }
         const float2 l = rw.l2[p0 + e];
-        x[e] = f2_sub(sr, f2_pack(l.x, l.y));
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
         float a0, a1;
-        f2_unpack(x[e], a0, a1);
-        float p0v = ex2_approx(a0), p1v = ex2_approx(a1);  // P
-        if (MASKED) {
-            const float2 b = *reinterpret_cast<const float2 *>(&rw.qb[2 * (p0 + e)]);
-            p0v = (key.k_ok && b.x == 0.f) ? p0v : 0.f;
-            p1v = (key.k_ok && b.y == 0.f) ? p1v : 0.f;
+        f2_unpack(f2_sub(sr, f2_pack(l.x, l.y)), a0, a1);
+        x[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // P
+    }
+    if (masked) {
+        const uint32_t ok_bits = key.k_ok ? qbits : 0u;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float p0v, p1v;
+            f2_unpack(x[e], p0v, p1v);
+            x[e] = f2_pack((ok_bits >> (2 * e)) & 1u ? p0v : 0.f, (ok_bits >> (2 * e + 1)) & 1u ? p1v : 0.f);
         }
-        x[e] = f2_pack(p0v, p1v);
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
         const f2_t s_raw = f2_pack(__uint_as_float(sv[OFF + 2 * e]), __uint_as_float(sv[OFF + 2 * e + 1]));
         const f2_t dp = f2_pack(__uint_as_float(dpv[OFF + 2 * e]), __uint_as_float(dpv[OFF + 2 * e + 1]));
         const float2 dd = rw.dsum[p0 + e];
-        f2_t dsr = f2_mul(x[e], f2_sub(dp, f2_pack(dd.x, dd.y)));
+        const f2_t dsr = f2_mul(x[e], f2_sub(dp, f2_pack(dd.x, dd.y)));  // P = 0 (padding, outside the window): dSR = 0
         float p0v, p1v;
         f2_unpack(x[e], p0v, p1v);
-        if (MASKED || FORM == 1) {  // P = 0 (padding, or a pair outside the window): nothing flows back, whatever dP holds
-            float g0, g1;
-            f2_unpack(dsr, g0, g1);
-            dsr = f2_pack(p0v != 0.f ? g0 : 0.f, p1v != 0.f ? g1 : 0.f);
-        }
         f2_t ds;
         if (FORM == 0) {
-            if (far) {
-                ds = f2_mul(dsr, scale2);
-            } else {
-                ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
-                f2_t w = f2_mul(f2_mul(dsr, s_raw), rb[e]);
-                if (MASKED) {  // S of a padded pair may be Inf / NaN: keep it out of the sum
-                    float w0, w1;
-                    f2_unpack(w, w0, w1);
-                    w = f2_pack(p0v != 0.f ? w0 : 0.f, p1v != 0.f ? w1 : 0.f);
-                }
-                dsig2 = f2_fma(w, arg[e], dsig2);
-            }
+            ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
+            dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
         } else {  // dS = dSR (1 + beta Rn sign(S)),  dR = dSR |S| 2 beta / (max - min),  dbeta = sum dSR Rn |S|
             float s0, s1, r0, r1, g0, g1, a0, a1;
             f2_unpack(s_raw, s0, s1);
             f2_unpack(dsr, g0, g1);
             f2_unpack(rb[e], r0, r1);
             f2_unpack(arg[e], a0, a1);
-            if (MASKED) {
-                s0 = p0v != 0.f ? s0 : 0.f;
-                s1 = p1v != 0.f ? s1 : 0.f;
-            }
             const float rn0 = fmaf(r0, fm.rn_a, fm.rn_b), rn1 = fmaf(r1, fm.rn_a, fm.rn_b);
             const float sg0 = (s0 > 0.f) ? 1.f : ((s0 < 0.f) ? -1.f : 0.f), sg1 = (s1 > 0.f) ? 1.f : ((s1 < 0.f) ? -1.f : 0.f);
             float sc0, sc1;
@@ -267,6 +250,7 @@ __device__ __forceinline__ void ga_bwd_chunk(const uint32_t (&sv)[32], const uin
     }
 }
 
+template <int FORM>
 __global__ void __launch_bounds__(GA_BWD_THREADS, 1)
 geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const GaBwdParams p) {
@@ -529,7 +513,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         const f2_t crbf2 = f2_pack(c_rbf, c_rbf), cs2 = f2_pack(c_s, c_s), scale2 = f2_pack(p.scale, p.scale);
         f2_t dsig2 = 0ull, dbeta2 = 0ull;
         GaForm fm;
-        ga_form_setup(fm, p.form, p.form == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
+        ga_form_setup(fm, FORM, FORM == 1 ? p.beta[h] : 0.f, p.min_rbf, p.max_rbf);
         GaBwdKey key;
         const float ckn = c_rbf * (kcx * kcx + kcy * kcy + kcz * kcz);
         key.ckn2 = f2_pack(ckn, ckn);
@@ -576,69 +560,53 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             }
         };
 
-        for (int t = 0; ok && t < nt; ++t) {
-            const int rbuf = t % GA_ROW_BUFS;
+#pragma unroll 1
+        for (int u = 0; ok && u < nsub; ++u) {
+            const int t = u >> 1, sub = u & 1, rbuf = t % GA_ROW_BUFS;
+            const uint32_t par = (uint32_t)(u & 1);
             const bool masked = key_hole || (tile_word(t) & 0x8000) != 0;
             const GaQueryRows &rw = sm.rows[rbuf];
             uint8_t *ds_tile = sm.ds[t & 1];
+            if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T, G^T(u) have landed in TMEM (the producer waited for the rows)
+            tc_fence_after();
+            const int col0 = sub * GA_SUB + half * 32;  // first query column (inside the tile) of this thread's 32
+            auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
+                const float4 sp = rw.sph[g];
+                const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
+                const float reach = wk_reach + sp.w;
+                return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+            };
+            const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
+            const uint32_t qbits = rw.qbits[col0 / 32];
+            uint32_t sv[32], dpv[32], gv[32];
+            tmem_ld32(tm_s + lane_base + half * 32, sv);
+            tmem_ld32(tm_dp + lane_base + half * 32, dpv);
+            if (!(far0 && far1)) tmem_ld32(tm_g + (u & 1) * GA_SUB + lane_base + half * 32, gv);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sm.bar_spfree);  // the accumulators may be overwritten with the next sub-tile's
+            uint32_t pw[16], dw[16];
+            ga_bwd_chunk<FORM, 0>(sv, dpv, gv, far0, masked, qbits & 0xffffu, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
+            ga_bwd_chunk<FORM, 16>(sv, dpv, gv, far1, masked, qbits >> 16, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
+            // P^T(u-1) is read by dV(u-1): no store before it has completed (the dS^T buffer of this tile was last read
+            // by dK / dQ two query tiles ago)
+            if (u > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
+            tmem_st16(tm_p + lane_base + half * 16, pw);
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
-                const int u = 2 * t + sub;
-                const uint32_t par = (uint32_t)(u & 1);
-                if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T, G^T(u) have landed in TMEM (the producer waited for the rows)
-                tc_fence_after();
-                uint32_t sv[32], dpv[32];
-                tmem_ld32(tm_s + lane_base + half * 32, sv);
-                tmem_ld32(tm_dp + lane_base + half * 32, dpv);
-                tmem_wait_ld();
-                tc_fence_before();
-                mbar_arrive(&sm.bar_spfree);  // the accumulators may be overwritten with the next sub-tile's
-                const int col0 = sub * GA_SUB + half * 32;  // first query column (inside the tile) of this thread's 32
-                const uint32_t g_taddr = tm_g + (u & 1) * GA_SUB + lane_base + half * 32;
-                auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
-                    const float4 sp = rw.sph[g];
-                    const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
-                    const float reach = wk_reach + sp.w;
-                    return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-                };
-                uint32_t pw[16], dw[16];
-                const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
-#define PAI_GA_BWD2(MASKED, FORM, MODE)                                                                                            \
-    do {                                                                                                                           \
-        ga_bwd_chunk<MASKED, FORM, 0, MODE>(sv, dpv, g_taddr, far0, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);   \
-        ga_bwd_chunk<MASKED, FORM, 16, MODE>(sv, dpv, g_taddr, far1, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw); \
-    } while (0)
-                if (p.form == 0) {
-                    if (!far0 && !far1) {
-                        if (masked) PAI_GA_BWD2(true, 0, 0); else PAI_GA_BWD2(false, 0, 0);
-                    } else if (far0 && far1) {
-                        if (masked) PAI_GA_BWD2(true, 0, 1); else PAI_GA_BWD2(false, 0, 1);
-                    } else {
-                        if (masked) PAI_GA_BWD2(true, 0, 2); else PAI_GA_BWD2(false, 0, 2);
-                    }
-                } else {
-                    if (masked) PAI_GA_BWD2(true, 1, 2); else PAI_GA_BWD2(false, 1, 2);
+            for (int c = 0; c < 4; ++c)  // 8 queries = one 16-byte chunk of the swizzled key row, sub-tile `sub`
+                *reinterpret_cast<uint4 *>(ds_tile + sub * GA_TILE_BYTES + sw128_offset(r, half * 4 + c)) =
+                    make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
+            tmem_wait_st();
+            fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
+            tc_fence_before();
+            mbar_arrive(&sm.bar_pds);
+            if (sub == 1) {
+                mbar_arrive(&sm.bar_rowsfree[rbuf]);  // the stager may reuse this tile's row buffer
+                if (t > 0) {  // dQ(t-1) completed long ago: read it out now, off the tensor core's critical path
+                    if (!(ok = wait_w(&sm.bar_dq, (uint32_t)((t - 1) & 1)))) break;
+                    tc_fence_after();
+                    read_dq(t - 1);
                 }
-#undef PAI_GA_BWD2
-                // P^T(u-1) is read by dV(u-1): no store before it has completed (the dS^T buffer of this tile was last read
-                // by dK / dQ two query tiles ago)
-                if (u > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
-                tmem_st16(tm_p + lane_base + half * 16, pw);
-#pragma unroll
-                for (int c = 0; c < 4; ++c)  // 8 queries = one 16-byte chunk of the swizzled key row, sub-tile `sub`
-                    *reinterpret_cast<uint4 *>(ds_tile + sub * GA_TILE_BYTES + sw128_offset(r, half * 4 + c)) =
-                        make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
-                tmem_wait_st();
-                fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
-                tc_fence_before();
-                mbar_arrive(&sm.bar_pds);
-            }
-            if (!ok) break;
-            mbar_arrive(&sm.bar_rowsfree[rbuf]);  // the stager may reuse this tile's row buffer
-            if (t > 0) {  // dQ(t-1) completed long ago: read it out now, off the tensor core's critical path
-                if (!(ok = wait_w(&sm.bar_dq, (uint32_t)((t - 1) & 1)))) break;
-                tc_fence_after();
-                read_dq(t - 1);
             }
         }
 
@@ -688,7 +656,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         const float sig = p.sigma[h];
         const float c_rbf = -1.4426950408889634f / (2.f * sig * sig);
-        if (p.form == 0) {
+        if (FORM == 0) {
             // sum of dSR * S_raw * R * (c_rbf d^2), S = scale * S_raw:  dsigma = sum dSR S R d^2 / sigma^3
             atomicAdd(p.dsigma + h, tot * p.scale / (c_rbf * sig * sig * sig));
         } else {

@@ -7,34 +7,36 @@
 // instantiation (FORM = 1).
 //
 // One CTA = 128 query rows of one (batch, head): four math warps (one thread per query row = TMEM lane, so a row
-// needs no exchange between threads), a producer warp (lane 0 issues every TMA load and MMA) and a stager warp.  Two
-// CTAs share an SM: their phases drift apart, so the SFU-heavy and FMA-heavy stretches of one overlap the waits of
-// the other, and a CTA's set-up hides behind its neighbour's work.  Keys are taken 64 at a time (a "step"; two steps
-// per 128-key tile of the batch plan).
-// Tensor memory (256 columns): S [0,64) fp32, G [64,128) fp32, O [128,192) fp32, P [192,224) bf16 pairs.
-//   S  = Q K^T : tcgen05.mma, A = Q tile, B = K step (both K-major, 128-byte swizzle, via TMA);
-//   G          : the geometry of the step comes from the tensor core as well: G_ij = |k_j|^2 - 2 q_i . k_j
+// needs no exchange between threads) and four helper warps: one thread issues the S and G MMAs, one the P V MMAs, one the
+// TMA loads of K and V, and a whole warp stages the keys' geometry.  Two CTAs share an SM.  Keys are taken 32 at a time (a "unit"; four
+// units per 128-key tile of the batch plan, two per 64-key TMA box), and every per-unit buffer in tensor memory is
+// doubled, so the tensor core works on unit w + 1 while the math warps hold unit w:
+// Tensor memory (256 columns): S 2 x [32] fp32 at 0, G 2 x [32] fp32 at 64, O [64] fp32 at 128, P 2 x [16] bf16 pairs at 192.
+//   S  = Q K^T : tcgen05.mma, A = Q tile, B = 32 rows of a K box (both K-major, 128-byte swizzle, via TMA);
+//   G          : the geometry of the unit comes from the tensor core as well: G_ij = |k_j|^2 - 2 q_i . k_j
 //                (coordinates centred on the tile's first valid query) is a product of two narrow operand tiles
 //                that the threads write themselves, each fp32 coordinate split into three bf16 terms
 //                (ga_write_geo_row), so that |r_i - r_j|^2 = G_ij + |q_i|^2 to fp32 accuracy.  Reading key
 //                coordinates from shared memory instead costs every warp a broadcast load per key pair, which
 //                made the shared-memory pipe, not the SFU, the limiter of this stage;
-//   softmax    : a math thread reads the 64 logits of its row ONCE into registers (tcgen05.ld), G group by group,
-//                and releases the columns, so the tensor core computes the next step underneath the softmax of
-//                this one.  R = 2^(c G + c |q|^2), SR = S scale (1 + R) in packed fp32x2 arithmetic.
-//                A group of 16 keys whose bounding sphere lies farther than 5.9 sigma_h from the bounding sphere
-//                of the warp's 32 queries has R < 2^-25 for every pair, where S (1 + R) == S in fp32: there
-//                the exponential is skipped (most of the off-diagonal work of the narrow heads).  P is written
-//                as bf16 straight into tensor memory;
-//   O += P V   : tcgen05.mma with the A operand (P) read from tensor memory, B = V step (MN-major: keys
-//                are the K dimension), accumulated in TMEM [128 x 64] across the steps.  The running
-//                maximum is only raised when a step exceeds it by more than 2^8 (then the accumulator and
-//                the row sum are rescaled); otherwise P is computed against the slightly stale maximum,
-//                which is exact after the final normalisation.
-// K and V are double-buffered.  The stager warp runs up to three key tiles ahead: geometry operand rows, masks and
-// bounding spheres.  Key tiles without any valid key are never loaded (list from the batch plan, geoattn_plan.cuh);
-// tiles without a padded key take a path without the mask; CTAs without any valid query only write zeros.  Every
-// wait is bounded and abortable (tc.cuh).
+//   softmax    : the loop over units is NOT unrolled and has one body for every case (far / near groups and the
+//                key mask are warp-uniform branches inside it): the whole loop is a few hundred instructions.
+//                An unrolled loop with one specialised copy per case ran 30 % slower although it executed
+//                fewer instructions, because the warps of an SM were fetching many different copies.
+//                A math thread reads the 32 logits of its row and their G into registers (tcgen05.ld), so the
+//                columns are free for unit w + 2 at once.  R = 2^(c G + c |q|^2), SR = S scale (1 + R) in packed
+//                fp32x2 arithmetic.  A group of 16 keys whose bounding sphere lies farther than 5.9 sigma_h from
+//                the bounding sphere of the warp's 32 queries has R < 2^-25 for every pair, where S (1 + R) == S
+//                in fp32: there the exponential is skipped (most of the off-diagonal work of the narrow heads).
+//                P is written as bf16 straight into tensor memory;
+//   O += P V   : tcgen05.mma with the A operand (P) read from tensor memory, B = 32 rows of a V box (MN-major:
+//                keys are the K dimension), accumulated in TMEM [128 x 64] across the units.  The running
+//                maximum is only raised when a unit exceeds it by more than 2^GA_RESCALE_THRESHOLD (then the
+//                accumulator and the row sum are rescaled); otherwise P is computed against the stale maximum,
+//                which is exact after the final normalisation (floating point keeps the relative accuracy).
+// The stager warp runs up to three key tiles ahead: geometry operand rows, mask bits and bounding spheres.  Key
+// tiles without any valid key are never loaded (list from the batch plan, geoattn_plan.cuh); CTAs without any
+// valid query only write zeros.  Every wait is bounded and abortable (tc.cuh).
 #pragma once
 #include "geoattn_plan.cuh"
 #include "tc.cuh"
@@ -43,12 +45,13 @@ namespace pai {
 
 constexpr int GA_BM = 128;  // query rows per CTA
 constexpr int GA_BN = 128;  // tokens per tile of the batch plan (and per query / key tile of the backward)
-constexpr int GA_BS = 64;   // keys per step of the forward
+constexpr int GA_BS = 64;   // keys per TMA box of the forward
+constexpr int GA_UNIT = 32; // keys per unit of the forward
 constexpr int GA_D = 64;    // head dimension
 constexpr int GA_MAX_TILES = GA_PLAN_MAX_TILES;
 constexpr int GA_FWD_MATH_THREADS = 128;
-constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 64;  // + the producer warp and the stager warp
-constexpr float GA_RESCALE_THRESHOLD = 8.f;                 // log2 units
+constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 128;  // + the S-issuer, stager, loader and PV-issuer warps
+constexpr float GA_RESCALE_THRESHOLD = 24.f;                // log2 units
 constexpr uint32_t GA_TMEM_COLS = 256;
 constexpr uint32_t GA_TILE_BYTES = GA_BN * GA_D * 2;  // 16 KiB
 constexpr uint32_t GA_STEP_BYTES = GA_BS * GA_D * 2;  // 8 KiB
@@ -58,7 +61,7 @@ constexpr float GA_FAR_SIGMAS = 5.9f;                   // exp(-d^2 / 2 sigma^2)
 constexpr int GA_GEO_K = 32;                            // bf16 columns of the geometry operands (24 used)
 
 struct GaKeyCoords {                  // per-key side data of one tile
-    alignas(16) float kb[GA_BN];      // 0 for a valid key, -inf for a padded one
+    uint32_t vbits[GA_BN / 32];       // bit i of word u: key 32 u + i is valid
     float4 sph[GA_BN / 16];           // bounding sphere of each group of 16 keys: centre, radius (< 0: no valid key)
 };
 
@@ -70,7 +73,7 @@ struct GaFwdSmem {
     // side (column blocks 0 and 1).  Slot 0: the queries; slots 1..3: the ring of staged key tiles.
     alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaKeyCoords kc[GA_KC_BUFS];
-    uint64_t bar_q, bar_k[2], bar_v[2], bar_s, bar_sfree, bar_p, bar_o, bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
+    uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_vfree[2], bar_s[2], bar_sfree[2], bar_p[2], bar_o[2], bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
     uint16_t tiles[GA_MAX_TILES];                 // key tiles with a valid key; bit 15: the tile also has a padded key
     uint32_t tmem_base;
     int abort;                                    // raised by the first wait that expires
@@ -195,12 +198,13 @@ template <typename Smem>
 __device__ __forceinline__ uint8_t *ga_geo_tile(Smem &sm, int slot) { return sm.geo[slot >> 1]; }
 __device__ __forceinline__ int ga_geo_block(int slot) { return slot & 1; }
 
-// Stages one key of a key tile: its geometry operand row, its mask entry and, with the other 15 keys of its half-warp,
+// Stages one key of a key tile: its geometry operand row, its mask bit and, with the other 15 keys of its half-warp,
 // the bounding sphere of the group of 16.  Executed by whole warps with key = (lane + 32 m): the 16 lanes of a half-warp
 // hold 16 consecutive keys.  `x, y, z` are the centred coordinates (0 for a padded key).
 __device__ __forceinline__ void ga_stage_key(GaKeyCoords &kc, uint8_t *geo_tile, int geo_block, int key, bool ok, float x, float y, float z) {
     ga_write_geo_row<false>(geo_tile, geo_block, key, x, y, z, x * x + y * y + z * z);
-    kc.kb[key] = ok ? 0.f : -INFINITY;
+    const uint32_t bits = __ballot_sync(0xffffffffu, ok);
+    if ((key & 31) == 0) kc.vbits[key >> 5] = bits;
     // bounding sphere of the 16 keys of this half-warp (valid keys only): centre = mean, radius = largest distance
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded keys carry 0
 #pragma unroll
@@ -218,71 +222,59 @@ __device__ __forceinline__ void ga_stage_key(GaKeyCoords &kc, uint8_t *geo_tile,
     if ((key & 15) == 0) kc.sph[key >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
 }
 
-// 16 logits (8 key pairs) of one row, held in registers: v[] holds raw S on entry and SR on return, g[] the matching
-// G values; returns the maximum.  SR = (S * c_s) * (1 + R) with R = 2^(c_rbf * (G + |q|^2)).
-// FAR: 0 = the group is near (R evaluated), 1 = far (R does not count), 2 = decided at run time by `far_rt`
-// (warp-uniform).  With 0 or 1 the body has no branch, so the four groups of a row form one straight-line block.
-template <bool MASKED, int FORM, int OFF, int FAR>
-__device__ __forceinline__ float ga_sr_chunk(uint32_t (&w)[32], uint32_t g_taddr, bool far_rt, const float *kb, f2_t crbf2,
-                                             f2_t cqn2, f2_t cs2, const GaForm &fm) {
-#define v(i) w[OFF + (i)]
-    const bool far = FAR == 2 ? far_rt : (FAR == 1);
+// 16 logits (8 key pairs) of one row, held in registers: s[OFF..OFF+16) holds raw S on entry and SR on return,
+// g[] the matching G values; returns the maximum.  SR = (S * c_s) * (1 + R) with R = 2^(c_rbf * (G + |q|^2)).
+// `far` (warp-uniform): the group's R does not count.
+template <int FORM, int OFF>
+__device__ __forceinline__ float ga_sr_chunk(uint32_t (&s)[32], const uint32_t (&g)[32], bool far, f2_t crbf2, f2_t cqn2, f2_t cs2,
+                                             const GaForm &fm) {
     float m_loc = -INFINITY;
-    f2_t rb[8];
     if (!far) {
-        uint32_t gw[16];  // the 16 G values of the group, straight from tensor memory
-        tmem_ld16(g_taddr + OFF, gw);
-        tmem_wait_ld();
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             float a0, a1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(gw[2 * e]), __uint_as_float(gw[2 * e + 1])), crbf2, cqn2), a0, a1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(g[OFF + 2 * e]), __uint_as_float(g[OFF + 2 * e + 1])), crbf2, cqn2), a0, a1);
             if (FORM == 1) {  // keep R <= 1 exactly (the d^2 of a coincident pair can round below zero)
                 a0 = fminf(a0, 0.f);
                 a1 = fminf(a1, 0.f);
             }
-            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // R
+            const float r0 = ex2_approx(a0), r1 = ex2_approx(a1);  // R
+            const f2_t t2 = f2_mul(f2_pack(__uint_as_float(s[OFF + 2 * e]), __uint_as_float(s[OFF + 2 * e + 1])), cs2);
+            float v0, v1;
+            if (FORM == 0) {
+                f2_unpack(f2_fma(t2, f2_pack(r0, r1), t2), v0, v1);
+            } else {
+                float t0, t1;
+                f2_unpack(t2, t0, t1);
+                const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
+                const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
+                v0 = (r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY;
+                v1 = (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY;
+            }
+            s[OFF + 2 * e] = __float_as_uint(v0);
+            s[OFF + 2 * e + 1] = __float_as_uint(v1);
+            m_loc = max3(m_loc, v0, v1);
         }
-    }
+    } else {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const f2_t t2 = f2_mul(f2_pack(__uint_as_float(v(2 * e)), __uint_as_float(v(2 * e + 1))), cs2);
-        f2_t sr;
-        if (FORM == 0) {
-            sr = far ? t2 : f2_fma(t2, rb[e], t2);
-        } else if (far && fm.far_masked) {
-            sr = f2_pack(-INFINITY, -INFINITY);
-        } else {
-            float t0, t1, r0 = 0.f, r1 = 0.f;  // a far group inside the window (min_rbf <= 0): R counts as 0
-            f2_unpack(t2, t0, t1);
-            if (!far) f2_unpack(rb[e], r0, r1);
-            const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
-            const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
-            sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
+        for (int e = 0; e < 8; ++e) {
+            const f2_t t2 = f2_mul(f2_pack(__uint_as_float(s[OFF + 2 * e]), __uint_as_float(s[OFF + 2 * e + 1])), cs2);
+            float v0, v1;
+            f2_unpack(t2, v0, v1);
+            if (FORM == 1) {
+                if (fm.far_masked) {
+                    v0 = v1 = -INFINITY;
+                } else {  // a far group inside the window (min_rbf <= 0): R counts as 0
+                    v0 = (0.f >= fm.rmin && 0.f <= fm.rmax) ? fmaf(fm.beta * fm.rn_b, fabsf(v0), v0) : -INFINITY;
+                    v1 = (0.f >= fm.rmin && 0.f <= fm.rmax) ? fmaf(fm.beta * fm.rn_b, fabsf(v1), v1) : -INFINITY;
+                }
+            }
+            s[OFF + 2 * e] = __float_as_uint(v0);
+            s[OFF + 2 * e + 1] = __float_as_uint(v1);
+            m_loc = max3(m_loc, v0, v1);
         }
-        float v0, v1;
-        f2_unpack(sr, v0, v1);
-        if (MASKED) {  // select, do not add: a padded key may hold Inf / NaN
-            const float2 b = *reinterpret_cast<const float2 *>(kb + 2 * e);
-            v0 = b.x == 0.f ? v0 : -INFINITY;
-            v1 = b.y == 0.f ? v1 : -INFINITY;
-        }
-        v(2 * e) = __float_as_uint(v0);
-        v(2 * e + 1) = __float_as_uint(v1);
-        m_loc = max3(m_loc, v0, v1);
     }
     return m_loc;
-#undef v
-}
-
-// 32 logits of one thread (two groups of 16 keys; H = which 32 of the thread's 64 = of the step's keys).  MODE 0: every
-// group of the step is near, 1: every group is far, 2: per group (`far`).  `kb`: the mask entries of the step's 64 keys.
-template <bool MASKED, int FORM, int MODE, int H>
-__device__ __forceinline__ float ga_sr_half(uint32_t (&sv)[32], uint32_t gv, const float *kb, const bool (&far)[4], f2_t crbf2, f2_t cqn2,
-                                            f2_t cs2, const GaForm &fm) {
-    const float m0 = ga_sr_chunk<MASKED, FORM, 0, MODE>(sv, gv, far[2 * H], kb + (2 * H) * 16, crbf2, cqn2, cs2, fm);
-    const float m1 = ga_sr_chunk<MASKED, FORM, 16, MODE>(sv, gv, far[2 * H + 1], kb + (2 * H + 1) * 16, crbf2, cqn2, cs2, fm);
-    return fmaxf(m0, m1);
 }
 
 template <int FORM>
@@ -324,19 +316,24 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         return;
     }
-    // steps of 64 keys: u = 2 t + sub; the second half of the sequence's last tile may lie entirely past N
-    const int nu = 2 * nt - (((tile_word_g(nt - 1) & 0x7fff) * GA_BN + GA_BS >= N) ? 1 : 0);
+    // units of 32 keys: w = 4 t + quarter; the trailing units of the sequence's last tile may lie entirely past N
+    const int last_keys = min(GA_BN, N - (tile_word_g(nt - 1) & 0x7fff) * GA_BN);
+    const int nw = 4 * (nt - 1) + (last_keys + GA_UNIT - 1) / GA_UNIT;
+    const int nbox = (nw + 1) >> 1;  // TMA boxes of 64 keys
     if (is_producer) {
         if (lane == 0) {
             mbar_init(&sm.bar_q, 1);
-            mbar_init(&sm.bar_k[0], 1);
-            mbar_init(&sm.bar_k[1], 1);
-            mbar_init(&sm.bar_v[0], 1);
-            mbar_init(&sm.bar_v[1], 1);
-            mbar_init(&sm.bar_s, 1);
-            mbar_init(&sm.bar_o, 1);
-            mbar_init(&sm.bar_sfree, GA_FWD_MATH_THREADS);
-            mbar_init(&sm.bar_p, GA_FWD_MATH_THREADS);
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&sm.bar_k[b], 1);
+                mbar_init(&sm.bar_v[b], 1);
+                mbar_init(&sm.bar_kfree[b], 1);
+                mbar_init(&sm.bar_vfree[b], 1);
+                mbar_init(&sm.bar_s[b], 1);
+                mbar_init(&sm.bar_o[b], 1);
+                mbar_init(&sm.bar_sfree[b], GA_FWD_MATH_THREADS);
+                mbar_init(&sm.bar_p[b], GA_FWD_MATH_THREADS);
+            }
 #pragma unroll
             for (int b = 0; b < GA_KC_BUFS; ++b) {
                 mbar_init(&sm.bar_kc[b], 32);
@@ -347,12 +344,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // the first loads leave before anything else is set up
             mbar_expect_tx(&sm.bar_q, GA_TILE_BYTES);
             tma_load_4d(sm.q, &map_q, 0, i0, h, z, &sm.bar_q);
-            for (int u = 0; u < 2 && u < nu; ++u) {
-                const int j0 = (tile_word_g(u >> 1) & 0x7fff) * GA_BN + (u & 1) * GA_BS;
-                mbar_expect_tx(&sm.bar_k[u], GA_STEP_BYTES);
-                tma_load_4d(sm.k[u], &map_k, 0, j0, h, z, &sm.bar_k[u]);
-                mbar_expect_tx(&sm.bar_v[u], GA_STEP_BYTES);
-                tma_load_4d(sm.v[u], &map_v, 0, j0, h, z, &sm.bar_v[u]);
+            for (int j = 0; j < 2 && j < nbox; ++j) {
+                const int j0 = (tile_word_g(j >> 1) & 0x7fff) * GA_BN + (j & 1) * GA_BS;
+                mbar_expect_tx(&sm.bar_k[j], GA_STEP_BYTES);
+                tma_load_4d(sm.k[j], &map_k, 0, j0, h, z, &sm.bar_k[j]);
+                mbar_expect_tx(&sm.bar_v[j], GA_STEP_BYTES);
+                tma_load_4d(sm.v[j], &map_v, 0, j0, h, z, &sm.bar_v[j]);
             }
             sm.abort = 0;
         }
@@ -410,15 +407,16 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     __syncthreads();  // barriers initialised, TMEM allocated, tile list and the queries' geometry operand in place
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
-    const uint32_t tmem_s = tmem;          // columns [0,64): S
-    const uint32_t tmem_g = tmem + 64;     // columns [64,128): G = |k|^2 - 2 q.k
+    const uint32_t tmem_s = tmem;          // columns [0,64): S of units w (even) and w + 1 (odd), 32 each
+    const uint32_t tmem_g = tmem + 64;     // columns [64,128): G = |k|^2 - 2 q.k, likewise
     const uint32_t tmem_o = tmem + 128;    // columns [128,192): O accumulator
-    const uint32_t tmem_p = tmem + 192;    // columns [192,224): P as bf16 pairs (A operand of P V)
+    const uint32_t tmem_p = tmem + 192;    // columns [192,224): P as bf16 pairs (A operand of P V), 16 per unit parity
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bool is_loader = warp == GA_FWD_MATH_THREADS / 32 + 2, is_pv = warp == GA_FWD_MATH_THREADS / 32 + 3;
 
     if (is_stager) {
         // ================================ stager warp ================================================
-        // Runs up to GA_KC_BUFS key tiles ahead of the math warps: geometry operand rows, masks and bounding spheres.
+        // Runs up to GA_KC_BUFS key tiles ahead of the math warps: geometry operand rows, mask bits and bounding spheres.
         for (int t = 0; t < nt; ++t) {
             const int b = t % GA_KC_BUFS;
             if (t > 0) key_load(tile_word(t) & 0x7fff, kl);
@@ -428,80 +426,23 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             key_stage(tile_word(t) & 0x7fff, b, kl);
             mbar_arrive(&sm.bar_kc[b]);
         }
-    } else if (is_producer) {
-        // ================================ producer warp ==============================================
+    } else if (is_loader) {
+        // ================================ loader warp ================================================
+        // K / V box j goes into buffer j & 1 once the MMAs that read box j - 2 have completed.
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_BS, false, false);  // Q K^T and G: both K-major, N = 64
-            constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);    // P V: V is MN-major
-            // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
-            const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
-            const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
-            const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
-            const uint64_t geo_desc[2] = {umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.geo[1]), 16, 1024)};
-            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
-            constexpr uint64_t STEP_ROWS = (uint64_t)(GA_BS * 128) >> 4;  // 64 rows of a swizzled tile, in 16-byte units
-            // S(u) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(u): 2 more over the
-            // geometry operands (the keys' rows start 64 rows into the staged tile for the second step of a tile)
-            auto issue_s = [&](int u) {
-                const int b = u & 1, t = u >> 1;
-#pragma unroll
-                for (int kk = 0; kk < GA_D / 16; ++kk)
-                    umma_ss(tmem_s, q_desc + (uint64_t)(kk * 2), k_desc[b] + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
-                const uint64_t qg = geo_slot_desc(0), kg = geo_slot_desc(1 + t % GA_KC_BUFS) + (uint64_t)(u & 1) * STEP_ROWS;
-#pragma unroll
-                for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
-                    umma_ss(tmem_g, qg + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
-                umma_commit(&sm.bar_s);
-            };
-            auto issue_pv = [&](int u) {  // 4 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
-                const int b = u & 1;
-#pragma unroll
-                for (int kk = 0; kk < GA_BS / 16; ++kk)
-                    umma_ts(tmem_o, tmem_p + kk * 8, v_desc[b] + (uint64_t)(kk * 128), IDESC_O, (u == 0 && kk == 0) ? 0u : 1u);
-                umma_commit(&sm.bar_o);
-            };
-            auto key0 = [&](int u) -> int { return (tile_word(u >> 1) & 0x7fff) * GA_BN + (u & 1) * GA_BS; };
-            auto load_k = [&](int u) {
-                const int b = u & 1;
+            bool ok = true;
+            for (int j = 2; ok && j < nbox; ++j) {
+                const int b = j & 1;
+                const uint32_t par = (uint32_t)(((j >> 1) - 1) & 1);
+                const int j0 = (tile_word(j >> 1) & 0x7fff) * GA_BN + (j & 1) * GA_BS;
+                if (!(ok = mbar_wait_abortable(&sm.bar_kfree[b], par, abort_flag))) break;
                 mbar_expect_tx(&sm.bar_k[b], GA_STEP_BYTES);
-                tma_load_4d(sm.k[b], &map_k, 0, key0(u), h, z, &sm.bar_k[b]);
-            };
-            auto load_v = [&](int u) {
-                const int b = u & 1;
+                tma_load_4d(sm.k[b], &map_k, 0, j0, h, z, &sm.bar_k[b]);
+                if (!(ok = mbar_wait_abortable(&sm.bar_vfree[b], par, abort_flag))) break;
                 mbar_expect_tx(&sm.bar_v[b], GA_STEP_BYTES);
-                tma_load_4d(sm.v[b], &map_v, 0, key0(u), h, z, &sm.bar_v[b]);
-            };
-            bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag) && mbar_wait_abortable(&sm.bar_k[0], 0, abort_flag) &&
-                      mbar_wait_abortable(&sm.bar_kc[0], 0, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                issue_s(0);
+                tma_load_4d(sm.v[b], &map_v, 0, j0, h, z, &sm.bar_v[b]);
             }
-            for (int u = 0; ok && u < nu; ++u) {
-                const uint32_t par = (uint32_t)(u & 1);
-                const int b = u & 1;
-                if (u + 1 < nu) {
-                    // every math thread holds S(u), G(u) in registers: their columns and K buffer b are free
-                    if (!(ok = mbar_wait_abortable(&sm.bar_sfree, par, abort_flag))) break;
-                    if (u + 2 < nu) load_k(u + 2);
-                    if (!(ok = mbar_wait_abortable(&sm.bar_k[b ^ 1], (uint32_t)(((u + 1) >> 1) & 1), abort_flag))) break;
-                    if (b == 1) {  // the next step opens key tile t + 1: its staged geometry operand
-                        const int t1 = (u + 1) >> 1;
-                        if (!(ok = mbar_wait_abortable(&sm.bar_kc[t1 % GA_KC_BUFS], (uint32_t)((t1 / GA_KC_BUFS) & 1), abort_flag))) break;
-                    }
-                    tc_fence_after();
-                    issue_s(u + 1);  // S, G(u+1) run underneath the softmax of step u
-                }
-                if (!(ok = mbar_wait_abortable(&sm.bar_p, par, abort_flag))) break;  // P(u) in TMEM, O rescaled if need be
-                if (!(ok = mbar_wait_abortable(&sm.bar_v[b], (uint32_t)((u >> 1) & 1), abort_flag))) break;
-                tc_fence_after();
-                issue_pv(u);
-                if (u + 2 < nu) {  // V buffer b is free once P V(u) has completed
-                    if (!(ok = mbar_wait_abortable(&sm.bar_o, par, abort_flag))) break;
-                    load_v(u + 2);
-                }
-            }
-            if (!ok) {
+            if (!ok || *abort_flag) {
                 // Gave up: the copies already issued may still be landing in this CTA's shared memory.  Wait for
                 // them (bounded) so that the CTA does not exit underneath them.
                 for (int b = 0; b < 2; ++b) {
@@ -509,6 +450,66 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     mbar_wait_bounded(&sm.bar_v[b], 0, 1u << 12);
                 }
                 mbar_wait_bounded(&sm.bar_q, 0, 1u << 12);
+            }
+        }
+        __syncwarp();
+    } else if (is_producer) {
+        // ================================ S-issuer warp ==============================================
+        // S(w), G(w) for w >= 2 leave as soon as the math threads have read unit w - 2 out of the same columns: one and
+        // a half units before they are needed.  (A single thread issuing every MMA of a unit in turn took longer per unit
+        // than the softmax of the unit, about 80 cycles an MMA, and was the pacemaker of the CTA.)
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_UNIT, false, false);  // Q K^T and G: both K-major, N = 32
+            // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
+            const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
+            const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
+            const uint64_t geo_desc[2] = {umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.geo[1]), 16, 1024)};
+            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
+            constexpr uint64_t UNIT_ROWS = (uint64_t)(GA_UNIT * 128) >> 4;  // 32 rows of a swizzled tile, in 16-byte units
+            // S(w) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(w): 2 more over the
+            // geometry operands (the keys' rows start 32 (w mod 4) rows into the staged tile)
+            auto issue_s = [&](int w) {
+                const int sb = w & 1, kb = (w >> 1) & 1, t = w >> 2;
+                const uint64_t kd = k_desc[kb] + (uint64_t)(w & 1) * UNIT_ROWS;
+#pragma unroll
+                for (int kk = 0; kk < GA_D / 16; ++kk)
+                    umma_ss(tmem_s + sb * GA_UNIT, q_desc + (uint64_t)(kk * 2), kd + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
+                const uint64_t qg = geo_slot_desc(0), kg = geo_slot_desc(1 + t % GA_KC_BUFS) + (uint64_t)(w & 3) * UNIT_ROWS;
+#pragma unroll
+                for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
+                    umma_ss(tmem_g + sb * GA_UNIT, qg + (uint64_t)(kk * 2), kg + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
+                umma_commit(&sm.bar_s[sb]);
+                if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_kfree[kb]);  // the box's last reader
+            };
+            bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag);
+            for (int w = 0; ok && w < nw; ++w) {
+                const int t = w >> 2;
+                // every math thread holds S(w-2), G(w-2) in registers: their columns are free
+                if (w >= 2 && !(ok = mbar_wait_abortable(&sm.bar_sfree[w & 1], (uint32_t)(((w - 2) >> 1) & 1), abort_flag))) break;
+                if ((w & 1) == 0 && !(ok = mbar_wait_abortable(&sm.bar_k[(w >> 1) & 1], (uint32_t)((w >> 2) & 1), abort_flag))) break;
+                if ((w & 3) == 0 && !(ok = mbar_wait_abortable(&sm.bar_kc[t % GA_KC_BUFS], (uint32_t)((t / GA_KC_BUFS) & 1), abort_flag))) break;
+                tc_fence_after();
+                issue_s(w);
+            }
+        }
+        __syncwarp();
+    } else if (is_pv) {
+        // ================================ PV-issuer warp =============================================
+        if (lane == 0) {
+            constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);      // P V: V is MN-major
+            const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
+            bool ok = true;
+            for (int w = 0; ok && w < nw; ++w) {
+                const int pb = w & 1, vb = (w >> 1) & 1;
+                if (!(ok = mbar_wait_abortable(&sm.bar_p[pb], (uint32_t)((w >> 1) & 1), abort_flag))) break;  // P(w) in TMEM, O rescaled if need be
+                if ((w & 1) == 0 && !(ok = mbar_wait_abortable(&sm.bar_v[vb], (uint32_t)((w >> 2) & 1), abort_flag))) break;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < GA_UNIT / 16; ++kk)  // 2 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
+                    umma_ts(tmem_o, tmem_p + pb * (GA_UNIT / 2) + kk * 8, v_desc[vb] + (uint64_t)(((w & 1) * 2 + kk) * 128), IDESC_O,
+                            (w == 0 && kk == 0) ? 0u : 1u);
+                umma_commit(&sm.bar_o[pb]);
+                if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_vfree[vb]);
             }
         }
         __syncwarp();
@@ -550,84 +551,55 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
         };
 
-        for (int u = 0; ok && u < nu; ++u) {
-            const uint32_t par = (uint32_t)(u & 1);
-            const int t = u >> 1, sub = u & 1, cb = t % GA_KC_BUFS;
+#pragma unroll 1
+        for (int w = 0; ok && w < nw; ++w) {
+            const int sb = w & 1, t = w >> 2, qd = w & 3, cb = t % GA_KC_BUFS;
             const bool has_hole = (tile_word(t) & 0x8000) != 0;
-            uint32_t s0[32], s1[32];
-            if (!(ok = wait_w(&sm.bar_s, par))) break;  // S(u), G(u) have landed in TMEM (the producer waited for the staged key tile)
+            if (!(ok = wait_w(&sm.bar_s[sb], (uint32_t)((w >> 1) & 1)))) break;  // S(w), G(w) have landed in TMEM
             tc_fence_after();
             const GaKeyCoords &kc = sm.kc[cb];
-            const float *kb = kc.kb + sub * GA_BS;
-            bool far[4];
-            int nfar = 0;
+            bool far[2];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {  // far test of the step's four key groups against this warp's queries (warp-uniform)
-                const float4 sp = kc.sph[sub * 4 + c];
+            for (int c = 0; c < 2; ++c) {  // far test of the unit's two key groups against this warp's queries (warp-uniform)
+                const float4 sp = kc.sph[qd * 2 + c];
                 const float dx = sp.x - wqx, dy = sp.y - wqy, dz = sp.z - wqz;
                 const float reach = wq_reach + sp.w;  // wq_reach = cut + radius of the query sphere (-inf: test off)
                 far[c] = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-                nfar += far[c] ? 1 : 0;
             }
-            // S of the row into registers, G group by group, SR in place (it stays for the P phase)
-            uint32_t gv = tmem_g + lane_base;
-            float m_a, m_b;
-#define PAI_GA_HALF(H, SV, MASKED, MODE) ga_sr_half<MASKED, FORM, MODE, H>(SV, gv, kb, far, crbf2, cqn2, cs2, fm)
-#define PAI_GA_DISPATCH(H, SV, OUT)                                                                       \
-    if (FORM == 0 && nfar == 0) {                                                                         \
-        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 0); else OUT = PAI_GA_HALF(H, SV, false, 0);         \
-    } else if (FORM == 0 && nfar == 4) {                                                                  \
-        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 1); else OUT = PAI_GA_HALF(H, SV, false, 1);         \
-    } else {                                                                                              \
-        if (has_hole) OUT = PAI_GA_HALF(H, SV, true, 2); else OUT = PAI_GA_HALF(H, SV, false, 2);         \
-    }
-            tmem_ld32(tmem_s + lane_base, s0);
-            tmem_ld32(tmem_s + lane_base + 32, s1);
+            const uint32_t vbits = kc.vbits[qd];
+            uint32_t s[32], g[32];
+            tmem_ld32(tmem_s + sb * GA_UNIT + lane_base, s);
+            if (!(far[0] && far[1])) tmem_ld32(tmem_g + sb * GA_UNIT + lane_base, g);
             tmem_wait_ld();
-            PAI_GA_DISPATCH(0, s0, m_a)
-            gv += 32;
-            PAI_GA_DISPATCH(1, s1, m_b)
-#undef PAI_GA_DISPATCH
-#undef PAI_GA_HALF
             tc_fence_before();
-            mbar_arrive(&sm.bar_sfree);  // S and G are in registers: the tensor core may overwrite them with the next step's
-            if (sub == 1 || u + 1 == nu) mbar_arrive(&sm.bar_kcfree[cb]);  // ... and the stager may reuse this key tile's buffer
-            // the row maximum of the step (finite for form 0: every listed tile holds a valid key, though a step of it may
-            // not; form 1 can mask a whole row)
-            const float m_tile = fmaxf(m_a, m_b);
+            mbar_arrive(&sm.bar_sfree[sb]);  // S and G are in registers: the tensor core may overwrite them with unit w + 2
+            if (qd == 3 || w + 1 == nw) mbar_arrive(&sm.bar_kcfree[cb]);  // the stager may reuse this key tile's buffer
+            float m_unit = fmaxf(ga_sr_chunk<FORM, 0>(s, g, far[0], crbf2, cqn2, cs2, fm), ga_sr_chunk<FORM, 16>(s, g, far[1], crbf2, cqn2, cs2, fm));
+            if (has_hole) {  // select, do not add: a padded key may hold Inf / NaN
+                m_unit = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float v = (vbits >> i) & 1u ? __uint_as_float(s[i]) : -INFINITY;
+                    s[i] = __float_as_uint(v);
+                    m_unit = fmaxf(m_unit, v);
+                }
+            }
+            // the row maximum (finite for form 0 once the row has met a valid key; form 1 can mask a whole row)
             float alpha = 1.f;
             bool raise = false;
             if (m_run == -INFINITY) {
-                m_run = m_tile;
-            } else if (m_tile > m_run + GA_RESCALE_THRESHOLD) {
+                m_run = m_unit;
+            } else if (m_unit > m_run + GA_RESCALE_THRESHOLD) {
                 raise = true;
-                alpha = ex2_approx(m_run - m_tile);
-                m_run = m_tile;
+                alpha = ex2_approx(m_run - m_unit);
+                m_run = m_unit;
             }
-            // P = 2^(SR - m), row sum, bf16 pairs
-            const float m_safe = m_run == -INFINITY ? 0.f : m_run;  // a row without any valid pair so far: P = 2^(-inf) = 0
-            const f2_t mn2 = f2_pack(m_safe, m_safe);
-            f2_t l2 = 0ull, l2b = 0ull;
-            uint32_t pw[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) {
-                float a0, a1;
-                const f2_t sr2 = e < 16 ? f2_pack(__uint_as_float(s0[2 * e]), __uint_as_float(s0[2 * e + 1]))
-                                        : f2_pack(__uint_as_float(s1[2 * e - 32]), __uint_as_float(s1[2 * e - 31]));
-                f2_unpack(f2_sub(sr2, mn2), a0, a1);
-                const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
-                if (e & 1) l2b = f2_add(l2b, f2_pack(p0, p1));
-                else l2 = f2_add(l2, f2_pack(p0, p1));
-                pw[e] = pack_bf16x2(p0, p1);
-            }
-            float l0, l1;
-            f2_unpack(f2_add(l2, l2b), l0, l1);
-            l_run = l_run * alpha + (l0 + l1);
-            if (u > 0) {  // P V(u-1) has completed: the P columns are free and the O accumulator is at rest
-                if (!(ok = wait_w(&sm.bar_o, par ^ 1))) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, raise)) {
-#pragma unroll
+            if (__any_sync(0xffffffffu, raise)) {  // rare: rescale the row sum and the accumulator
+                l_run *= alpha;
+                if (w > 0) {  // P V(w-1) must have completed: the O accumulator is at rest
+                    if (!(ok = wait_w(&sm.bar_o[(w - 1) & 1], (uint32_t)(((w - 1) >> 1) & 1)))) break;
+                    tc_fence_after();
+#pragma unroll 1
                     for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
                         tmem_ld32(tmem_o + lane_base + c * 32, v);
@@ -638,14 +610,33 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     }
                 }
             }
-            tmem_st32(tmem_p + lane_base, pw);
+            // P = 2^(SR - m), row sum, bf16 pairs
+            const float m_safe = m_run == -INFINITY ? 0.f : m_run;  // a row without any valid pair so far: P = 2^(-inf) = 0
+            const f2_t mn2 = f2_pack(m_safe, m_safe);
+            f2_t l2 = 0ull, l2b = 0ull;
+            uint32_t pw[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+                float a0, a1;
+                f2_unpack(f2_sub(f2_pack(__uint_as_float(s[2 * e]), __uint_as_float(s[2 * e + 1])), mn2), a0, a1);
+                const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+                if (e & 1) l2b = f2_add(l2b, f2_pack(p0, p1));
+                else l2 = f2_add(l2, f2_pack(p0, p1));
+                pw[e] = pack_bf16x2(p0, p1);
+            }
+            float l0, l1;
+            f2_unpack(f2_add(l2, l2b), l0, l1);
+            l_run += l0 + l1;
+            // P V(w-2), the last reader of these P columns, has long completed
+            if (w >= 2 && !(ok = wait_w(&sm.bar_o[sb], (uint32_t)(((w - 2) >> 1) & 1)))) break;
+            tmem_st16(tmem_p + sb * (GA_UNIT / 2) + lane_base, pw);
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&sm.bar_p);
+            mbar_arrive(&sm.bar_p[sb]);
         }
 
         // ---- epilogue ----------------------------------------------------------------------------------
-        if (ok) ok = wait_w(&sm.bar_o, (uint32_t)((nu - 1) & 1));
+        if (ok) ok = wait_w(&sm.bar_o[(nw - 1) & 1], (uint32_t)(((nw - 1) >> 1) & 1));  // (the units' P V complete in issue order)
         if (ok) {  // (warp-uniform: tcgen05.ld needs all 32 lanes, rows past N included; only the stores are per row)
             tc_fence_after();
             // select, do not multiply by 0: padding may hold Inf / NaN in Q, K or V
