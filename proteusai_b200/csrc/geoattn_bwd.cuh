@@ -35,8 +35,8 @@
 namespace pai {
 
 constexpr uint32_t GA_BWD_TMEM_COLS = 512;
-constexpr int GA_BWD_MATH_THREADS = 256;
-constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 64;  // + the producer warp and the stager warp
+constexpr int GA_BWD_MATH_THREADS = 512;
+constexpr int GA_BWD_THREADS = GA_BWD_MATH_THREADS + 96;  // + the two issuer warps and the stager warp
 constexpr int GA_ROW_BUFS = 3;
 constexpr int GA_SUB = 64;  // queries per sub-tile (two sub-tiles per 128-row query tile)
 
@@ -139,101 +139,89 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile,
     if ((i & 15) == 0) rw.sph[i >> 4] = make_float4(cx, cy, cz, n > 0.f ? sqrtf(d2) * 1.0001f + 1e-4f : -1.f);
 }
 
-// 16 query columns (8 pairs) of one key row: recompute P, form dS and the spread-gradient term.  sv / dpv / gv hold the
-// raw S^T, dP^T and G^T = |q|^2 - 2 k.q values of the thread's 32 columns of this sub-tile (|r_k - r_q|^2 = G^T + |k|^2),
-// of which this call takes OFF .. OFF + 15; the results come back as bf16 pairs in pw / dw [OFF/2 .. OFF/2 + 7].  `p0` is
-// the index of the first of the 8 query pairs inside the tile's row arrays.
+// The 16 query columns (8 pairs) of one key row that a thread owns in a sub-tile: recompute P, form dS and the
+// spread-gradient term.  sv / dpv / gv hold the raw S^T, dP^T and G^T = |q|^2 - 2 k.q values (|r_k - r_q|^2 = G^T + |k|^2);
+// the results come back as bf16 pairs in pw / dw.  `p0` is the index of the first of the 8 query pairs inside the
+// tile's row arrays.
 // `masked` (warp-uniform): the key tile or the query tile holds a padded token; `qbits`: validity of the 16 queries.
 // S^T and dP^T of a padded pair are then replaced by 0 and its P by 0, so whatever the padding holds, Inf or NaN
 // included, never reaches a result.  `far` (warp-uniform): the 16 queries are too far from the warp's keys for R to
-// count; R = 0 then goes through the same arithmetic.  One body serves every case: the loop that calls it is not
-// unrolled, which keeps the instruction footprint of the kernel small.
-template <int FORM, int OFF>
-__device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[32], uint32_t (&dpv)[32], const uint32_t (&gv)[32], bool far, bool masked,
+// count; R = 0 then goes through the same arithmetic.  One body serves every case, and every pair goes through the
+// whole chain in one pass so that few values are live at a time.
+template <int FORM>
+__device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)[16], const uint32_t (&gv)[16], bool far, bool masked,
                                              uint32_t qbits, const GaQueryRows &rw, int p0, const GaBwdKey &key, f2_t crbf2, f2_t cs2,
-                                             f2_t scale2, const GaForm &fm, f2_t &dsig2, f2_t &dbeta2, uint32_t (&pw)[16],
-                                             uint32_t (&dw)[16]) {
-    constexpr int POFF = OFF / 2;
+                                             f2_t scale2, const GaForm &fm, f2_t &dsig2, f2_t &dbeta2, uint32_t (&pw)[8],
+                                             uint32_t (&dw)[8]) {
     const f2_t one2 = f2_pack(1.f, 1.f);
     if (far && FORM == 1 && fm.far_masked) {  // every pair of the group is outside the RBF window: P = 0
 #pragma unroll
-        for (int e = 0; e < 8; ++e) pw[POFF + e] = dw[POFF + e] = 0u;
+        for (int e = 0; e < 8; ++e) pw[e] = dw[e] = 0u;
         return;
     }
+    const uint32_t ok_bits = masked ? (key.k_ok ? qbits : 0u) : 0xffffu;
     if (masked) {
-        const uint32_t ok_bits = key.k_ok ? qbits : 0u;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const bool ok = (ok_bits >> i) & 1u;
-            sv[OFF + i] = ok ? sv[OFF + i] : 0u;
-            dpv[OFF + i] = ok ? dpv[OFF + i] : 0u;
+            sv[i] = ok ? sv[i] : 0u;
+            dpv[i] = ok ? dpv[i] : 0u;
         }
     }
-    f2_t arg[8], rb[8];
-    if (!far) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {  // c_rbf * d^2 and R
+    for (int e = 0; e < 8; ++e) {
+        f2_t arg = 0ull, rb = 0ull;
+        if (!far) {  // c_rbf * d^2 and R
             float a0, a1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(gv[OFF + 2 * e]), __uint_as_float(gv[OFF + 2 * e + 1])), crbf2, key.ckn2), a0, a1);
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(gv[2 * e]), __uint_as_float(gv[2 * e + 1])), crbf2, key.ckn2), a0, a1);
             if (FORM == 1) {
                 a0 = fminf(a0, 0.f);
                 a1 = fminf(a1, 0.f);
             }
-            arg[e] = f2_pack(a0, a1);
-            rb[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));
+            arg = f2_pack(a0, a1);
+            rb = f2_pack(ex2_approx(a0), ex2_approx(a1));
         }
-    } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) arg[e] = rb[e] = 0ull;
-    }
-    f2_t x[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const f2_t s_raw = f2_pack(__uint_as_float(sv[OFF + 2 * e]), __uint_as_float(sv[OFF + 2 * e + 1]));
+        const f2_t s_raw = f2_pack(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1]));
         const f2_t t2 = f2_mul(s_raw, cs2);
-        f2_t sr;
+        const f2_t onep = f2_add(rb, one2);
+        const float2 l = rw.l2[p0 + e];
+        f2_t x;
         if (FORM == 0) {
-            sr = f2_fma(t2, rb[e], t2);
+            x = f2_fma(t2, onep, f2_pack(-l.x, -l.y));
         } else {
             float t0, t1, r0, r1;
             f2_unpack(t2, t0, t1);
-            f2_unpack(rb[e], r0, r1);  // 0 for a far group
+            f2_unpack(rb, r0, r1);  // 0 for a far group
             const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
             const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
-            sr = f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY);
+            x = f2_sub(f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY),
+                       f2_pack(l.x, l.y));
         }
-        const float2 l = rw.l2[p0 + e];
-        float a0, a1;
-        f2_unpack(f2_sub(sr, f2_pack(l.x, l.y)), a0, a1);
-        x[e] = f2_pack(ex2_approx(a0), ex2_approx(a1));  // P
-    }
-    if (masked) {
-        const uint32_t ok_bits = key.k_ok ? qbits : 0u;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            float p0v, p1v;
-            f2_unpack(x[e], p0v, p1v);
-            x[e] = f2_pack((ok_bits >> (2 * e)) & 1u ? p0v : 0.f, (ok_bits >> (2 * e + 1)) & 1u ? p1v : 0.f);
-        }
-    }
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-        const f2_t s_raw = f2_pack(__uint_as_float(sv[OFF + 2 * e]), __uint_as_float(sv[OFF + 2 * e + 1]));
-        const f2_t dp = f2_pack(__uint_as_float(dpv[OFF + 2 * e]), __uint_as_float(dpv[OFF + 2 * e + 1]));
-        const float2 dd = rw.dsum[p0 + e];
-        const f2_t dsr = f2_mul(x[e], f2_sub(dp, f2_pack(dd.x, dd.y)));  // P = 0 (padding, outside the window): dSR = 0
         float p0v, p1v;
-        f2_unpack(x[e], p0v, p1v);
+        {
+            float a0, a1;
+            f2_unpack(x, a0, a1);
+            p0v = ex2_approx(a0);  // P
+            p1v = ex2_approx(a1);
+        }
+        if (masked) {
+            p0v = (ok_bits >> (2 * e)) & 1u ? p0v : 0.f;
+            p1v = (ok_bits >> (2 * e + 1)) & 1u ? p1v : 0.f;
+        }
+        const f2_t pp = f2_pack(p0v, p1v);
+        const f2_t dp = f2_pack(__uint_as_float(dpv[2 * e]), __uint_as_float(dpv[2 * e + 1]));
+        const float2 dd = rw.dsum[p0 + e];
+        const f2_t dsr = f2_mul(pp, f2_sub(dp, f2_pack(dd.x, dd.y)));  // P = 0 (padding, outside the window): dSR = 0
         f2_t ds;
         if (FORM == 0) {
-            ds = f2_mul(f2_mul(dsr, scale2), f2_add(rb[e], one2));
-            dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb[e]), arg[e], dsig2);
+            ds = f2_mul(f2_mul(dsr, scale2), onep);
+            dsig2 = f2_fma(f2_mul(f2_mul(dsr, s_raw), rb), arg, dsig2);
         } else {  // dS = dSR (1 + beta Rn sign(S)),  dR = dSR |S| 2 beta / (max - min),  dbeta = sum dSR Rn |S|
             float s0, s1, r0, r1, g0, g1, a0, a1;
             f2_unpack(s_raw, s0, s1);
             f2_unpack(dsr, g0, g1);
-            f2_unpack(rb[e], r0, r1);
-            f2_unpack(arg[e], a0, a1);
+            f2_unpack(rb, r0, r1);
+            f2_unpack(arg, a0, a1);
             const float rn0 = fmaf(r0, fm.rn_a, fm.rn_b), rn1 = fmaf(r1, fm.rn_a, fm.rn_b);
             const float sg0 = (s0 > 0.f) ? 1.f : ((s0 < 0.f) ? -1.f : 0.f), sg1 = (s1 > 0.f) ? 1.f : ((s1 < 0.f) ? -1.f : 0.f);
             float sc0, sc1;
@@ -245,8 +233,8 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[32], uint32_t (&dpv)
         }
         float d0, d1;
         f2_unpack(ds, d0, d1);
-        pw[POFF + e] = pack_bf16x2(p0v, p1v);
-        dw[POFF + e] = pack_bf16x2(d0, d1);
+        pw[e] = pack_bf16x2(p0v, p1v);
+        dw[e] = pack_bf16x2(d0, d1);
     }
 }
 
@@ -259,7 +247,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
     const bool is_producer = warp == GA_BWD_MATH_THREADS / 32, is_stager = warp == GA_BWD_MATH_THREADS / 32 + 1;
-    const int half = (warp >> 2) & 1;             // which 32 query columns of a sub-tile / which 32 output columns
+    const bool is_grad_issuer = warp == GA_BWD_MATH_THREADS / 32 + 2;
+    const int grp = (warp >> 2) & 3;              // which 16 query columns of a sub-tile / which 16 output columns
     const int r = (warp & 3) * 32 + lane;         // key row inside the tile = TMEM lane
     const int N = p.N;
     const int tiles_all = (N + GA_BM - 1) / GA_BM;
@@ -275,7 +264,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint8_t *vz = p.valid ? p.valid + (size_t)z * N : nullptr;
 
     // ---- this CTA's keys, the live query tiles of the range ------------------------------------------
-    const int jrow = j0 + r;  // the key whose dK / dV row this thread writes (32 of its 64 columns)
+    const int jrow = j0 + r;  // the key whose dK / dV row this thread writes (16 of its 64 columns)
     const bool k_ok = is_math && jrow < N && (vz ? vz[jrow] != 0 : true);
     const int k_info = p.plan ? ga_plan_info(p.plan, p.Z, N, z)[j0 / GA_BN] : ga_plan_info_unmasked(N, j0 / GA_BN);
     const int *tl = p.plan ? ga_plan_tiles(p.plan, p.Z, N, z) : nullptr;
@@ -285,12 +274,12 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     int first = 0, nt = 0;
     while (first < nt_all && (word_g(first) & 0x7fff) < p.qt_begin) ++first;
     while (first + nt < nt_all && (word_g(first + nt) & 0x7fff) < p.qt_end) ++nt;
-    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + half * 32;
-    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + half * 32;
+    float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + grp * 16;
+    float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + grp * 16;
     if (k_info < 0 || nt == 0) {  // no valid key here, or no query to hear from: zeros
         if (is_math && jrow < N) {
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {
                 reinterpret_cast<float4 *>(dk_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
                 reinterpret_cast<float4 *>(dv_row)[c] = make_float4(0.f, 0.f, 0.f, 0.f);
             }
@@ -378,7 +367,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         kcy = cz[jrow * 3 + 1] - ory;
         kcz = cz[jrow * 3 + 2] - orz;
     }
-    if (tid < GA_BN) {  // (tid < 128: r == tid, half == 0)
+    if (tid < GA_BN) {  // (tid < 128: r == tid, grp == 0)
         ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), tid, -2.f * kcx, -2.f * kcy, -2.f * kcz, 1.f);
         fence_proxy_async();
     }
@@ -405,8 +394,13 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             row_stage(tile_word(t) & 0x7fff, b, rl);
             mbar_arrive(&sm.bar_rows[b]);
         }
-    } else if (is_producer) {
-        // ================================ producer warp ==============================================
+    } else if (is_producer || is_grad_issuer) {
+        // ================================ issuer warps ===============================================
+        // Two threads issue the MMAs: an MMA instruction holds its issuing thread until the tensor core has taken it
+        // (about 55 cycles each in a stream, 400 to 500 cycles until the first of a batch completes), so one thread
+        // issuing all 22 MMAs of a sub-tile in turn, with its waits in between, was busy for longer than the math warps
+        // need for the sub-tile.  The first thread issues S^T, dP^T, G^T of the next sub-tile, the second dV, dK, dQ of
+        // this one and the TMA loads of Q / dO.
         if (lane == 0) {
             const uint32_t k_addr = smem_u32(sm.k), v_addr = smem_u32(sm.v);
             constexpr uint32_t IDESC_SP = umma_idesc_bf16(128, GA_SUB, false, false);  // S^T, dP^T, G^T of a sub-tile: [128 x 64]
@@ -415,69 +409,39 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
             const uint64_t k_km = umma_desc_sw128(k_addr, 16, 1024), v_km = umma_desc_sw128(v_addr, 16, 1024);  // K-major operands
             const uint64_t k_mn = umma_desc_sw128(k_addr, 0, 1024);                                              // B of dQ
-            uint64_t q_km[2], do_km[2], q_mn[2], do_mn[2], ds_km[2], ds_mn[2], geo_desc[2];
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                q_km[b] = umma_desc_sw128(smem_u32(sm.q[b]), 16, 1024);
-                do_km[b] = umma_desc_sw128(smem_u32(sm.dout[b]), 16, 1024);
-                q_mn[b] = umma_desc_sw128(smem_u32(sm.q[b]), 0, 1024);
-                do_mn[b] = umma_desc_sw128(smem_u32(sm.dout[b]), 0, 1024);
-                ds_km[b] = umma_desc_sw128(smem_u32(sm.ds[b]), 16, 1024);
-                ds_mn[b] = umma_desc_sw128(smem_u32(sm.ds[b]), GA_TILE_BYTES, 1024);
-                geo_desc[b] = umma_desc_sw128(smem_u32(sm.geo[b]), 16, 1024);
-            }
-            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
+            constexpr uint64_t BUF = (uint64_t)GA_TILE_BYTES >> 4;  // the second buffer of a pair follows the first
+            const uint64_t q_km = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024), do_km = umma_desc_sw128(smem_u32(sm.dout[0]), 16, 1024);
+            const uint64_t q_mn = umma_desc_sw128(smem_u32(sm.q[0]), 0, 1024), do_mn = umma_desc_sw128(smem_u32(sm.dout[0]), 0, 1024);
+            const uint64_t ds_km = umma_desc_sw128(smem_u32(sm.ds[0]), 16, 1024), ds_mn = umma_desc_sw128(smem_u32(sm.ds[0]), GA_TILE_BYTES, 1024);
+            const uint64_t geo0 = umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024);
+            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo0 + (uint64_t)(slot >> 1) * BUF + (uint64_t)(ga_geo_block(slot) * 4); };
             constexpr uint64_t SUB_ROWS = (uint64_t)(GA_SUB * 128) >> 4;  // 64 rows of a swizzled tile, in 16-byte units
-            auto load_qdo = [&](int t) {
-                const int b = t & 1;
-                const int i0 = (tile_word(t) & 0x7fff) * GA_BM;
-                mbar_expect_tx(&sm.bar_qdo[b], 2 * GA_TILE_BYTES);
-                tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
-                tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
-            };
-            // Sub-tile u = 2 t + s (queries 64 s .. 64 s + 63 of tile t): S^T = K Q^T and dP^T = V dO^T, 4 + 4 MMAs of K = 16
-            // over d = 64; G^T over the geometry operands, 2 MMAs.  B operands start 64 rows into their tiles for s = 1.
-            auto issue_sdg = [&](int u) {
-                const int t = u >> 1, sub = u & 1, b = t & 1;
-                const uint64_t qd = q_km[b] + sub * SUB_ROWS, dd = do_km[b] + sub * SUB_ROWS;
+            if (is_producer) {
+                // Sub-tile u = 2 t + s (queries 64 s .. 64 s + 63 of tile t): S^T = K Q^T and dP^T = V dO^T, 4 + 4 MMAs of K = 16
+                // over d = 64; G^T over the geometry operands, 2 MMAs.  B operands start 64 rows into their tiles for s = 1.
+                auto issue_sdg = [&](int u) {
+                    const int t = u >> 1, sub = u & 1, b = t & 1;
+                    const uint64_t qd = q_km + b * BUF + sub * SUB_ROWS, dd = do_km + b * BUF + sub * SUB_ROWS;
 #pragma unroll
-                for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_s, k_km + (uint64_t)(kk * 2), qd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_s, k_km + (uint64_t)(kk * 2), qd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
 #pragma unroll
-                for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), dd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
-                const uint64_t kg = geo_slot_desc(0), qg = geo_slot_desc(1 + t % GA_ROW_BUFS) + sub * SUB_ROWS;
+                    for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), dd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                    const uint64_t kg = geo_slot_desc(0), qg = geo_slot_desc(1 + t % GA_ROW_BUFS) + sub * SUB_ROWS;
 #pragma unroll
-                for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
-                    umma_ss(tm_g + (u & 1) * GA_SUB, kg + (uint64_t)(kk * 2), qg + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
-                umma_commit(&sm.bar_sp);
-            };
-            auto issue_dv_dk = [&](int u) {  // K = 16 queries per step, 4 steps per sub-tile
-                const int t = u >> 1, sub = u & 1, b = t & 1;
-#pragma unroll
-                for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
-                    umma_ts(tm_dv, tm_p + kk * 8, do_mn[b] + sub * SUB_ROWS + (uint64_t)(kk * 128), IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
-#pragma unroll
-                for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dK += dS^T Q: the sub-tile of dS^T, 32 B per step inside the swizzled row
-                    umma_ss(tm_dk, ds_km[b] + (uint64_t)(sub * (GA_TILE_BYTES >> 4) + kk * 2), q_mn[b] + sub * SUB_ROWS + (uint64_t)(kk * 128),
-                            IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
-                umma_commit(&sm.bar_vk);
-            };
-            auto issue_dq = [&](int b) {  // dQ = dS K: K = 16 keys per step, 2 KiB down the dS^T tile (M = queries: two sub-tiles)
-#pragma unroll
-                for (int kk = 0; kk < GA_BN / 16; ++kk)
-                    umma_ss(tm_dq, ds_mn[b] + (uint64_t)(kk * 128), k_mn + (uint64_t)(kk * 128), IDESC_NN, kk > 0 ? 1u : 0u);
-                umma_commit(&sm.bar_dq);
-            };
-            bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag) &&
-                      mbar_wait_abortable(&sm.bar_rows[0], 0, abort_flag);
-            if (ok) {
-                tc_fence_after();
-                issue_sdg(0);
-            }
-            for (int u = 0; ok && u < nsub; ++u) {
-                const int t = u >> 1, sub = u & 1, b = t & 1;
-                const uint32_t par = (uint32_t)(u & 1);
-                if (u + 1 < nsub) {  // every math thread holds its S^T, dP^T(u) in registers: compute the next sub-tile's
-                    if (!(ok = mbar_wait_abortable(&sm.bar_spfree, par, abort_flag))) break;
+                    for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
+                        umma_ss(tm_g + (u & 1) * GA_SUB, kg + (uint64_t)(kk * 2), qg + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                    umma_commit(&sm.bar_sp);
+                };
+                bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag) &&
+                          mbar_wait_abortable(&sm.bar_rows[0], 0, abort_flag);
+                if (ok) {
+                    tc_fence_after();
+                    issue_sdg(0);
+                }
+                for (int u = 0; ok && u + 1 < nsub; ++u) {
+                    const int t = u >> 1, sub = u & 1, b = t & 1;
+                    // every math thread holds its S^T, dP^T(u) in registers: compute the next sub-tile's
+                    if (!(ok = mbar_wait_abortable(&sm.bar_spfree, (uint32_t)(u & 1), abort_flag))) break;
                     if (sub == 1) {  // the next sub-tile opens query tile t + 1
                         if (!(ok = mbar_wait_abortable(&sm.bar_qdo[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
                         if (!(ok = mbar_wait_abortable(&sm.bar_rows[(t + 1) % GA_ROW_BUFS], (uint32_t)(((t + 1) / GA_ROW_BUFS) & 1), abort_flag))) break;
@@ -485,23 +449,54 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                     tc_fence_after();
                     issue_sdg(u + 1);  // (its G^T buffer was last read for sub-tile u - 1, which has handed over P^T and dS^T)
                 }
-                if (!(ok = mbar_wait_abortable(&sm.bar_pds, par, abort_flag))) break;  // P^T(u) in TMEM, dS^T(u) in shared memory
-                tc_fence_after();
-                issue_dv_dk(u);
-                if (sub == 1) {
-                    if (t > 0 && !(ok = mbar_wait_abortable(&sm.bar_dqr, (uint32_t)((t - 1) & 1), abort_flag))) break;  // dQ(t-1) read out
+            } else {
+                auto load_qdo = [&](int t) {
+                    const int b = t & 1;
+                    const int i0 = (tile_word(t) & 0x7fff) * GA_BM;
+                    mbar_expect_tx(&sm.bar_qdo[b], 2 * GA_TILE_BYTES);
+                    tma_load_3d(sm.q[b], &map_q, 0, i0, zh_local, &sm.bar_qdo[b]);
+                    tma_load_3d(sm.dout[b], &map_do, 0, i0, zh_local, &sm.bar_qdo[b]);
+                };
+                auto issue_dv_dk = [&](int u) {  // K = 16 queries per step, 4 steps per sub-tile
+                    const int t = u >> 1, sub = u & 1, b = t & 1;
+#pragma unroll
+                    for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dV += P^T dO: P^T advances 8 TMEM columns, dO 2 KiB (16 rows)
+                        umma_ts(tm_dv, tm_p + kk * 8, do_mn + b * BUF + sub * SUB_ROWS + (uint64_t)(kk * 128), IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
+#pragma unroll
+                    for (int kk = 0; kk < GA_SUB / 16; ++kk)  // dK += dS^T Q: the sub-tile of dS^T, 32 B per step inside the swizzled row
+                        umma_ss(tm_dk, ds_km + b * 2 * BUF + (uint64_t)(sub * (GA_TILE_BYTES >> 4) + kk * 2),
+                                q_mn + b * BUF + sub * SUB_ROWS + (uint64_t)(kk * 128), IDESC_KN, (u == 0 && kk == 0) ? 0u : 1u);
+                    umma_commit(&sm.bar_vk);
+                };
+                auto issue_dq = [&](int b) {  // dQ = dS K: K = 16 keys per step, 2 KiB down the dS^T tile (M = queries: two sub-tiles)
+#pragma unroll
+                    for (int kk = 0; kk < GA_BN / 16; ++kk)
+                        umma_ss(tm_dq, ds_mn + b * 2 * BUF + (uint64_t)(kk * 128), k_mn + (uint64_t)(kk * 128), IDESC_NN, kk > 0 ? 1u : 0u);
+                    umma_commit(&sm.bar_dq);
+                };
+                bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag);
+                for (int u = 0; ok && u < nsub; ++u) {
+                    const int t = u >> 1, sub = u & 1, b = t & 1;
+                    const uint32_t par = (uint32_t)(u & 1);
+                    if (!(ok = mbar_wait_abortable(&sm.bar_pds, par, abort_flag))) break;  // P^T(u) in TMEM, dS^T(u) in shared memory
+                    if (sub == 0 && !(ok = mbar_wait_abortable(&sm.bar_qdo[b], (uint32_t)((t >> 1) & 1), abort_flag))) break;  // (long landed)
                     tc_fence_after();
-                    issue_dq(b);
-                    if (t + 2 < nt) {  // Q / dO buffer b is free once the sub-tile MMAs of tile t are done
-                        if (!(ok = mbar_wait_abortable(&sm.bar_vk, par, abort_flag))) break;
-                        load_qdo(t + 2);
+                    issue_dv_dk(u);
+                    if (sub == 1) {
+                        if (t > 0 && !(ok = mbar_wait_abortable(&sm.bar_dqr, (uint32_t)((t - 1) & 1), abort_flag))) break;  // dQ(t-1) read out
+                        tc_fence_after();
+                        issue_dq(b);
+                        if (t + 2 < nt) {  // Q / dO buffer b is free once the sub-tile MMAs of tile t are done
+                            if (!(ok = mbar_wait_abortable(&sm.bar_vk, par, abort_flag))) break;
+                            load_qdo(t + 2);
+                        }
                     }
                 }
-            }
-            if (!ok) {  // gave up: let the copies already issued land before the CTA exits (bounded)
-                mbar_wait_bounded(&sm.bar_kv, 0, 1u << 12);
-                mbar_wait_bounded(&sm.bar_qdo[0], 0, 1u << 12);
-                mbar_wait_bounded(&sm.bar_qdo[1], 0, 1u << 12);
+                if (!ok || *abort_flag) {  // gave up: let the copies already issued land before the CTA exits (bounded)
+                    mbar_wait_bounded(&sm.bar_kv, 0, 1u << 12);
+                    mbar_wait_bounded(&sm.bar_qdo[0], 0, 1u << 12);
+                    mbar_wait_bounded(&sm.bar_qdo[1], 0, 1u << 12);
+                }
             }
         }
         __syncwarp();
@@ -545,16 +540,16 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
         };
         auto read_dq = [&](int t) {  // dQ tile of query tile t: TMEM -> registers -> vector reductions into the global fp32 dQ
-            uint32_t v[32];
-            tmem_ld32(tm_dq + lane_base + half * 32, v);
+            uint32_t v[16];
+            tmem_ld16(tm_dq + lane_base + grp * 16, v);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&sm.bar_dqr);
             const int row = (tile_word(t) & 0x7fff) * GA_BM + r;
             if (row < N) {
-                float *dst = p.dq + ((size_t)zh * N + row) * GA_D + half * 32;
+                float *dst = p.dq + ((size_t)zh * N + row) * GA_D + grp * 16;
 #pragma unroll
-                for (int e = 0; e < 32; e += 4)
+                for (int e = 0; e < 16; e += 4)
                     red_add_v4(dst + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
                                __uint_as_float(v[e + 3]));
             }
@@ -569,32 +564,31 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             uint8_t *ds_tile = sm.ds[t & 1];
             if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T, G^T(u) have landed in TMEM (the producer waited for the rows)
             tc_fence_after();
-            const int col0 = sub * GA_SUB + half * 32;  // first query column (inside the tile) of this thread's 32
-            auto far_of = [&](int g) -> bool {  // group g (16 queries) of the tile against this warp's keys
-                const float4 sp = rw.sph[g];
+            const int col0 = sub * GA_SUB + grp * 16;  // first query column (inside the tile) of this thread's 16
+            bool far;
+            {  // the thread's group of 16 queries against this warp's keys
+                const float4 sp = rw.sph[col0 / 16];
                 const float dx = sp.x - wkx, dy = sp.y - wky, dz = sp.z - wkz;
                 const float reach = wk_reach + sp.w;
-                return sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
-            };
-            const bool far0 = far_of(col0 / 16), far1 = far_of(col0 / 16 + 1);
-            const uint32_t qbits = rw.qbits[col0 / 32];
-            uint32_t sv[32], dpv[32], gv[32];
-            tmem_ld32(tm_s + lane_base + half * 32, sv);
-            tmem_ld32(tm_dp + lane_base + half * 32, dpv);
-            if (!(far0 && far1)) tmem_ld32(tm_g + (u & 1) * GA_SUB + lane_base + half * 32, gv);
+                far = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
+            }
+            const uint32_t qbits = (rw.qbits[col0 / 32] >> (col0 & 16)) & 0xffffu;
+            uint32_t sv[16], dpv[16], gv[16];
+            tmem_ld16(tm_s + lane_base + grp * 16, sv);
+            tmem_ld16(tm_dp + lane_base + grp * 16, dpv);
+            if (!far) tmem_ld16(tm_g + (u & 1) * GA_SUB + lane_base + grp * 16, gv);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&sm.bar_spfree);  // the accumulators may be overwritten with the next sub-tile's
-            uint32_t pw[16], dw[16];
-            ga_bwd_chunk<FORM, 0>(sv, dpv, gv, far0, masked, qbits & 0xffffu, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
-            ga_bwd_chunk<FORM, 16>(sv, dpv, gv, far1, masked, qbits >> 16, rw, col0 / 2 + 8, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
+            uint32_t pw[8], dw[8];
+            ga_bwd_chunk<FORM>(sv, dpv, gv, far, masked, qbits, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
             // P^T(u-1) is read by dV(u-1): no store before it has completed (the dS^T buffer of this tile was last read
             // by dK / dQ two query tiles ago)
             if (u > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
-            tmem_st16(tm_p + lane_base + half * 16, pw);
+            tmem_st8(tm_p + lane_base + grp * 8, pw);
 #pragma unroll
-            for (int c = 0; c < 4; ++c)  // 8 queries = one 16-byte chunk of the swizzled key row, sub-tile `sub`
-                *reinterpret_cast<uint4 *>(ds_tile + sub * GA_TILE_BYTES + sw128_offset(r, half * 4 + c)) =
+            for (int c = 0; c < 2; ++c)  // 8 queries = one 16-byte chunk of the swizzled key row, sub-tile `sub`
+                *reinterpret_cast<uint4 *>(ds_tile + sub * GA_TILE_BYTES + sw128_offset(r, grp * 2 + c)) =
                     make_uint4(dw[4 * c], dw[4 * c + 1], dw[4 * c + 2], dw[4 * c + 3]);
             tmem_wait_st();
             fence_proxy_async();  // dS^T (generic-proxy stores) must be visible to the tensor core
@@ -619,13 +613,13 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         if (ok) {
             tc_fence_after();
-            uint32_t a[32], b[32];
-            tmem_ld32(tm_dv + lane_base + half * 32, a);
-            tmem_ld32(tm_dk + lane_base + half * 32, b);
+            uint32_t a[16], b[16];
+            tmem_ld16(tm_dv + lane_base + grp * 16, a);
+            tmem_ld16(tm_dk + lane_base + grp * 16, b);
             tmem_wait_ld();
             if (jrow < N) {
 #pragma unroll
-                for (int e = 0; e < 32; e += 4) {
+                for (int e = 0; e < 16; e += 4) {
                     // a padded key row holds exact zeros (its P and dS were selected to 0)
                     *reinterpret_cast<uint4 *>(dv_row + e) = make_uint4(a[e], a[e + 1], a[e + 2], a[e + 3]);
                     *reinterpret_cast<uint4 *>(dk_row + e) = make_uint4(b[e], b[e + 1], b[e + 2], b[e + 3]);

@@ -413,6 +413,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const uint32_t tmem_p = tmem + 192;    // columns [192,224): P as bf16 pairs (A operand of P V), 16 per unit parity
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const bool is_loader = warp == GA_FWD_MATH_THREADS / 32 + 2, is_pv = warp == GA_FWD_MATH_THREADS / 32 + 3;
+    // Every warp waits as a whole and keeps `ok` uniform: tcgen05.ld / st and the votes need all 32 lanes, and a helper
+    // warp whose lanes 1..31 sit at a reconvergence point while lane 0 loops runs several times slower than a
+    // converged warp in which lane 0 alone issues the copy or MMA.
+    auto wait_w = [&](uint64_t *bar, uint32_t parity) -> bool {
+        return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
+    };
 
     if (is_stager) {
         // ================================ stager warp ================================================
@@ -421,36 +427,37 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const int b = t % GA_KC_BUFS;
             if (t > 0) key_load(tile_word(t) & 0x7fff, kl);
             // buffer b was last used by tile t - GA_KC_BUFS: every math thread has left it (and its G MMAs have completed)
-            if (t >= GA_KC_BUFS && !__all_sync(0xffffffffu, mbar_wait_abortable(&sm.bar_kcfree[b], (uint32_t)((t / GA_KC_BUFS - 1) & 1), abort_flag) ? 1 : 0))
-                break;  // (decided by the whole warp: the staging below shuffles across all 32 lanes)
+            if (t >= GA_KC_BUFS && !wait_w(&sm.bar_kcfree[b], (uint32_t)((t / GA_KC_BUFS - 1) & 1))) break;
             key_stage(tile_word(t) & 0x7fff, b, kl);
             mbar_arrive(&sm.bar_kc[b]);
         }
     } else if (is_loader) {
         // ================================ loader warp ================================================
         // K / V box j goes into buffer j & 1 once the MMAs that read box j - 2 have completed.
-        if (lane == 0) {
-            bool ok = true;
-            for (int j = 2; ok && j < nbox; ++j) {
-                const int b = j & 1;
-                const uint32_t par = (uint32_t)(((j >> 1) - 1) & 1);
-                const int j0 = (tile_word(j >> 1) & 0x7fff) * GA_BN + (j & 1) * GA_BS;
-                if (!(ok = mbar_wait_abortable(&sm.bar_kfree[b], par, abort_flag))) break;
+        bool ok = true;
+        for (int j = 2; ok && j < nbox; ++j) {
+            const int b = j & 1;
+            const uint32_t par = (uint32_t)(((j >> 1) - 1) & 1);
+            const int j0 = (tile_word(j >> 1) & 0x7fff) * GA_BN + (j & 1) * GA_BS;
+            if (!(ok = wait_w(&sm.bar_kfree[b], par))) break;
+            if (lane == 0) {
                 mbar_expect_tx(&sm.bar_k[b], GA_STEP_BYTES);
                 tma_load_4d(sm.k[b], &map_k, 0, j0, h, z, &sm.bar_k[b]);
-                if (!(ok = mbar_wait_abortable(&sm.bar_vfree[b], par, abort_flag))) break;
+            }
+            if (!(ok = wait_w(&sm.bar_vfree[b], par))) break;
+            if (lane == 0) {
                 mbar_expect_tx(&sm.bar_v[b], GA_STEP_BYTES);
                 tma_load_4d(sm.v[b], &map_v, 0, j0, h, z, &sm.bar_v[b]);
             }
-            if (!ok || *abort_flag) {
-                // Gave up: the copies already issued may still be landing in this CTA's shared memory.  Wait for
-                // them (bounded) so that the CTA does not exit underneath them.
-                for (int b = 0; b < 2; ++b) {
-                    mbar_wait_bounded(&sm.bar_k[b], 0, 1u << 12);
-                    mbar_wait_bounded(&sm.bar_v[b], 0, 1u << 12);
-                }
-                mbar_wait_bounded(&sm.bar_q, 0, 1u << 12);
+        }
+        if (lane == 0 && (!ok || *abort_flag)) {
+            // Gave up: the copies already issued may still be landing in this CTA's shared memory.  Wait for
+            // them (bounded) so that the CTA does not exit underneath them.
+            for (int b = 0; b < 2; ++b) {
+                mbar_wait_bounded(&sm.bar_k[b], 0, 1u << 12);
+                mbar_wait_bounded(&sm.bar_v[b], 0, 1u << 12);
             }
+            mbar_wait_bounded(&sm.bar_q, 0, 1u << 12);
         }
         __syncwarp();
     } else if (is_producer) {
@@ -458,7 +465,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // S(w), G(w) for w >= 2 leave as soon as the math threads have read unit w - 2 out of the same columns: one and
         // a half units before they are needed.  (A single thread issuing every MMA of a unit in turn took longer per unit
         // than the softmax of the unit, about 80 cycles an MMA, and was the pacemaker of the CTA.)
-        if (lane == 0) {
+        {
             constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_UNIT, false, false);  // Q K^T and G: both K-major, N = 32
             // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
             const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
@@ -481,35 +488,39 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 umma_commit(&sm.bar_s[sb]);
                 if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_kfree[kb]);  // the box's last reader
             };
-            bool ok = mbar_wait_abortable(&sm.bar_q, 0, abort_flag);
+            bool ok = wait_w(&sm.bar_q, 0);
             for (int w = 0; ok && w < nw; ++w) {
                 const int t = w >> 2;
                 // every math thread holds S(w-2), G(w-2) in registers: their columns are free
-                if (w >= 2 && !(ok = mbar_wait_abortable(&sm.bar_sfree[w & 1], (uint32_t)(((w - 2) >> 1) & 1), abort_flag))) break;
-                if ((w & 1) == 0 && !(ok = mbar_wait_abortable(&sm.bar_k[(w >> 1) & 1], (uint32_t)((w >> 2) & 1), abort_flag))) break;
-                if ((w & 3) == 0 && !(ok = mbar_wait_abortable(&sm.bar_kc[t % GA_KC_BUFS], (uint32_t)((t / GA_KC_BUFS) & 1), abort_flag))) break;
+                if (w >= 2 && !(ok = wait_w(&sm.bar_sfree[w & 1], (uint32_t)(((w - 2) >> 1) & 1)))) break;
+                if ((w & 1) == 0 && !(ok = wait_w(&sm.bar_k[(w >> 1) & 1], (uint32_t)((w >> 2) & 1)))) break;
+                if ((w & 3) == 0 && !(ok = wait_w(&sm.bar_kc[t % GA_KC_BUFS], (uint32_t)((t / GA_KC_BUFS) & 1)))) break;
                 tc_fence_after();
-                issue_s(w);
+                if (lane == 0) issue_s(w);
+                __syncwarp();
             }
         }
         __syncwarp();
     } else if (is_pv) {
         // ================================ PV-issuer warp =============================================
-        if (lane == 0) {
+        {
             constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);      // P V: V is MN-major
             const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
             bool ok = true;
             for (int w = 0; ok && w < nw; ++w) {
                 const int pb = w & 1, vb = (w >> 1) & 1;
-                if (!(ok = mbar_wait_abortable(&sm.bar_p[pb], (uint32_t)((w >> 1) & 1), abort_flag))) break;  // P(w) in TMEM, O rescaled if need be
-                if ((w & 1) == 0 && !(ok = mbar_wait_abortable(&sm.bar_v[vb], (uint32_t)((w >> 2) & 1), abort_flag))) break;
+                if (!(ok = wait_w(&sm.bar_p[pb], (uint32_t)((w >> 1) & 1)))) break;  // P(w) in TMEM, O rescaled if need be
+                if ((w & 1) == 0 && !(ok = wait_w(&sm.bar_v[vb], (uint32_t)((w >> 2) & 1)))) break;
                 tc_fence_after();
+                if (lane == 0) {
 #pragma unroll
-                for (int kk = 0; kk < GA_UNIT / 16; ++kk)  // 2 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
-                    umma_ts(tmem_o, tmem_p + pb * (GA_UNIT / 2) + kk * 8, v_desc[vb] + (uint64_t)(((w & 1) * 2 + kk) * 128), IDESC_O,
-                            (w == 0 && kk == 0) ? 0u : 1u);
-                umma_commit(&sm.bar_o[pb]);
-                if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_vfree[vb]);
+                    for (int kk = 0; kk < GA_UNIT / 16; ++kk)  // 2 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
+                        umma_ts(tmem_o, tmem_p + pb * (GA_UNIT / 2) + kk * 8, v_desc[vb] + (uint64_t)(((w & 1) * 2 + kk) * 128), IDESC_O,
+                                (w == 0 && kk == 0) ? 0u : 1u);
+                    umma_commit(&sm.bar_o[pb]);
+                    if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_vfree[vb]);
+                }
+                __syncwarp();
             }
         }
         __syncwarp();
@@ -545,11 +556,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (!p.far_skip || !(fm.far_cut < INFINITY)) wq_reach = -INFINITY;  // test off
         }
         float m_run = -INFINITY, l_run = 0.f;
-        // `ok` is kept uniform across the warp (tcgen05.ld / st and the votes below need all 32 lanes)
         bool ok = true;
-        auto wait_w = [&](uint64_t *bar, uint32_t parity) -> bool {
-            return __all_sync(0xffffffffu, mbar_wait_abortable(bar, parity, abort_flag) ? 1 : 0) != 0;
-        };
 
 #pragma unroll 1
         for (int w = 0; ok && w < nw; ++w) {
