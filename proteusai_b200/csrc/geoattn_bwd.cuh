@@ -41,8 +41,10 @@ constexpr int GA_ROW_BUFS = 3;
 constexpr int GA_SUB = 64;  // queries per sub-tile (two sub-tiles per 128-row query tile)
 
 struct GaQueryRows {                  // per-query inputs of one query tile, two queries per entry
-    float2 l2[GA_BM / 2];             // log-sum-exp in base-2 units (+inf: padded query or row without a valid pair)
-    float2 dsum[GA_BM / 2];           // D_i
+    float4 qa[GA_BM / 2];             // centred coordinates {x_i, x_i+1, y_i, y_i+1}
+    float4 qc[GA_BM / 2];             // {z_i, z_i+1, |q_i|^2, |q_i+1|^2}
+    float4 ld[GA_BM / 2];             // {L_i, L_i+1, D_i, D_i+1}: log-sum-exp in base-2 units (+inf: padded query or row
+                                      // without a valid pair) and D
     uint32_t qbits[GA_BM / 32];       // bit i of word u: query 32 u + i is valid
     float4 sph[GA_BM / 16];           // bounding sphere of each group of 16 queries (radius < 0: no valid query)
 };
@@ -53,11 +55,9 @@ struct GaBwdSmem {
     alignas(1024) uint8_t q[2][GA_TILE_BYTES];
     alignas(1024) uint8_t dout[2][GA_TILE_BYTES];
     alignas(1024) uint8_t ds[2][2 * GA_TILE_BYTES];  // dS^T [128 keys x 128 queries] bf16: two [128 x 64] swizzled sub-tiles
-    // Geometry operands (see ga_write_geo_row): slot 0 = the keys (-2 k, 1), slots 1..3 = the ring of staged query tiles (q, |q|^2)
-    alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaQueryRows rows[GA_ROW_BUFS];
     uint16_t tiles[GA_MAX_TILES];          // live query tiles of the range; bit 15: the tile also holds a padded query
-    uint64_t bar_kv, bar_qdo[2], bar_sp, bar_spfree, bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS], bar_rowsfree[GA_ROW_BUFS];
+    uint64_t bar_kv, bar_qdo[2], bar_sp[2], bar_spfree[2], bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS], bar_rowsfree[GA_ROW_BUFS];
     uint32_t tmem_base;
     int abort;
     float dsig[GA_BWD_MATH_THREADS / 32];
@@ -109,18 +109,23 @@ __device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
-struct GaBwdKey {  // per-thread constants of the thread's key
-    f2_t ckn2;  // c_rbf |k|^2 (centred)
+struct GaBwdKey {  // per-thread constants of the thread's key (centred coordinates k)
+    f2_t ax2, ay2, az2;  // -2 c_rbf k
+    f2_t ckn2;           // c_rbf |k|^2
     bool k_ok;
 };
 
-// Stages one query of a query tile: its geometry operand row (q, |q|^2), log-sum-exp, D, validity and, with the other 15
-// queries of its half-warp, the bounding sphere of the group of 16.  Executed by whole warps with query = lane + 32 m.
-__device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile, int geo_block, int i, bool ok, float x, float y, float z,
-                                             float l2, float dsum) {
-    ga_write_geo_row<false>(geo_tile, geo_block, i, x, y, z, x * x + y * y + z * z);
-    reinterpret_cast<float *>(&rw.l2[i >> 1])[i & 1] = l2;
-    reinterpret_cast<float *>(&rw.dsum[i >> 1])[i & 1] = dsum;
+// Stages one query of a query tile: centred coordinates, log-sum-exp, D, validity and, with the other 15 queries of its
+// half-warp, the bounding sphere of the group of 16.  Executed by whole warps with query = lane + 32 m.
+__device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, int i, bool ok, float x, float y, float z, float l2, float dsum) {
+    float *qa = reinterpret_cast<float *>(&rw.qa[i >> 1]), *qc = reinterpret_cast<float *>(&rw.qc[i >> 1]);
+    float *ld = reinterpret_cast<float *>(&rw.ld[i >> 1]);
+    qa[i & 1] = x;
+    qa[2 + (i & 1)] = y;
+    qc[i & 1] = z;
+    qc[2 + (i & 1)] = x * x + y * y + z * z;
+    ld[i & 1] = l2;
+    ld[2 + (i & 1)] = dsum;
     const uint32_t bits = __ballot_sync(0xffffffffu, ok);
     if ((i & 31) == 0) rw.qbits[i >> 5] = bits;
     float n = ok ? 1.f : 0.f, sx = x, sy = y, sz = z;  // padded queries carry 0
@@ -140,7 +145,8 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile,
 }
 
 // The 16 query columns (8 pairs) of one key row that a thread owns in a sub-tile: recompute P, form dS and the
-// spread-gradient term.  sv / dpv / gv hold the raw S^T, dP^T and G^T = |q|^2 - 2 k.q values (|r_k - r_q|^2 = G^T + |k|^2);
+// spread-gradient term.  sv / dpv hold the raw S^T and dP^T values; the queries' coordinates come from shared memory
+// (every lane reads the same entry) and c_rbf |r_k - r_q|^2 = c_rbf |q|^2 - 2 c_rbf k.q + c_rbf |k|^2 takes four packed FMAs a pair;
 // the results come back as bf16 pairs in pw / dw.  `p0` is the index of the first of the 8 query pairs inside the
 // tile's row arrays.
 // `masked` (warp-uniform): the key tile or the query tile holds a padded token; `qbits`: validity of the 16 queries.
@@ -149,7 +155,7 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, uint8_t *geo_tile,
 // count; R = 0 then goes through the same arithmetic.  One body serves every case, and every pair goes through the
 // whole chain in one pass so that few values are live at a time.
 template <int FORM>
-__device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)[16], const uint32_t (&gv)[16], bool far, bool masked,
+__device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)[16], bool far, bool masked,
                                              uint32_t qbits, const GaQueryRows &rw, int p0, const GaBwdKey &key, f2_t crbf2, f2_t cs2,
                                              f2_t scale2, const GaForm &fm, f2_t &dsig2, f2_t &dbeta2, uint32_t (&pw)[8],
                                              uint32_t (&dw)[8]) {
@@ -172,8 +178,12 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)
     for (int e = 0; e < 8; ++e) {
         f2_t arg = 0ull, rb = 0ull;
         if (!far) {  // c_rbf * d^2 and R
+            const float4 qa = rw.qa[p0 + e], qc = rw.qc[p0 + e];
+            f2_t t = f2_fma(key.ax2, f2_pack(qa.x, qa.y), key.ckn2);
+            t = f2_fma(key.ay2, f2_pack(qa.z, qa.w), t);
+            t = f2_fma(key.az2, f2_pack(qc.x, qc.y), t);
             float a0, a1;
-            f2_unpack(f2_fma(f2_pack(__uint_as_float(gv[2 * e]), __uint_as_float(gv[2 * e + 1])), crbf2, key.ckn2), a0, a1);
+            f2_unpack(f2_fma(crbf2, f2_pack(qc.z, qc.w), t), a0, a1);
             if (FORM == 1) {
                 a0 = fminf(a0, 0.f);
                 a1 = fminf(a1, 0.f);
@@ -184,7 +194,7 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)
         const f2_t s_raw = f2_pack(__uint_as_float(sv[2 * e]), __uint_as_float(sv[2 * e + 1]));
         const f2_t t2 = f2_mul(s_raw, cs2);
         const f2_t onep = f2_add(rb, one2);
-        const float2 l = rw.l2[p0 + e];
+        const float4 l = rw.ld[p0 + e];  // {L pair, D pair}
         f2_t x;
         if (FORM == 0) {
             x = f2_fma(t2, onep, f2_pack(-l.x, -l.y));
@@ -210,8 +220,7 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)
         }
         const f2_t pp = f2_pack(p0v, p1v);
         const f2_t dp = f2_pack(__uint_as_float(dpv[2 * e]), __uint_as_float(dpv[2 * e + 1]));
-        const float2 dd = rw.dsum[p0 + e];
-        const f2_t dsr = f2_mul(pp, f2_sub(dp, f2_pack(dd.x, dd.y)));  // P = 0 (padding, outside the window): dSR = 0
+        const f2_t dsr = f2_mul(pp, f2_sub(dp, f2_pack(l.z, l.w)));  // P = 0 (padding, outside the window): dSR = 0
         f2_t ds;
         if (FORM == 0) {
             ds = f2_mul(f2_mul(dsr, scale2), onep);
@@ -301,10 +310,12 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             mbar_init(&sm.bar_kv, 1);
             mbar_init(&sm.bar_qdo[0], 1);
             mbar_init(&sm.bar_qdo[1], 1);
-            mbar_init(&sm.bar_sp, 1);
+            mbar_init(&sm.bar_sp[0], 1);
+            mbar_init(&sm.bar_sp[1], 1);
             mbar_init(&sm.bar_vk, 1);
             mbar_init(&sm.bar_dq, 1);
-            mbar_init(&sm.bar_spfree, GA_BWD_MATH_THREADS);
+            mbar_init(&sm.bar_spfree[0], GA_BWD_MATH_THREADS);
+            mbar_init(&sm.bar_spfree[1], GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_pds, GA_BWD_MATH_THREADS);
             mbar_init(&sm.bar_dqr, GA_BWD_MATH_THREADS);
 #pragma unroll
@@ -355,31 +366,26 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const bool ok = i < N && q.vb[m] != 0;
             // +inf: P = 0 for a padded query and for a row without any valid pair
             const float l2 = (ok && q.lse[m] != -INFINITY) ? q.lse[m] * 1.4426950408889634f : INFINITY;
-            ga_stage_row(sm.rows[buf], ga_geo_tile(sm, 1 + buf), ga_geo_block(1 + buf), lane + 32 * m, ok, ok ? q.gx[m] - orx : 0.f,
-                         ok ? q.gy[m] - ory : 0.f, ok ? q.gz[m] - orz : 0.f, l2, ok ? q.ds[m] : 0.f);
+            ga_stage_row(sm.rows[buf], lane + 32 * m, ok, ok ? q.gx[m] - orx : 0.f, ok ? q.gy[m] - ory : 0.f, ok ? q.gz[m] - orz : 0.f, l2,
+                         ok ? q.ds[m] : 0.f);
         }
-        fence_proxy_async();  // the geometry rows (generic-proxy stores) must be visible to the tensor core
     };
-    // this thread's key, centred; the keys' geometry operand: (-2 k, 1)
+    // this thread's key, centred
     float kcx = 0.f, kcy = 0.f, kcz = 0.f;
     if (k_ok) {
         kcx = cz[jrow * 3] - orx;
         kcy = cz[jrow * 3 + 1] - ory;
         kcz = cz[jrow * 3 + 2] - orz;
     }
-    if (tid < GA_BN) {  // (tid < 128: r == tid, grp == 0)
-        ga_write_geo_row<true>(ga_geo_tile(sm, 0), ga_geo_block(0), tid, -2.f * kcx, -2.f * kcy, -2.f * kcz, 1.f);
-        fence_proxy_async();
-    }
     RowLoad rl;
     if (is_stager) row_load(word_g(first) & 0x7fff, rl);  // in flight across the barrier
     tc_fence_before();
-    __syncthreads();  // barriers initialised, TMEM allocated, tile list and the keys' geometry operand in place
+    __syncthreads();  // barriers initialised, TMEM allocated, tile list in place
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
-    // S^T [0,64), dP^T [64,128), G^T two buffers [128,192) [192,256), P^T [256,288), dV [320,384), dK [384,448), dQ [448,512)
-    const uint32_t tm_s = tmem, tm_dp = tmem + 64, tm_g = tmem + 128, tm_p = tmem + 256, tm_dv = tmem + 320, tm_dk = tmem + 384,
-                   tm_dq = tmem + 448;
+    // two stages of S^T [0,64) [64,128) and dP^T [128,192) [192,256) (sub-tile u uses stage u & 1), P^T [256,288), dV [320,384),
+    // dK [384,448), dQ [448,512)
+    const uint32_t tm_s = tmem, tm_dp = tmem + 128, tm_p = tmem + 256, tm_dv = tmem + 320, tm_dk = tmem + 384, tm_dq = tmem + 448;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
 
     if (is_stager) {
@@ -388,7 +394,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int t = 0; t < nt; ++t) {
             const int b = t % GA_ROW_BUFS;
             if (t > 0) row_load(tile_word(t) & 0x7fff, rl);
-            // buffer b was last used by tile t - GA_ROW_BUFS: every math thread has left it (and its G MMAs have completed)
+            // buffer b was last used by tile t - GA_ROW_BUFS: every math thread has left it
             if (t >= GA_ROW_BUFS && !__all_sync(0xffffffffu, mbar_wait_abortable(&sm.bar_rowsfree[b], (uint32_t)((t / GA_ROW_BUFS - 1) & 1), abort_flag) ? 1 : 0))
                 break;  // (decided by the whole warp: the staging below shuffles across all 32 lanes)
             row_stage(tile_word(t) & 0x7fff, b, rl);
@@ -413,41 +419,29 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const uint64_t q_km = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024), do_km = umma_desc_sw128(smem_u32(sm.dout[0]), 16, 1024);
             const uint64_t q_mn = umma_desc_sw128(smem_u32(sm.q[0]), 0, 1024), do_mn = umma_desc_sw128(smem_u32(sm.dout[0]), 0, 1024);
             const uint64_t ds_km = umma_desc_sw128(smem_u32(sm.ds[0]), 16, 1024), ds_mn = umma_desc_sw128(smem_u32(sm.ds[0]), GA_TILE_BYTES, 1024);
-            const uint64_t geo0 = umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024);
-            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo0 + (uint64_t)(slot >> 1) * BUF + (uint64_t)(ga_geo_block(slot) * 4); };
             constexpr uint64_t SUB_ROWS = (uint64_t)(GA_SUB * 128) >> 4;  // 64 rows of a swizzled tile, in 16-byte units
             if (is_producer) {
                 // Sub-tile u = 2 t + s (queries 64 s .. 64 s + 63 of tile t): S^T = K Q^T and dP^T = V dO^T, 4 + 4 MMAs of K = 16
-                // over d = 64; G^T over the geometry operands, 2 MMAs.  B operands start 64 rows into their tiles for s = 1.
-                auto issue_sdg = [&](int u) {
+                // over d = 64, into stage s.  B operands start 64 rows into their tiles for s = 1.
+                auto issue_sdp = [&](int u) {
                     const int t = u >> 1, sub = u & 1, b = t & 1;
                     const uint64_t qd = q_km + b * BUF + sub * SUB_ROWS, dd = do_km + b * BUF + sub * SUB_ROWS;
 #pragma unroll
-                    for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_s, k_km + (uint64_t)(kk * 2), qd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                    for (int kk = 0; kk < GA_D / 16; ++kk)
+                        umma_ss(tm_s + sub * GA_SUB, k_km + (uint64_t)(kk * 2), qd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kk = 0; kk < GA_D / 16; ++kk) umma_ss(tm_dp, v_km + (uint64_t)(kk * 2), dd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
-                    const uint64_t kg = geo_slot_desc(0), qg = geo_slot_desc(1 + t % GA_ROW_BUFS) + sub * SUB_ROWS;
-#pragma unroll
-                    for (int kk = 0; kk < GA_GEO_K / 16; ++kk)
-                        umma_ss(tm_g + (u & 1) * GA_SUB, kg + (uint64_t)(kk * 2), qg + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
-                    umma_commit(&sm.bar_sp);
+                    for (int kk = 0; kk < GA_D / 16; ++kk)
+                        umma_ss(tm_dp + sub * GA_SUB, v_km + (uint64_t)(kk * 2), dd + (uint64_t)(kk * 2), IDESC_SP, kk > 0 ? 1u : 0u);
+                    umma_commit(&sm.bar_sp[sub]);
                 };
-                bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag) && mbar_wait_abortable(&sm.bar_qdo[0], 0, abort_flag) &&
-                          mbar_wait_abortable(&sm.bar_rows[0], 0, abort_flag);
-                if (ok) {
-                    tc_fence_after();
-                    issue_sdg(0);
-                }
-                for (int u = 0; ok && u + 1 < nsub; ++u) {
+                bool ok = mbar_wait_abortable(&sm.bar_kv, 0, abort_flag);
+                for (int u = 0; ok && u < nsub; ++u) {
                     const int t = u >> 1, sub = u & 1, b = t & 1;
-                    // every math thread holds its S^T, dP^T(u) in registers: compute the next sub-tile's
-                    if (!(ok = mbar_wait_abortable(&sm.bar_spfree, (uint32_t)(u & 1), abort_flag))) break;
-                    if (sub == 1) {  // the next sub-tile opens query tile t + 1
-                        if (!(ok = mbar_wait_abortable(&sm.bar_qdo[b ^ 1], (uint32_t)(((t + 1) >> 1) & 1), abort_flag))) break;
-                        if (!(ok = mbar_wait_abortable(&sm.bar_rows[(t + 1) % GA_ROW_BUFS], (uint32_t)(((t + 1) / GA_ROW_BUFS) & 1), abort_flag))) break;
-                    }
+                    // stage `sub` was last used by sub-tile u - 2: every math thread holds its S^T, dP^T in registers
+                    if (u >= 2 && !(ok = mbar_wait_abortable(&sm.bar_spfree[sub], (uint32_t)((t - 1) & 1), abort_flag))) break;
+                    if (sub == 0 && !(ok = mbar_wait_abortable(&sm.bar_qdo[b], (uint32_t)((t >> 1) & 1), abort_flag))) break;
                     tc_fence_after();
-                    issue_sdg(u + 1);  // (its G^T buffer was last read for sub-tile u - 1, which has handed over P^T and dS^T)
+                    issue_sdp(u);
                 }
             } else {
                 auto load_qdo = [&](int t) {
@@ -512,6 +506,9 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         GaBwdKey key;
         const float ckn = c_rbf * (kcx * kcx + kcy * kcy + kcz * kcz);
         key.ckn2 = f2_pack(ckn, ckn);
+        key.ax2 = f2_pack(-2.f * c_rbf * kcx, -2.f * c_rbf * kcx);
+        key.ay2 = f2_pack(-2.f * c_rbf * kcy, -2.f * c_rbf * kcy);
+        key.az2 = f2_pack(-2.f * c_rbf * kcz, -2.f * c_rbf * kcz);
         key.k_ok = k_ok;
         // bounding sphere of the warp's valid keys; wk_reach = (distance beyond which R does not count) + radius
         float wkx, wky, wkz, wk_reach;
@@ -562,7 +559,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             const bool masked = key_hole || (tile_word(t) & 0x8000) != 0;
             const GaQueryRows &rw = sm.rows[rbuf];
             uint8_t *ds_tile = sm.ds[t & 1];
-            if (!(ok = wait_w(&sm.bar_sp, par))) break;  // S^T, dP^T, G^T(u) have landed in TMEM (the producer waited for the rows)
+            if (sub == 0 && !(ok = wait_w(&sm.bar_rows[rbuf], (uint32_t)((t / GA_ROW_BUFS) & 1)))) break;  // the tile's staged rows
+            if (!(ok = wait_w(&sm.bar_sp[sub], (uint32_t)(t & 1)))) break;  // S^T, dP^T(u) have landed in TMEM
             tc_fence_after();
             const int col0 = sub * GA_SUB + grp * 16;  // first query column (inside the tile) of this thread's 16
             bool far;
@@ -573,15 +571,14 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 far = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
             }
             const uint32_t qbits = (rw.qbits[col0 / 32] >> (col0 & 16)) & 0xffffu;
-            uint32_t sv[16], dpv[16], gv[16];
-            tmem_ld16(tm_s + lane_base + grp * 16, sv);
-            tmem_ld16(tm_dp + lane_base + grp * 16, dpv);
-            if (!far) tmem_ld16(tm_g + (u & 1) * GA_SUB + lane_base + grp * 16, gv);
+            uint32_t sv[16], dpv[16];
+            tmem_ld16(tm_s + sub * GA_SUB + lane_base + grp * 16, sv);
+            tmem_ld16(tm_dp + sub * GA_SUB + lane_base + grp * 16, dpv);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&sm.bar_spfree);  // the accumulators may be overwritten with the next sub-tile's
+            mbar_arrive(&sm.bar_spfree[sub]);  // the stage may be overwritten with sub-tile u + 2
             uint32_t pw[8], dw[8];
-            ga_bwd_chunk<FORM>(sv, dpv, gv, far, masked, qbits, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
+            ga_bwd_chunk<FORM>(sv, dpv, far, masked, qbits, rw, col0 / 2, key, crbf2, cs2, scale2, fm, dsig2, dbeta2, pw, dw);
             // P^T(u-1) is read by dV(u-1): no store before it has completed (the dS^T buffer of this tile was last read
             // by dK / dQ two query tiles ago)
             if (u > 0 && !(ok = wait_w(&sm.bar_vk, par ^ 1))) break;
