@@ -180,6 +180,28 @@ size_t pai_geoattn_plan_bytes(int Z, int N);
 int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Geometric attention: balanced schedule.
+ * No counterpart in the reference, which launches one program per (query block, batch x head) pair
+ *   (old/old_scripts/attn/geometric_attn.py:582-585).  The work items of the attention kernels, (sample, head, 128-token
+ *   tile) triples, cost as much as their sample has non-empty tiles; with one CTA per item the SM that happens to get
+ *   two long items finishes a third later than the average on a batch of mixed lengths.  A schedule assigns the
+ *   items of a plan to `bins` persistent CTAs beforehand, longest first, each to the bin with the least work.
+ *   One schedule serves every call with the same plan, H and direction.
+ *
+ *   plan       from pai_geoattn_plan (same Z, N)
+ *   bins       CTAs of the launch, at most 1024: twice the SM count for the forward (two CTAs share an SM), the SM
+ *              count for the backward
+ *   backward   0: for pai_geoattn_fwd*, 1: for pai_geoattn_bwd (the fixed cost of an item differs)
+ *   sched      at least pai_geoattn_schedule_bytes(Z,N,H,bins) bytes, 16-byte aligned, written by the call
+ * The attention calls take the schedule as (sched, sched_bins); sched = NULL launches one CTA per item.  A schedule
+ *   needs `valid` and its plan, and only applies to a call over the whole problem (zh_begin = 0, zh_end = Z*H,
+ *   q_begin = 0, q_end = N): other ranges with a schedule are PAI_ERR_BAD_ROW_RANGE.
+ */
+size_t pai_geoattn_schedule_bytes(int Z, int N, int H, int bins);
+int pai_geoattn_schedule(const void *plan, int Z, int N, int H, int bins, int backward, void *sched, size_t sched_bytes,
+                         void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Geometric attention, forward.
  * Replaces the Triton launch `_attn_fwd[grid](...)` in _geometric_attn.forward
  *   (old/old_scripts/attn/geometric_attn.py:553-607; kernel :57-260).  Two logit forms:
@@ -198,6 +220,7 @@ int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan
  *   betas    [H]       fp32                 per-head RBF weight (logit_form 1)
  *   valid    [Z,N]     u8                   1 = real token, 0 = padding; NULL = all valid
  *   plan                                    from pai_geoattn_plan for this `valid` (required with `valid`, ignored without)
+ *   sched, sched_bins                       from pai_geoattn_schedule(..., backward = 0), or NULL, 0
  *   O        [Z,H,N,d] bf16                 rows of padded queries are written as zeros (whatever Q, K, V hold there)
  *   L        [Z,H,N]   fp32                 log-sum-exp of SR over the keys (natural log); -inf for rows without a valid pair
  *   scale                                    softmax scale, 1/sqrt(d) in the reference
@@ -210,7 +233,8 @@ int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan
  * bf16 x bf16 -> fp32 tensor-core products, fp32 softmax, P rounded to bf16 before P V.
  */
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, const void *plan, void *O, float *L,
+                    const float *betas, const uint8_t *valid, const void *plan, const void *sched, int sched_bins,
+                    void *O, float *L,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
                     int zh_begin, int zh_end, int q_begin, int q_end, void *stream);
 
@@ -229,7 +253,7 @@ int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *co
  */
 int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides,
                             const void *V, const int64_t *v_strides, const float *coords, const float *sigma,
-                            const float *betas, const uint8_t *valid, const void *plan,
+                            const float *betas, const uint8_t *valid, const void *plan, const void *sched, int sched_bins,
                             void *O, const int64_t *o_strides, float *L,
                             int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
                             int zh_begin, int zh_end, int q_begin, int q_end, void *stream);
@@ -249,13 +273,15 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
  *   workspace      scratch of at least pai_geoattn_bwd_workspace_bytes(Z,H,N,d) bytes, 16-byte aligned
  *                  (holds D, one fp32 per query row)
  *   valid, plan, zh_begin, zh_end  as in the forward
+ *   sched, sched_bins  from pai_geoattn_schedule(..., backward = 1), or NULL, 0
  *   q_begin, q_end only the query rows [q_begin, q_end) contribute: dK, dV, dsigma, dbetas are then partial sums
  *                  that the caller adds over the query shards (an all-reduce across ranks); same alignment rule
  */
 size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d);
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
                     const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
-                    const void *plan, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
+                    const void *plan, const void *sched, int sched_bins,
+                    float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
                     void *workspace, size_t workspace_bytes,
                     int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form,
                     int zh_begin, int zh_end, int q_begin, int q_end, void *stream);

@@ -30,12 +30,14 @@ SIGNATURES = {
     "pai_we_bwd_dk_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_plan_bytes": (c_size_t, [c_int, c_int]),
     "pai_geoattn_plan": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "pai_geoattn_fwd": (c_int, [c_void_p] * 10 + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+    "pai_geoattn_schedule_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "pai_geoattn_schedule": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "pai_geoattn_fwd": (c_int, [c_void_p] * 9 + [c_int, c_void_p, c_void_p] + [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
                                 c_int, c_int, c_int, c_int, c_void_p]),
-    "pai_geoattn_fwd_strided": (c_int, [c_void_p, _I64P, c_void_p, _I64P, c_void_p, _I64P] + [c_void_p] * 6 + [_I64P, c_void_p] +
+    "pai_geoattn_fwd_strided": (c_int, [c_void_p, _I64P, c_void_p, _I64P, c_void_p, _I64P] + [c_void_p] * 6 + [c_int, c_void_p] + [_I64P, c_void_p] +
                                 [c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "pai_geoattn_bwd_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
-    "pai_geoattn_bwd": (c_int, [c_void_p] * 16 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
+    "pai_geoattn_bwd": (c_int, [c_void_p] * 12 + [c_int] + [c_void_p] * 5 + [c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_int,
                                 c_int, c_int, c_int, c_int, c_void_p]),
     "pai_add_layernorm_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, ctypes.c_longlong, c_int, c_float, c_void_p]),
     "pai_gelu_bf16": (c_int, [c_void_p, c_void_p, ctypes.c_longlong, c_void_p]),

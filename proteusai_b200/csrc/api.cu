@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(256) sfu_peak_kernel(int iters, float seed) {
 
 extern "C" {
 
-int pai_abi_version(void) { return 5; }  // 5: flags in pai_we_fwd; attention batch plan and query-row ranges; test-only entries
+int pai_abi_version(void) { return 6; }  // 6: balanced attention schedules (5: WE flags, batch plan, query-row ranges, test-only entries)
 
 const char *pai_status_str(int status) {
     switch (status) {
@@ -257,6 +257,26 @@ int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan
     return (int)cudaPeekAtLastError();
 }
 
+size_t pai_geoattn_schedule_bytes(int Z, int N, int H, int bins) {
+    if (Z < 1 || N < 1 || H < 1 || bins < 1 || bins > pai::GA_SCHED_MAX_BINS) return 0;
+    return pai::ga_sched_words(Z, N, H, bins) * sizeof(int);
+}
+
+int pai_geoattn_schedule(const void *plan, int Z, int N, int H, int bins, int backward, void *sched, size_t sched_bytes, void *stream) {
+    if (!plan || !sched) return PAI_ERR_NULL_POINTER;
+    if (Z < 1 || H < 1 || (long long)Z * H > 65535 || N < 1 || N > pai::GA_BN * pai::GA_MAX_TILES) return PAI_ERR_BAD_SHAPE;
+    if (bins < 1 || bins > pai::GA_SCHED_MAX_BINS) return PAI_ERR_BAD_SHAPE;
+    if (!aligned(plan, 16) || !aligned(sched, 16)) return PAI_ERR_MISALIGNED;
+    if (sched_bytes < pai_geoattn_schedule_bytes(Z, N, H, bins)) return PAI_ERR_WORKSPACE_TOO_SMALL;
+    if (int e = require_sm100()) return e;
+    // cost of a work item in eighths of a (128 x 128) tile: the tiles it visits plus its set-up and epilogue
+    // (measured: set-up, first loads and epilogue of an item take as long as 1.5 tiles in the backward, 0.6 in the forward);
+    // the forward runs two CTAs on an SM
+    pai::geoattn_schedule_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const int *)plan, (int *)sched, Z, N, H, bins, 8,
+                                                                       backward ? 12 : 5, backward ? 0 : 1);
+    return (int)cudaPeekAtLastError();
+}
+
 namespace {
 // argument checks shared by the attention entry points; *qt0, *qt1: query tiles of the row range
 int check_attn_common(int Z, int H, int N, int d, int logit_form, const float *betas, float min_rbf, float max_rbf,
@@ -277,17 +297,28 @@ int check_attn_common(int Z, int H, int N, int d, int logit_form, const float *b
 bool order_applies(const void *plan, int Z, int H, int zh_begin, int zh_end) {
     return plan != nullptr && zh_begin == 0 && zh_end == Z * H && g_tune[PAI_TUNE_GA_NO_ORDER] == 0;
 }
+// a schedule covers the whole problem: every (batch, head) pair and every query row
+int check_sched(const void *plan, const void *sched, int sched_bins, int Z, int H, int N, int zh_begin, int zh_end, int q_begin, int q_end) {
+    if (!sched) return 0;
+    if (!plan) return PAI_ERR_NULL_POINTER;
+    if (!aligned(sched, 16)) return PAI_ERR_MISALIGNED;
+    if (sched_bins < 1 || sched_bins > pai::GA_SCHED_MAX_BINS) return PAI_ERR_BAD_SHAPE;
+    if (zh_begin != 0 || zh_end != Z * H || q_begin != 0 || q_end != N) return PAI_ERR_BAD_ROW_RANGE;
+    return 0;
+}
 }  // namespace
 
 int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void *K, const int64_t *k_strides, const void *V,
                             const int64_t *v_strides, const float *coords, const float *sigma, const float *betas,
-                            const uint8_t *valid, const void *plan, void *O, const int64_t *o_strides, float *L, int Z, int H,
+                            const uint8_t *valid, const void *plan, const void *sched, int sched_bins, void *O, const int64_t *o_strides,
+                            float *L, int Z, int H,
                             int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
                             int q_begin, int q_end, void *stream) {
     if (!Q || !K || !V || !coords || !sigma || !O || !L || !q_strides || !k_strides || !v_strides || !o_strides)
         return PAI_ERR_NULL_POINTER;
     if (int e = check_attn_common(Z, H, N, d, logit_form, betas, min_rbf, max_rbf, valid, plan, zh_begin, zh_end, q_begin, q_end))
         return e;
+    if (int e = check_sched(valid ? plan : nullptr, sched, sched_bins, Z, H, N, zh_begin, zh_end, q_begin, q_end)) return e;
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(coords, 4) ||
         !aligned(sigma, 4) || !aligned(L, 4))
         return PAI_ERR_MISALIGNED;
@@ -346,18 +377,20 @@ int pai_geoattn_fwd_strided(const void *Q, const int64_t *q_strides, const void 
     p.beta = betas;
     p.min_rbf = min_rbf;
     p.max_rbf = max_rbf;
+    p.sched = (valid && g_tune[PAI_TUNE_GA_NO_ORDER] == 0) ? (const int *)sched : nullptr;
     dim3 grid((q_end - q_begin + pai::GA_BM - 1) / pai::GA_BM, nzh, 1);
+    if (p.sched) grid = dim3(sched_bins, 1, 1);
     if (logit_form == 0) pai::geoattn_fwd_kernel<0><<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     else pai::geoattn_fwd_kernel<1><<<grid, pai::GA_FWD_THREADS, smem, (cudaStream_t)stream>>>(mq, mk, mv, p);
     return (int)cudaPeekAtLastError();
 }
 
 int pai_geoattn_fwd(const void *Q, const void *K, const void *V, const float *coords, const float *sigma,
-                    const float *betas, const uint8_t *valid, const void *plan, void *O, float *L, int Z, int H,
-                    int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
+                    const float *betas, const uint8_t *valid, const void *plan, const void *sched, int sched_bins, void *O, float *L,
+                    int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf, int logit_form, int zh_begin, int zh_end,
                     int q_begin, int q_end, void *stream) {
     const int64_t st[3] = {(int64_t)H * N * d, (int64_t)N * d, (int64_t)d};  // contiguous [Z,H,N,d]
-    return pai_geoattn_fwd_strided(Q, st, K, st, V, st, coords, sigma, betas, valid, plan, O, st, L, Z, H, N, d, scale,
+    return pai_geoattn_fwd_strided(Q, st, K, st, V, st, coords, sigma, betas, valid, plan, sched, sched_bins, O, st, L, Z, H, N, d, scale,
                                    min_rbf, max_rbf, logit_form, zh_begin, zh_end, q_begin, q_end, stream);
 }
 
@@ -369,7 +402,8 @@ size_t pai_geoattn_bwd_workspace_bytes(int Z, int H, int N, int d) {
 
 int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, const void *dO, const float *L,
                     const float *coords, const float *sigma, const float *betas, const uint8_t *valid,
-                    const void *plan, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas, void *workspace,
+                    const void *plan, const void *sched, int sched_bins, float *dQ, float *dK, float *dV, float *dsigma, float *dbetas,
+                    void *workspace,
                     size_t workspace_bytes, int Z, int H, int N, int d, float scale, float min_rbf, float max_rbf,
                     int logit_form, int zh_begin, int zh_end, int q_begin, int q_end, void *stream) {
     if (!Q || !K || !V || !O || !dO || !L || !coords || !sigma || !dQ || !dK || !dV || !dsigma || !workspace)
@@ -377,6 +411,7 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     if (logit_form == 1 && !dbetas) return PAI_ERR_NULL_POINTER;
     if (int e = check_attn_common(Z, H, N, d, logit_form, betas, min_rbf, max_rbf, valid, plan, zh_begin, zh_end, q_begin, q_end))
         return e;
+    if (int e = check_sched(valid ? plan : nullptr, sched, sched_bins, Z, H, N, zh_begin, zh_end, q_begin, q_end)) return e;
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16) || !aligned(dO, 16) || !aligned(dQ, 16) ||
         !aligned(dK, 16) || !aligned(dV, 16) || !aligned(L, 4) || !aligned(coords, 4) || !aligned(sigma, 4) ||
         !aligned(dsigma, 4) || !aligned(workspace, 16))
@@ -443,7 +478,9 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     p.N = N;
     p.zh_begin = zh_begin;
     p.scale = scale;
+    p.sched = (valid && g_tune[PAI_TUNE_GA_NO_ORDER] == 0) ? (const int *)sched : nullptr;
     dim3 grid((N + pai::GA_BN - 1) / pai::GA_BN, nzh, 1);
+    if (p.sched) grid = dim3(sched_bins, 1, 1);
     if (p.form == 0) pai::geoattn_bwd_kernel<0><<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
     else pai::geoattn_bwd_kernel<1><<<grid, pai::GA_BWD_THREADS, smem, st>>>(mq, mk, mv, mdo, p);
     return (int)cudaPeekAtLastError();

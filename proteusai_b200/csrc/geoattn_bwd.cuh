@@ -83,6 +83,7 @@ struct GaBwdParams {
     float min_rbf, max_rbf;
     int use_order;         // issue the samples in the plan's longest-first order
     int far_skip;          // skip the RBF arithmetic of far query groups
+    const int *sched;      // balanced schedule (geoattn_plan.cuh) or nullptr: one CTA per item
     int qt_begin, qt_end;  // query tiles [qt_begin, qt_end) are visited
 };
 
@@ -247,12 +248,12 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)
     }
 }
 
+// One work item: the key tile `k_tile` of the (batch, head) pair `zh_local` of the launch.  Every thread of the CTA calls
+// it; tensor memory is allocated by the caller.  `fresh`: the CTA has not initialised its barriers yet; a live item
+// clears it, later ones invalidate the barriers before they initialise them again.
 template <int FORM>
-__global__ void __launch_bounds__(GA_BWD_THREADS, 1)
-geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const GaBwdParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    GaBwdSmem &sm = *reinterpret_cast<GaBwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+__device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMap &map_q, const CUtensorMap &map_k, const CUtensorMap &map_v,
+                                                 const CUtensorMap &map_do, const GaBwdParams &p, int zh_local, int k_tile, bool &fresh) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_BWD_MATH_THREADS / 32;
     const bool is_producer = warp == GA_BWD_MATH_THREADS / 32, is_stager = warp == GA_BWD_MATH_THREADS / 32 + 1;
@@ -261,14 +262,9 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int r = (warp & 3) * 32 + lane;         // key row inside the tile = TMEM lane
     const int N = p.N;
     const int tiles_all = (N + GA_BM - 1) / GA_BM;
-    int zh_local = blockIdx.y;
-    if (p.use_order) {  // samples longest first
-        const int zp = zh_local / p.H;
-        zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
-    }
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
-    const int j0 = blockIdx.x * GA_BN;
+    const int j0 = k_tile * GA_BN;
     const float *cz = p.coords + (size_t)z * N * 3;
     const uint8_t *vz = p.valid ? p.valid + (size_t)z * N : nullptr;
 
@@ -280,9 +276,12 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int nt_all = p.plan ? ga_plan_count(p.plan, p.Z)[z] : tiles_all;
     auto word_g = [&](int t) -> int { return tl ? tl[t] : (ga_plan_info_unmasked(N, t) | t); };
     // the list is ascending: the tiles of [qt_begin, qt_end) are a contiguous run of it
-    int first = 0, nt = 0;
-    while (first < nt_all && (word_g(first) & 0x7fff) < p.qt_begin) ++first;
-    while (first + nt < nt_all && (word_g(first + nt) & 0x7fff) < p.qt_end) ++nt;
+    int first = 0, nt = nt_all;
+    if (p.qt_begin > 0 || p.qt_end < tiles_all) {  // (a chain of dependent global loads: only when the range is a part)
+        nt = 0;
+        while (first < nt_all && (word_g(first) & 0x7fff) < p.qt_begin) ++first;
+        while (first + nt < nt_all && (word_g(first + nt) & 0x7fff) < p.qt_end) ++nt;
+    }
     float *dk_row = p.dk + ((size_t)zh * N + jrow) * GA_D + grp * 16;
     float *dv_row = p.dv + ((size_t)zh * N + jrow) * GA_D + grp * 16;
     if (k_info < 0 || nt == 0) {  // no valid key here, or no query to hear from: zeros
@@ -307,6 +306,24 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     // ---- set-up ------------------------------------------------------------------------------------
     if (is_producer) {
         if (lane == 0) {
+            if (!fresh) {
+                mbar_inval(&sm.bar_kv);
+                mbar_inval(&sm.bar_pds);
+                mbar_inval(&sm.bar_vk);
+                mbar_inval(&sm.bar_dq);
+                mbar_inval(&sm.bar_dqr);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    mbar_inval(&sm.bar_qdo[b]);
+                    mbar_inval(&sm.bar_sp[b]);
+                    mbar_inval(&sm.bar_spfree[b]);
+                }
+#pragma unroll
+                for (int b = 0; b < GA_ROW_BUFS; ++b) {
+                    mbar_inval(&sm.bar_rows[b]);
+                    mbar_inval(&sm.bar_rowsfree[b]);
+                }
+            }
             mbar_init(&sm.bar_kv, 1);
             mbar_init(&sm.bar_qdo[0], 1);
             mbar_init(&sm.bar_qdo[1], 1);
@@ -335,11 +352,8 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 tma_load_3d(sm.q[t], &map_q, 0, i0, zh_local, &sm.bar_qdo[t]);
                 tma_load_3d(sm.dout[t], &map_do, 0, i0, zh_local, &sm.bar_qdo[t]);
             }
-            sm.abort = 0;
         }
         __syncwarp();
-        tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
-        tmem_relinquish();
     }
     // Per-query inputs of four queries per stager lane (queries lane + 32 m of a tile): the loads are issued at once
     // from clamped indices, none waits for the validity bytes.
@@ -381,6 +395,7 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (is_stager) row_load(word_g(first) & 0x7fff, rl);  // in flight across the barrier
     tc_fence_before();
     __syncthreads();  // barriers initialised, TMEM allocated, tile list in place
+    fresh = false;
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
     // two stages of S^T [0,64) [64,128) and dP^T [128,192) [192,256) (sub-tile u uses stage u & 1), P^T [256,288), dV [320,384),
@@ -656,7 +671,60 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
             if (p.dbeta) atomicAdd(p.dbeta + h, totb * p.scale);
         }
     }
-    if (is_producer) tmem_dealloc(tmem, GA_BWD_TMEM_COLS);
+}
+
+// Grid without a schedule: one CTA per (key tile, (batch, head) pair), the samples longest first when the plan's order
+// applies.  With a schedule (geoattn_plan.cuh): `bins` persistent CTAs, each working through the items assigned to it and
+// writing the zeros of its share of the key tiles without a valid key.
+template <int FORM>
+__global__ void __launch_bounds__(GA_BWD_THREADS, 1)
+geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do, const GaBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    GaBwdSmem &sm = *reinterpret_cast<GaBwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5;
+    if (warp == GA_BWD_MATH_THREADS / 32) {
+        if (threadIdx.x == GA_BWD_MATH_THREADS) sm.abort = 0;
+        __syncwarp();
+        tmem_alloc(&sm.tmem_base, GA_BWD_TMEM_COLS);
+        tmem_relinquish();
+    }
+    // one loop (and one copy of the item's code) for both kinds of launch
+    int n_dead = 0, n_live = 1, bins = 1;
+    const int *dead = nullptr, *items = nullptr;
+    if (p.sched != nullptr) {
+        bins = p.sched[0];
+        n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
+        n_live = ga_sched_count(p.sched)[blockIdx.x];
+        dead = ga_sched_dead(p.sched);
+        items = ga_sched_items(p.sched, blockIdx.x);
+    }
+    bool fresh = true;  // the barriers have not been initialised yet
+#pragma unroll 1
+    for (int k = 0; k < n_dead + n_live; ++k) {
+        int zh_local, tile;
+        if (p.sched == nullptr) {
+            zh_local = blockIdx.y;  // index into the shard of (batch, head) pairs
+            tile = blockIdx.x;
+            if (p.use_order) {      // samples longest first: the short ones fill the tail of the launch
+                const int zp = zh_local / p.H;
+                zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
+            }
+        } else {
+            const int item = k < n_dead ? dead[blockIdx.x + k * bins] : items[k - n_dead];
+            zh_local = item >> 10;
+            tile = item & 1023;
+        }
+        geoattn_bwd_item<FORM>(sm, map_q, map_k, map_v, map_do, p, zh_local, tile, fresh);
+        if (!fresh) {
+            __syncthreads();  // (after a live item: thread 0 has read the item's partial sums; sm.abort is settled)
+            if (sm.abort) break;
+        }
+    }
+    // (a CTA that ran no live item has not synchronised since the allocation)
+    tc_fence_before();
+    __syncthreads();
+    if (warp == GA_BWD_MATH_THREADS / 32) tmem_dealloc(sm.tmem_base, GA_BWD_TMEM_COLS);
 }
 
 }  // namespace pai

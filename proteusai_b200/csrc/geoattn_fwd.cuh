@@ -91,6 +91,7 @@ struct GaFwdParams {
     int q_begin;           // first query row of the launch (a multiple of 128); blockIdx.x counts tiles from it
     int use_order;         // issue the samples in the plan's longest-first order (full sample range only)
     int far_skip;          // skip the RBF arithmetic of far key groups
+    const int *sched;      // balanced schedule (geoattn_plan.cuh) or nullptr: one CTA per item
     float scale;
     // logit form: 0 = S (1 + R);  1 = S + beta Rn |S| with Rn = 2 (R - min_rbf) / (max_rbf - min_rbf) - 1 and pairs
     // with R outside [min_rbf, max_rbf] masked out (the form of old/old_scripts/attn/geometric_attn.py:193-201)
@@ -277,26 +278,21 @@ __device__ __forceinline__ float ga_sr_chunk(uint32_t (&s)[32], const uint32_t (
     return m_loc;
 }
 
+// One work item: the query tile `q_tile` (counted from q_begin) of the (batch, head) pair `zh_local` of the launch.  Every
+// thread of the CTA calls it; tensor memory is allocated by the caller.  `fresh`: the CTA has not initialised its barriers
+// yet; a live item clears it, later ones invalidate the barriers before they initialise them again.
 template <int FORM>
-__global__ void __launch_bounds__(GA_FWD_THREADS, 2)
-geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const GaFwdParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    GaFwdSmem &sm = *reinterpret_cast<GaFwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+__device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMap &map_q, const CUtensorMap &map_k, const CUtensorMap &map_v,
+                                                 const GaFwdParams &p, int zh_local, int q_tile, bool &fresh) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool is_math = warp < GA_FWD_MATH_THREADS / 32;
     const bool is_producer = warp == GA_FWD_MATH_THREADS / 32, is_stager = warp == GA_FWD_MATH_THREADS / 32 + 1;
     const int r = tid & (GA_BM - 1);              // math threads: query row inside the tile = TMEM lane
     const int N = p.N;
     const int tiles_all = (N + GA_BN - 1) / GA_BN;
-    int zh_local = blockIdx.y;                    // index into the shard of (batch, head) pairs
-    if (p.use_order) {  // samples longest first: the short ones fill the tail of the launch
-        const int zp = zh_local / p.H;
-        zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
-    }
     const int zh = p.zh_begin + zh_local;
     const int z = zh / p.H, h = zh - z * p.H;
-    const int i0 = p.q_begin + blockIdx.x * GA_BM;
+    const int i0 = p.q_begin + q_tile * GA_BM;
     const int row = i0 + r;
     const float *cz = p.coords + (size_t)z * N * 3;
     const uint8_t *vz = p.valid ? p.valid + (size_t)z * N : nullptr;
@@ -322,6 +318,26 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int nbox = (nw + 1) >> 1;  // TMA boxes of 64 keys
     if (is_producer) {
         if (lane == 0) {
+            if (!fresh) {
+                mbar_inval(&sm.bar_q);
+                mbar_inval(&sm.bar_o[0]);
+                mbar_inval(&sm.bar_o[1]);
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+                    mbar_inval(&sm.bar_k[b]);
+                    mbar_inval(&sm.bar_v[b]);
+                    mbar_inval(&sm.bar_kfree[b]);
+                    mbar_inval(&sm.bar_vfree[b]);
+                    mbar_inval(&sm.bar_s[b]);
+                    mbar_inval(&sm.bar_sfree[b]);
+                    mbar_inval(&sm.bar_p[b]);
+                }
+#pragma unroll
+                for (int b = 0; b < GA_KC_BUFS; ++b) {
+                    mbar_inval(&sm.bar_kc[b]);
+                    mbar_inval(&sm.bar_kcfree[b]);
+                }
+            }
             mbar_init(&sm.bar_q, 1);
 #pragma unroll
             for (int b = 0; b < 2; ++b) {
@@ -351,11 +367,8 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 mbar_expect_tx(&sm.bar_v[j], GA_STEP_BYTES);
                 tma_load_4d(sm.v[j], &map_v, 0, j0, h, z, &sm.bar_v[j]);
             }
-            sm.abort = 0;
         }
         __syncwarp();
-        tmem_alloc(&sm.tmem_base, GA_TMEM_COLS);
-        tmem_relinquish();
     }
     for (int t = tid; t < nt; t += GA_FWD_THREADS) sm.tiles[t] = (uint16_t)tile_word_g(t);
     auto tile_word = [&](int t) -> int { return (int)sm.tiles[t]; };  // (published by the barrier below)
@@ -405,6 +418,7 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     if (is_stager) key_load(tile_word_g(0) & 0x7fff, kl);  // in flight across the barrier
     tc_fence_before();
     __syncthreads();  // barriers initialised, TMEM allocated, tile list and the queries' geometry operand in place
+    fresh = false;
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
     const uint32_t tmem_s = tmem;          // columns [0,64): S of units w (even) and w + 1 (odd), 32 each
@@ -449,6 +463,12 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 mbar_expect_tx(&sm.bar_v[b], GA_STEP_BYTES);
                 tma_load_4d(sm.v[b], &map_v, 0, j0, h, z, &sm.bar_v[b]);
             }
+        }
+        // the commits behind the last S and P V MMAs also arrive on the buffers' release barriers: see them land before the
+        // item ends (the barriers are re-initialised for the CTA's next item)
+        for (int b = 0; ok && b < 2; ++b) {
+            const int nb = (nbox + 1 - b) >> 1;  // boxes that went through buffer b
+            if (nb > 0) ok = wait_w(&sm.bar_kfree[b], (uint32_t)((nb - 1) & 1)) && wait_w(&sm.bar_vfree[b], (uint32_t)((nb - 1) & 1));
         }
         if (lane == 0 && (!ok || *abort_flag)) {
             // Gave up: the copies already issued may still be landing in this CTA's shared memory.  Wait for
@@ -670,8 +690,61 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
     }
     tc_fence_before();
+    __syncthreads();  // every role has left the item: its barriers, buffers and tensor-memory columns can be reused
+}
+
+// Grid without a schedule: one CTA per (query tile, (batch, head) pair), the samples longest first when the plan's order
+// applies.  With a schedule (geoattn_plan.cuh): `bins` persistent CTAs, each working through the items assigned to it and
+// writing the zeros of its share of the tiles without a valid query.
+template <int FORM>
+__global__ void __launch_bounds__(GA_FWD_THREADS, 2)
+geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const GaFwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    GaFwdSmem &sm = *reinterpret_cast<GaFwdSmem *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5;
+    if (warp == GA_FWD_MATH_THREADS / 32) {
+        if (threadIdx.x == GA_FWD_MATH_THREADS) sm.abort = 0;
+        __syncwarp();
+        tmem_alloc(&sm.tmem_base, GA_TMEM_COLS);
+        tmem_relinquish();
+    }
+    // one loop (and one copy of the item's code) for both kinds of launch
+    int n_dead = 0, n_live = 1, bins = 1;
+    const int *dead = nullptr, *items = nullptr;
+    if (p.sched != nullptr) {
+        bins = p.sched[0];
+        n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
+        n_live = ga_sched_count(p.sched)[blockIdx.x];
+        dead = ga_sched_dead(p.sched);
+        items = ga_sched_items(p.sched, blockIdx.x);
+    }
+    bool fresh = true;  // the barriers have not been initialised yet
+#pragma unroll 1
+    for (int k = 0; k < n_dead + n_live; ++k) {
+        int zh_local, tile;
+        if (p.sched == nullptr) {
+            zh_local = blockIdx.y;  // index into the shard of (batch, head) pairs
+            tile = blockIdx.x;
+            if (p.use_order) {      // samples longest first: the short ones fill the tail of the launch
+                const int zp = zh_local / p.H;
+                zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
+            }
+        } else {
+            const int item = k < n_dead ? dead[blockIdx.x + k * bins] : items[k - n_dead];
+            zh_local = item >> 10;
+            tile = item & 1023;
+        }
+        geoattn_fwd_item<FORM>(sm, map_q, map_k, map_v, p, zh_local, tile, fresh);
+        if (!fresh) {
+            __syncthreads();  // (after a live item: thread 0 has read the item's partial sums; sm.abort is settled)
+            if (sm.abort) break;
+        }
+    }
+    // (a CTA that ran no live item has not synchronised since the allocation)
+    tc_fence_before();
     __syncthreads();
-    if (is_producer) tmem_dealloc(tmem, GA_TMEM_COLS);
+    if (warp == GA_FWD_MATH_THREADS / 32) tmem_dealloc(sm.tmem_base, GA_TMEM_COLS);
 }
 
 }  // namespace pai

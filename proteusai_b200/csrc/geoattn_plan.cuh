@@ -108,4 +108,135 @@ __global__ void __launch_bounds__(256) geoattn_plan_kernel(const uint8_t *valid,
     }
 }
 
+// ---- balanced schedule ------------------------------------------------------------------------------
+// The attention kernels' work items are (sample, head, 128-token tile) triples whose cost grows with the sample's
+// number of non-empty tiles.  A grid with one CTA per item leaves the pairing of long and short items on an SM to
+// the order in which SMs happen to fall free; on a batch of mixed lengths the busiest SM then carries a third more
+// than the average.  The schedule packs the live items into `bins` persistent CTAs beforehand so that the fullest
+// carries as little as possible (every item also pays a fixed set-up cost).  Tiles without a
+// valid token only need zeros written: they are listed separately and shared out round-robin.
+//
+// Layout (int32 words):
+//   [0] bins  [1] H  [2] Z  [3] N  [4] cap = slots per bin  [5] number of dead items  [6] number of live items  [7] capacity found
+//   count[bins]          live items of the bin
+//   items[bins][cap]     (sample * H + head) << 10 | tile
+//   dead [Z * H * T]     the first [5] entries: dead items, same packing
+constexpr int GA_SCHED_HEADER = 8;
+constexpr int GA_SCHED_MAX_BINS = 1024;
+__host__ __device__ inline int ga_sched_cap(int Z, int N, int H, int bins) {
+    const long long items = (long long)Z * H * ga_plan_tiles_per_sample(N);
+    return (int)(4 * ((items + bins - 1) / bins) + 8);
+}
+__host__ __device__ inline size_t ga_sched_words(int Z, int N, int H, int bins) {
+    return (size_t)GA_SCHED_HEADER + (size_t)bins + (size_t)bins * ga_sched_cap(Z, N, H, bins) +
+           (size_t)Z * H * ga_plan_tiles_per_sample(N);
+}
+__host__ __device__ inline const int *ga_sched_count(const int *sched) { return sched + GA_SCHED_HEADER; }
+__host__ __device__ inline const int *ga_sched_items(const int *sched, int bin) {
+    return sched + GA_SCHED_HEADER + sched[0] + (size_t)bin * sched[4];
+}
+__host__ __device__ inline const int *ga_sched_dead(const int *sched) {
+    return sched + GA_SCHED_HEADER + sched[0] + (size_t)sched[0] * sched[4];
+}
+
+// One CTA of 1024 threads; thread b keeps the load of bin b.  `tile_cost`, `item_cost`: cost of one non-empty tile
+// of the sample and fixed cost of an item, in the same (arbitrary) unit.
+// The items are packed by first fit, longest first, into bins of capacity C, and C is bisected down to the smallest
+// capacity for which every item finds a bin (MULTIFIT).  With `pair` the bins of the packing are SMs that run two
+// CTAs each: the items of SM b are dealt, longest first, to the lighter of CTAs b and b + bins / 2 (the launch
+// places them on one SM when it fills the machine in order; if it does not, only the balance suffers).
+__global__ void __launch_bounds__(1024) geoattn_schedule_kernel(const int *plan, int *sched, int Z, int N, int H, int bins, int tile_cost,
+                                                                int item_cost, int pair) {
+    __shared__ unsigned int best[2][32];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int T = ga_plan_tiles_per_sample(N);
+    const int cap = ga_sched_cap(Z, N, H, bins);
+    const int nb = pair ? bins / 2 : bins;  // bins of the packing
+    int *count = sched + GA_SCHED_HEADER, *items = count + bins, *dead = items + (size_t)bins * cap;
+    const int *order = ga_plan_order(plan), *cnt = ga_plan_count(plan, Z);
+    // totals: lower bound of the capacity
+    long long total = 0;
+    int biggest = 0, n_live = 0, n_dead = 0;
+    for (int s = 0; s < Z; ++s) {
+        const int z = order[s], c = cnt[z];
+        const int cost = c * tile_cost + item_cost;
+        n_live += c * H;
+        n_dead += (T - c) * H;
+        total += (long long)c * H * cost;
+        if (c > 0) biggest = max(biggest, cost);
+    }
+    unsigned int lo = (unsigned int)max((long long)biggest, (total + nb - 1) / nb), hi = 2 * lo + 1;  // first fit never needs more than 2 x optimum
+    int it = 0;
+    // pass < 12: bisection (nothing is written); the last pass packs with the capacity found and writes the lists
+    for (int pass = 0; pass <= 12; ++pass) {
+        const bool last = pass == 12;
+        const unsigned int C = last ? hi : (lo + hi) / 2;
+        unsigned int load = 0, load2[2] = {0, 0};
+        int mine = 0, mine2[2] = {0, 0}, nd = 0;
+        bool fail = false;
+        for (int s = 0; s < Z && !fail; ++s) {  // samples, longest first
+            const int z = order[s], c = cnt[z];
+            const int *info = ga_plan_info(plan, Z, N, z);
+            const unsigned int cost = (unsigned int)(c * tile_cost + item_cost);
+            for (int h = 0; h < H && !fail; ++h)
+                for (int x = 0; x < T; ++x) {
+                    const int item = ((z * H + h) << 10) | x;
+                    if (info[x] < 0) {
+                        if (last && tid == 0) dead[nd] = item;
+                        ++nd;
+                        continue;
+                    }
+                    // the first bin with room (a full list does not bid)
+                    unsigned int key = 0xffffffffu;
+                    if (tid < nb && mine < (pair ? 2 * cap - 2 : cap)) {
+                        if (load + cost <= C) key = (unsigned int)tid;
+                        else if (last) key = 0x80000000u | (unsigned int)tid;  // (never leave an item out: any list with a free slot)
+                    }
+                    key = __reduce_min_sync(0xffffffffu, key);
+                    if (lane == 0) best[it & 1][warp] = key;
+                    __syncthreads();
+                    unsigned int k = best[it & 1][lane];
+                    k = __reduce_min_sync(0xffffffffu, k);
+                    ++it;
+                    if (k == 0xffffffffu) {  // (the same for every thread)
+                        fail = true;
+                        break;
+                    }
+                    if ((int)(k & 0x7fffffffu) == tid) {
+                        ++mine;
+                        load += cost;
+                        if (last) {
+                            const int half = (pair && load2[1] < load2[0] && mine2[1] < cap) || (pair && mine2[0] >= cap) ? 1 : 0;
+                            items[(size_t)(tid + half * nb) * cap + mine2[half]] = item;
+                            ++mine2[half];
+                            load2[half] += cost;
+                        }
+                    }
+                }
+        }
+        if (last) {
+            if (tid < nb) {
+                count[tid] = mine2[0];
+                if (pair) count[tid + nb] = mine2[1];
+            }
+            if (pair && (bins & 1) && tid == 0) count[bins - 1] = 0;
+        } else if (fail) {
+            lo = C + 1;
+        } else {
+            hi = C;
+        }
+        if (!last && lo >= hi) pass = 11;  // converged: the next pass is the last
+    }
+    if (tid == 0) {
+        sched[0] = bins;
+        sched[1] = H;
+        sched[2] = Z;
+        sched[3] = N;
+        sched[4] = cap;
+        sched[5] = n_dead;
+        sched[6] = n_live;
+        sched[7] = (int)hi;
+    }
+}
+
 }  // namespace pai

@@ -97,7 +97,7 @@ class GeoPlan:
     """Per-mask data shared by every attention call of a batch: the validity bytes the kernels read and the
     batch plan (non-empty 128-token tiles per sample, samples longest first) made by ``pai_geoattn_plan``."""
 
-    __slots__ = ("mask", "version", "valid", "plan")
+    __slots__ = ("mask", "version", "valid", "plan", "schedules")
 
     def __init__(self, mask):
         self.mask, self.version = mask, mask._version
@@ -109,6 +109,25 @@ class GeoPlan:
         with torch.cuda.device(mask.device):
             _lib.check(lib.pai_geoattn_plan(_lib.ptr(self.valid), batch, n, _lib.ptr(self.plan), nbytes, _lib.current_stream()),
                        "pai_geoattn_plan")
+        self.schedules = {}
+
+    def schedule(self, nheads, backward):
+        """``(tensor, bins)``: the balanced assignment of this plan's work items to persistent CTAs for ``nheads`` heads
+        (``pai_geoattn_schedule``), made on first use; two CTAs per SM for the forward, one for the backward."""
+        key = (int(nheads), bool(backward))
+        hit = self.schedules.get(key)
+        if hit is None:
+            batch, n = self.mask.shape
+            sms = torch.cuda.get_device_properties(self.plan.device).multi_processor_count
+            bins = min(sms * (1 if backward else 2), 1024)
+            lib = _lib.lib()
+            nbytes = lib.pai_geoattn_schedule_bytes(batch, n, nheads, bins)
+            sched = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=self.plan.device)
+            with torch.cuda.device(self.plan.device):
+                _lib.check(lib.pai_geoattn_schedule(_lib.ptr(self.plan), batch, n, nheads, bins, 1 if backward else 0, _lib.ptr(sched),
+                                                    nbytes, _lib.current_stream()), "pai_geoattn_schedule")
+            hit = self.schedules[key] = (sched, bins)
+        return hit
 
 
 _plans = OrderedDict()  # (data_ptr, shape, device) -> GeoPlan; the entry keeps its mask alive, so the address cannot be reused
@@ -165,6 +184,9 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
     gp = geoattn_plan(mask)
+    # the whole problem in one call: use the balanced schedule of persistent CTAs
+    whole = gp is not None and zh_begin == 0 and zh_end == batch * nheads and q_begin == 0 and q_end == n
+    sched, bins = gp.schedule(nheads, False) if whole else (None, 0)
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
     if out is None:
         if out_layout == "znhd":
@@ -178,7 +200,8 @@ def geoattn_forward(Q, K, V, coords, spreads, mask=None, zh_begin=0, zh_end=None
     with torch.cuda.device(dev):
         _lib.check(_lib.lib().pai_geoattn_fwd_strided(
             _lib.ptr(Q), _strides3(Q), _lib.ptr(K), _strides3(K), _lib.ptr(V), _strides3(V), _lib.ptr(coords), _lib.ptr(sigma),
-            _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(out), _strides3(out),
+            _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(sched), bins, _lib.ptr(out),
+            _strides3(out),
             _lib.ptr(lse), batch, nheads, n, d_k, float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf),
             float(max_rbf), _FORMS[form], zh_begin, zh_end, q_begin, q_end, _lib.current_stream()), "pai_geoattn_fwd_strided")
     return out, lse
@@ -197,6 +220,8 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
     coords = coords.to(torch.float32).contiguous()
     sigma = spreads.detach().to(torch.float32).contiguous()
     gp = geoattn_plan(mask)
+    whole = gp is not None and zh_begin == 0 and zh_end == batch * nheads and q_begin == 0 and q_end == n
+    sched, bins = gp.schedule(nheads, True) if whole else (None, 0)
     dq, dk, dv = (torch.empty(batch, nheads, n, d_k, dtype=torch.float32, device=dev) for _ in range(3))
     dsig = torch.empty(nheads, dtype=torch.float32, device=dev)
     beta = None if betas is None else betas.detach().to(torch.float32).contiguous()
@@ -207,8 +232,8 @@ def geoattn_backward(Q, K, V, O, dO, lse, coords, spreads, mask=None, zh_begin=0
     with torch.cuda.device(dev):
         _lib.check(lib.pai_geoattn_bwd(
             _lib.ptr(Q), _lib.ptr(K), _lib.ptr(V), _lib.ptr(O), _lib.ptr(dO), _lib.ptr(lse), _lib.ptr(coords),
-            _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(dq),
-            _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig), _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k,
+            _lib.ptr(sigma), _lib.ptr(beta), _lib.ptr(gp.valid) if gp else None, _lib.ptr(gp.plan) if gp else None, _lib.ptr(sched), bins,
+            _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(dsig), _lib.ptr(dbeta), _lib.ptr(ws), ws_bytes, batch, nheads, n, d_k,
             float(scale) if scale is not None else 1.0 / (d_k ** 0.5), float(min_rbf), float(max_rbf), _FORMS[form], zh_begin,
             zh_end, q_begin, q_end, _lib.current_stream()), "pai_geoattn_bwd")
     if form == "beta_abs":

@@ -92,7 +92,8 @@ def test_dropin_aliases():
 def test_geoattn_argument_errors(lib):
     p = ctypes.c_void_p(0x1000)
     f = lib.pai_geoattn_fwd
-    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), kw.get("valid", None), kw.get("plan", None), p, p,
+    args = lambda **kw: [kw.get("Q", p), p, p, p, p, kw.get("betas", p), kw.get("valid", None), kw.get("plan", None),
+                         kw.get("sched", None), kw.get("bins", 0), p, p,
                          kw.get("Z", 2), kw.get("H", 2), kw.get("N", 256), kw.get("d", 64), 0.125, kw.get("lo", 0.0), kw.get("hi", 1.0),
                          kw.get("form", 0), kw.get("zb", 0), kw.get("ze", 4), kw.get("qb", 0), kw.get("qe", 256), None]
     assert f(*args(Q=None)) == -1
@@ -110,22 +111,25 @@ def test_geoattn_argument_errors(lib):
     assert f(*args(Q=ctypes.c_void_p(0x1008))) == -3
     assert f(*args(valid=p)) == -1        # a mask needs the plan made from it
     assert f(*args(valid=p, plan=ctypes.c_void_p(0x1004))) == -3
+    assert f(*args(valid=p, plan=p, sched=p, bins=0)) == -2              # a schedule names its number of CTAs
+    assert f(*args(valid=p, plan=p, sched=p, bins=296, qe=128)) == -6    # ... and covers the whole problem
+    assert f(*args(valid=p, plan=p, sched=ctypes.c_void_p(0x1004), bins=296)) == -3
     g = lib.pai_geoattn_bwd
     need = lib.pai_geoattn_bwd_workspace_bytes(2, 2, 64, 64)
     assert need == 2 * 2 * 64 * 4
-    base = [p] * 8 + [p, None, None] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, 0, 64, None]
+    base = [p] * 8 + [p, None, None, None, 0] + [p] * 5 + [p, need, 2, 2, 64, 64, 0.125, 0.0, 1.0, 0, 0, 4, 0, 64, None]
     bad = list(base)
-    bad[17] = need - 1
+    bad[19] = need - 1
     assert g(*bad) == -5
     bad = list(base)
     bad[0] = None
     assert g(*bad) == -1
     bad = list(base)
-    bad[25] = 1      # logit form 1 ...
-    bad[15] = None   # ... without a dbetas buffer
+    bad[27] = 1      # logit form 1 ...
+    bad[17] = None   # ... without a dbetas buffer
     assert g(*bad) == -1
     bad = list(base)
-    bad[28] = 32     # query range off the tile grid
+    bad[30] = 32     # query range off the tile grid
     assert g(*bad) == -6
     # the batch plan
     nbytes = lib.pai_geoattn_plan_bytes(4, 1000)
@@ -137,6 +141,15 @@ def test_geoattn_argument_errors(lib):
     assert h(p, 0, 1000, p, nbytes, None) == -2
     assert h(p, 4, 1000, ctypes.c_void_p(0x1004), nbytes, None) == -3
     assert lib.pai_tune_set(999, 1) == -4
+    # the balanced schedule
+    sbytes = lib.pai_geoattn_schedule_bytes(4, 1000, 8, 296)
+    assert sbytes == 4 * (8 + 296 + 296 * (4 * ((4 * 8 * 8 + 295) // 296) + 8) + 4 * 8 * 8)
+    assert lib.pai_geoattn_schedule_bytes(4, 1000, 8, 2000) == 0
+    k = lib.pai_geoattn_schedule
+    assert k(None, 4, 1000, 8, 296, 0, p, sbytes, None) == -1
+    assert k(p, 4, 1000, 8, 0, 0, p, sbytes, None) == -2
+    assert k(p, 4, 1000, 8, 296, 0, p, sbytes - 1, None) == -5
+    assert k(p, 4, 1000, 8, 296, 0, ctypes.c_void_p(0x1004), sbytes, None) == -3
 
 
 def test_strided_attention_and_row_op_argument_errors(lib):
@@ -144,7 +157,7 @@ def test_strided_attention_and_row_op_argument_errors(lib):
     i64 = lambda *v: (ctypes.c_int64 * 3)(*v)
     ok = i64(2 * 64 * 64, 64 * 64, 64)
     f = lib.pai_geoattn_fwd_strided
-    call = lambda **kw: f(p, kw.get("qs", ok), p, ok, p, ok, p, p, None, None, None, p, kw.get("os", ok), p, 2, 2, 64,
+    call = lambda **kw: f(p, kw.get("qs", ok), p, ok, p, ok, p, p, None, None, None, None, 0, p, kw.get("os", ok), p, 2, 2, 64,
                           kw.get("d", 64), 0.125, 0.0, 1.0, 0, 0, kw.get("ze", 4), 0, 64, None)
     assert call(qs=None) == -1
     assert call(d=32) == -4
