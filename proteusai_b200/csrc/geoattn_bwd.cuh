@@ -56,6 +56,7 @@ struct GaBwdSmem {
     alignas(1024) uint8_t dout[2][GA_TILE_BYTES];
     alignas(1024) uint8_t ds[2][2 * GA_TILE_BYTES];  // dS^T [128 keys x 128 queries] bf16: two [128 x 64] swizzled sub-tiles
     GaQueryRows rows[GA_ROW_BUFS];
+    alignas(16) float stage[GA_BWD_MATH_THREADS / 32][32 * 16];  // per-warp staging of outgoing rows (ga_warp_rows_out)
     uint16_t tiles[GA_MAX_TILES];          // live query tiles of the range; bit 15: the tile also holds a padded query
     uint64_t bar_kv, bar_qdo[2], bar_sp[2], bar_spfree[2], bar_pds, bar_vk, bar_dq, bar_dqr, bar_rows[GA_ROW_BUFS], bar_rowsfree[GA_ROW_BUFS];
     uint32_t tmem_base;
@@ -108,6 +109,30 @@ __global__ void __launch_bounds__(256) geoattn_bwd_prep_kernel(const __nv_bfloat
 
 __device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// A warp holds 32 rows x 16 fp32 (one row and 64 B per lane) bound for global rows 256 B apart.  Written lane by lane,
+// every store or reduction instruction would touch 32 sectors and fill half of each.  The block goes through 2 KiB of
+// shared memory instead (16-byte pieces swizzled by (row >> 1) & 3: conflict-free both ways) and leaves with four lanes
+// on the 64 B of one row: 8 rows, 16 whole sectors an instruction.  `dst`: row 0 of the block at the warp's column
+// offset; rows >= rows_valid are not written.
+template <bool REDUCE>
+__device__ __forceinline__ void ga_warp_rows_out(float *stage, const uint32_t (&v)[16], int lane, float *dst, int rows_valid) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4 *>(stage + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) = make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = (lane >> 2) + 8 * i, piece = lane & 3;
+        const float4 x = *reinterpret_cast<const float4 *>(stage + row * 16 + ((piece ^ ((row >> 1) & 3)) << 2));
+        if (row < rows_valid) {
+            float *g = dst + (size_t)row * GA_D + piece * 4;
+            if (REDUCE) red_add_v4(g, x.x, x.y, x.z, x.w);
+            else *reinterpret_cast<float4 *>(g) = x;
+        }
+    }
+    __syncwarp();  // the staging block may be rewritten
 }
 
 struct GaBwdKey {  // per-thread constants of the thread's key (centred coordinates k)
@@ -557,14 +582,8 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&sm.bar_dqr);
-            const int row = (tile_word(t) & 0x7fff) * GA_BM + r;
-            if (row < N) {
-                float *dst = p.dq + ((size_t)zh * N + row) * GA_D + grp * 16;
-#pragma unroll
-                for (int e = 0; e < 16; e += 4)
-                    red_add_v4(dst + e, __uint_as_float(v[e]), __uint_as_float(v[e + 1]), __uint_as_float(v[e + 2]),
-                               __uint_as_float(v[e + 3]));
-            }
+            const int row0 = (tile_word(t) & 0x7fff) * GA_BM + (warp & 3) * 32;  // first query row of this warp's block
+            ga_warp_rows_out<true>(sm.stage[warp], v, lane, p.dq + ((size_t)zh * N + row0) * GA_D + grp * 16, N - row0);
         };
 
 #pragma unroll 1
@@ -629,14 +648,11 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
             tmem_ld16(tm_dv + lane_base + grp * 16, a);
             tmem_ld16(tm_dk + lane_base + grp * 16, b);
             tmem_wait_ld();
-            if (jrow < N) {
-#pragma unroll
-                for (int e = 0; e < 16; e += 4) {
-                    // a padded key row holds exact zeros (its P and dS were selected to 0)
-                    *reinterpret_cast<uint4 *>(dv_row + e) = make_uint4(a[e], a[e + 1], a[e + 2], a[e + 3]);
-                    *reinterpret_cast<uint4 *>(dk_row + e) = make_uint4(b[e], b[e + 1], b[e + 2], b[e + 3]);
-                }
-            }
+            // (a padded key row holds exact zeros: its P and dS were selected to 0)
+            const int row0 = j0 + (warp & 3) * 32;
+            const size_t off = ((size_t)zh * N + row0) * GA_D + grp * 16;
+            ga_warp_rows_out<false>(sm.stage[warp], a, lane, p.dv + off, N - row0);
+            ga_warp_rows_out<false>(sm.stage[warp], b, lane, p.dk + off, N - row0);
         }
         float d0, d1, b0, b1;
         f2_unpack(dsig2, d0, d1);
@@ -690,18 +706,15 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_relinquish();
     }
     // one loop (and one copy of the item's code) for both kinds of launch
-    int n_dead = 0, n_live = 1, bins = 1;
-    const int *dead = nullptr, *items = nullptr;
+    // (little state is kept across an item: the lists are looked up again for every item)
+    int total = 1;
     if (p.sched != nullptr) {
-        bins = p.sched[0];
-        n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
-        n_live = ga_sched_count(p.sched)[blockIdx.x];
-        dead = ga_sched_dead(p.sched);
-        items = ga_sched_items(p.sched, blockIdx.x);
+        const int bins = p.sched[0];
+        total = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins + ga_sched_count(p.sched)[blockIdx.x];
     }
     bool fresh = true;  // the barriers have not been initialised yet
 #pragma unroll 1
-    for (int k = 0; k < n_dead + n_live; ++k) {
+    for (int k = 0; k < total; ++k) {
         int zh_local, tile;
         if (p.sched == nullptr) {
             zh_local = blockIdx.y;  // index into the shard of (batch, head) pairs
@@ -711,7 +724,9 @@ geoattn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
             }
         } else {
-            const int item = k < n_dead ? dead[blockIdx.x + k * bins] : items[k - n_dead];
+            const int bins = p.sched[0];
+            const int n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
+            const int item = k < n_dead ? ga_sched_dead(p.sched)[blockIdx.x + k * bins] : ga_sched_items(p.sched, blockIdx.x)[k - n_dead];
             zh_local = item >> 10;
             tile = item & 1023;
         }

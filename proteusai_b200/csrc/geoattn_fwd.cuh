@@ -710,18 +710,15 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tmem_relinquish();
     }
     // one loop (and one copy of the item's code) for both kinds of launch
-    int n_dead = 0, n_live = 1, bins = 1;
-    const int *dead = nullptr, *items = nullptr;
+    // (little state is kept across an item: the lists are looked up again for every item)
+    int total = 1;
     if (p.sched != nullptr) {
-        bins = p.sched[0];
-        n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
-        n_live = ga_sched_count(p.sched)[blockIdx.x];
-        dead = ga_sched_dead(p.sched);
-        items = ga_sched_items(p.sched, blockIdx.x);
+        const int bins = p.sched[0];
+        total = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins + ga_sched_count(p.sched)[blockIdx.x];
     }
     bool fresh = true;  // the barriers have not been initialised yet
 #pragma unroll 1
-    for (int k = 0; k < n_dead + n_live; ++k) {
+    for (int k = 0; k < total; ++k) {
         int zh_local, tile;
         if (p.sched == nullptr) {
             zh_local = blockIdx.y;  // index into the shard of (batch, head) pairs
@@ -731,7 +728,9 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                 zh_local = ga_plan_order(p.plan)[zp] * p.H + (zh_local - zp * p.H);
             }
         } else {
-            const int item = k < n_dead ? dead[blockIdx.x + k * bins] : items[k - n_dead];
+            const int bins = p.sched[0];
+            const int n_dead = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins;  // this CTA's share of the tiles that only need zeros
+            const int item = k < n_dead ? ga_sched_dead(p.sched)[blockIdx.x + k * bins] : ga_sched_items(p.sched, blockIdx.x)[k - n_dead];
             zh_local = item >> 10;
             tile = item & 1023;
         }
