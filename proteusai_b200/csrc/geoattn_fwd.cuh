@@ -7,8 +7,8 @@
 // instantiation (FORM = 1).
 //
 // One CTA = 128 query rows of one (batch, head): four math warps (one thread per query row = TMEM lane, so a row
-// needs no exchange between threads) and four helper warps: one thread issues the S and G MMAs, one the P V MMAs, one the
-// TMA loads of K and V, and a whole warp stages the keys' geometry.  Two CTAs share an SM.  Keys are taken 32 at a time (a "unit"; four
+// needs no exchange between threads) and three helper warps: one thread issues the MMAs, one the TMA loads of K and V, and
+// a whole warp stages the keys' geometry.  Two CTAs share an SM.  Keys are taken 32 at a time (a "unit"; four
 // units per 128-key tile of the batch plan, two per 64-key TMA box), and every per-unit buffer in tensor memory is
 // doubled, so the tensor core works on unit w + 1 while the math warps hold unit w:
 // Tensor memory (256 columns): S 2 x [32] fp32 at 0, G 2 x [32] fp32 at 64, O [64] fp32 at 128, P 2 x [16] bf16 pairs at 192.
@@ -50,7 +50,7 @@ constexpr int GA_UNIT = 32; // keys per unit of the forward
 constexpr int GA_D = 64;    // head dimension
 constexpr int GA_MAX_TILES = GA_PLAN_MAX_TILES;
 constexpr int GA_FWD_MATH_THREADS = 128;
-constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 128;  // + the S-issuer, stager, loader and PV-issuer warps
+constexpr int GA_FWD_THREADS = GA_FWD_MATH_THREADS + 96;  // + the issuer, stager and loader warps
 constexpr float GA_RESCALE_THRESHOLD = 24.f;                // log2 units
 constexpr uint32_t GA_TMEM_COLS = 256;
 constexpr uint32_t GA_TILE_BYTES = GA_BN * GA_D * 2;  // 16 KiB
@@ -73,7 +73,7 @@ struct GaFwdSmem {
     // side (column blocks 0 and 1).  Slot 0: the queries; slots 1..3: the ring of staged key tiles.
     alignas(1024) uint8_t geo[2][GA_TILE_BYTES];
     GaKeyCoords kc[GA_KC_BUFS];
-    uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_vfree[2], bar_s[2], bar_sfree[2], bar_p[2], bar_o[2], bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
+    uint64_t bar_q, bar_k[2], bar_v[2], bar_kfree[2], bar_vfree[2], bar_s[2], bar_p[2], bar_o[2], bar_kc[GA_KC_BUFS], bar_kcfree[GA_KC_BUFS];
     uint16_t tiles[GA_MAX_TILES];                 // key tiles with a valid key; bit 15: the tile also has a padded key
     uint32_t tmem_base;
     int abort;                                    // raised by the first wait that expires
@@ -329,7 +329,6 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
                     mbar_inval(&sm.bar_kfree[b]);
                     mbar_inval(&sm.bar_vfree[b]);
                     mbar_inval(&sm.bar_s[b]);
-                    mbar_inval(&sm.bar_sfree[b]);
                     mbar_inval(&sm.bar_p[b]);
                 }
 #pragma unroll
@@ -347,7 +346,6 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
                 mbar_init(&sm.bar_vfree[b], 1);
                 mbar_init(&sm.bar_s[b], 1);
                 mbar_init(&sm.bar_o[b], 1);
-                mbar_init(&sm.bar_sfree[b], GA_FWD_MATH_THREADS);
                 mbar_init(&sm.bar_p[b], GA_FWD_MATH_THREADS);
             }
 #pragma unroll
@@ -426,7 +424,7 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
     const uint32_t tmem_o = tmem + 128;    // columns [128,192): O accumulator
     const uint32_t tmem_p = tmem + 192;    // columns [192,224): P as bf16 pairs (A operand of P V), 16 per unit parity
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const bool is_loader = warp == GA_FWD_MATH_THREADS / 32 + 2, is_pv = warp == GA_FWD_MATH_THREADS / 32 + 3;
+    const bool is_loader = warp == GA_FWD_MATH_THREADS / 32 + 2;
     // Every warp waits as a whole and keeps `ok` uniform: tcgen05.ld / st and the votes need all 32 lanes, and a helper
     // warp whose lanes 1..31 sit at a reconvergence point while lane 0 loops runs several times slower than a
     // converged warp in which lane 0 alone issues the copy or MMA.
@@ -481,23 +479,26 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
         }
         __syncwarp();
     } else if (is_producer) {
-        // ================================ S-issuer warp ==============================================
-        // S(w), G(w) for w >= 2 leave as soon as the math threads have read unit w - 2 out of the same columns: one and
-        // a half units before they are needed.  (A single thread issuing every MMA of a unit in turn took longer per unit
-        // than the softmax of the unit, about 80 cycles an MMA, and was the pacemaker of the CTA.)
+        // ================================ issuer warp ================================================
+        // One thread issues every MMA, in the order S(0), S(1), P V(0), S(2), P V(1), S(3), ...: S(w+2) follows P V(w) into
+        // the columns that unit w has left, a whole unit before the math warps want it.  The tensor core works through
+        // its queue in order, so a math thread that sees S(w) complete knows that P V(w-2) is complete too, and writes
+        // P(w) over P(w-2) without a further wait.
         {
             constexpr uint32_t IDESC_S = umma_idesc_bf16(GA_BM, GA_UNIT, false, false);  // Q K^T and G: both K-major, N = 32
             // descriptors are built once; a step of K = 16 adds to the 16-byte-granular address field
             const uint64_t q_desc = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
-            const uint64_t k_desc[2] = {umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.k[1]), 16, 1024)};
-            const uint64_t geo_desc[2] = {umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024), umma_desc_sw128(smem_u32(sm.geo[1]), 16, 1024)};
-            auto geo_slot_desc = [&](int slot) -> uint64_t { return geo_desc[slot >> 1] + (uint64_t)(ga_geo_block(slot) * 4); };
+            // (the second buffer of a pair follows the first: its descriptor is the first one's plus the distance)
+            const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024), geo_desc0 = umma_desc_sw128(smem_u32(sm.geo[0]), 16, 1024);
+            auto geo_slot_desc = [&](int slot) -> uint64_t {
+                return geo_desc0 + (uint64_t)(slot >> 1) * (GA_TILE_BYTES >> 4) + (uint64_t)(ga_geo_block(slot) * 4);
+            };
             constexpr uint64_t UNIT_ROWS = (uint64_t)(GA_UNIT * 128) >> 4;  // 32 rows of a swizzled tile, in 16-byte units
             // S(w) = Q K^T: 4 MMAs of K = 16 over d = 64 (32 B per step inside the swizzled row); G(w): 2 more over the
             // geometry operands (the keys' rows start 32 (w mod 4) rows into the staged tile)
             auto issue_s = [&](int w) {
                 const int sb = w & 1, kb = (w >> 1) & 1, t = w >> 2;
-                const uint64_t kd = k_desc[kb] + (uint64_t)(w & 1) * UNIT_ROWS;
+                const uint64_t kd = k_desc0 + (uint64_t)kb * (GA_STEP_BYTES >> 4) + (uint64_t)(w & 1) * UNIT_ROWS;
 #pragma unroll
                 for (int kk = 0; kk < GA_D / 16; ++kk)
                     umma_ss(tmem_s + sb * GA_UNIT, q_desc + (uint64_t)(kk * 2), kd + (uint64_t)(kk * 2), IDESC_S, kk > 0 ? 1u : 0u);
@@ -508,37 +509,40 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
                 umma_commit(&sm.bar_s[sb]);
                 if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_kfree[kb]);  // the box's last reader
             };
-            bool ok = wait_w(&sm.bar_q, 0);
-            for (int w = 0; ok && w < nw; ++w) {
-                const int t = w >> 2;
-                // every math thread holds S(w-2), G(w-2) in registers: their columns are free
-                if (w >= 2 && !(ok = wait_w(&sm.bar_sfree[w & 1], (uint32_t)(((w - 2) >> 1) & 1)))) break;
-                if ((w & 1) == 0 && !(ok = wait_w(&sm.bar_k[(w >> 1) & 1], (uint32_t)((w >> 2) & 1)))) break;
-                if ((w & 3) == 0 && !(ok = wait_w(&sm.bar_kc[t % GA_KC_BUFS], (uint32_t)((t / GA_KC_BUFS) & 1)))) break;
-                tc_fence_after();
-                if (lane == 0) issue_s(w);
-                __syncwarp();
-            }
-        }
-        __syncwarp();
-    } else if (is_pv) {
-        // ================================ PV-issuer warp =============================================
-        {
             constexpr uint32_t IDESC_O = umma_idesc_bf16(GA_BM, GA_D, false, true);      // P V: V is MN-major
-            const uint64_t v_desc[2] = {umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024), umma_desc_sw128(smem_u32(sm.v[1]), 0, 1024)};
-            bool ok = true;
-            for (int w = 0; ok && w < nw; ++w) {
+            const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sm.v[0]), 0, 1024);
+            auto issue_pv = [&](int w) {  // 2 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
                 const int pb = w & 1, vb = (w >> 1) & 1;
-                if (!(ok = wait_w(&sm.bar_p[pb], (uint32_t)((w >> 1) & 1)))) break;  // P(w) in TMEM, O rescaled if need be
-                if ((w & 1) == 0 && !(ok = wait_w(&sm.bar_v[vb], (uint32_t)((w >> 2) & 1)))) break;
+#pragma unroll
+                for (int kk = 0; kk < GA_UNIT / 16; ++kk)
+                    umma_ts(tmem_o, tmem_p + pb * (GA_UNIT / 2) + kk * 8, v_desc0 + (uint64_t)vb * (GA_STEP_BYTES >> 4) + (uint64_t)(((w & 1) * 2 + kk) * 128), IDESC_O,
+                            (w == 0 && kk == 0) ? 0u : 1u);
+                umma_commit(&sm.bar_o[pb]);
+                if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_vfree[vb]);
+            };
+            bool ok = wait_w(&sm.bar_q, 0) && wait_w(&sm.bar_k[0], 0) && wait_w(&sm.bar_kc[0], 0);
+            if (ok) {
                 tc_fence_after();
                 if (lane == 0) {
-#pragma unroll
-                    for (int kk = 0; kk < GA_UNIT / 16; ++kk)  // 2 MMAs of K = 16 keys: P advances 8 TMEM columns, V 2 KiB
-                        umma_ts(tmem_o, tmem_p + pb * (GA_UNIT / 2) + kk * 8, v_desc[vb] + (uint64_t)(((w & 1) * 2 + kk) * 128), IDESC_O,
-                                (w == 0 && kk == 0) ? 0u : 1u);
-                    umma_commit(&sm.bar_o[pb]);
-                    if ((w & 1) || w + 1 == nw) umma_commit(&sm.bar_vfree[vb]);
+                    issue_s(0);
+                    if (nw > 1) issue_s(1);
+                }
+                __syncwarp();
+            }
+            for (int w = 0; ok && w < nw; ++w) {
+                // P(w) in TMEM (and O rescaled if need be); its arrival also says that every math thread holds S(w), G(w)
+                // in registers, so that their columns can take unit w + 2
+                if (!(ok = wait_w(&sm.bar_p[w & 1], (uint32_t)((w >> 1) & 1)))) break;
+                if ((w & 1) == 0 && !(ok = wait_w(&sm.bar_v[(w >> 1) & 1], (uint32_t)((w >> 2) & 1)))) break;
+                const int w2 = w + 2, t2 = w2 >> 2;
+                if (w2 < nw) {
+                    if ((w2 & 1) == 0 && !(ok = wait_w(&sm.bar_k[(w2 >> 1) & 1], (uint32_t)((w2 >> 2) & 1)))) break;
+                    if ((w2 & 3) == 0 && !(ok = wait_w(&sm.bar_kc[t2 % GA_KC_BUFS], (uint32_t)((t2 / GA_KC_BUFS) & 1)))) break;
+                }
+                tc_fence_after();
+                if (lane == 0) {
+                    issue_pv(w);
+                    if (w2 < nw) issue_s(w2);
                 }
                 __syncwarp();
             }
@@ -599,7 +603,6 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
             if (!(far[0] && far[1])) tmem_ld32(tmem_g + sb * GA_UNIT + lane_base, g);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&sm.bar_sfree[sb]);  // S and G are in registers: the tensor core may overwrite them with unit w + 2
             if (qd == 3 || w + 1 == nw) mbar_arrive(&sm.bar_kcfree[cb]);  // the stager may reuse this key tile's buffer
             float m_unit = fmaxf(ga_sr_chunk<FORM, 0>(s, g, far[0], crbf2, cqn2, cs2, fm), ga_sr_chunk<FORM, 16>(s, g, far[1], crbf2, cqn2, cs2, fm));
             if (has_hole) {  // select, do not add: a padded key may hold Inf / NaN
@@ -654,8 +657,7 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
             float l0, l1;
             f2_unpack(f2_add(l2, l2b), l0, l1);
             l_run += l0 + l1;
-            // P V(w-2), the last reader of these P columns, has long completed
-            if (w >= 2 && !(ok = wait_w(&sm.bar_o[sb], (uint32_t)(((w - 2) >> 1) & 1)))) break;
+            // (P V(w-2), the last reader of these P columns, completed before S(w): the tensor core works in issue order)
             tmem_st16(tmem_p + sb * (GA_UNIT / 2) + lane_base, pw);
             tmem_wait_st();
             tc_fence_before();
