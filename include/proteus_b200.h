@@ -358,11 +358,12 @@ enum pai_tune_key {
     PAI_TUNE_WE_TJ = 1,           /* sources per staged tile: multiple of 4 up to 512 */
     PAI_TUNE_WE_WAVES = 2,        /* runs per resident CTA slot */
     PAI_TUNE_WE_RANGE_REDUCE = 3, /* 1: explicit range reduction of the phase before the SFU */
-    PAI_TUNE_WE_POLY_PAIRS = 4,   /* wavenumber pairs per lane evaluated on the FMA pipe (default 1) */
+    PAI_TUNE_WE_POLY_PAIRS = 4,   /* wavenumber pairs per lane evaluated on the FMA pipe (default 2) */
     PAI_TUNE_WE_NO_TMA = 5,       /* 1: plain loads instead of bulk copies for the source tiles */
     PAI_TUNE_GA_NO_FAR_SKIP = 6,  /* 1: evaluate the RBF of every key group, however far */
     PAI_TUNE_GA_NO_ORDER = 7,     /* 1: issue the samples in natural order instead of longest first */
-    PAI_TUNE_WE_NO_MIXED = 8,     /* 1: every warp evaluates on both pipes instead of separate SFU and polynomial warps */
+    PAI_TUNE_WE_MIXED = 8,        /* 1: separate SFU and polynomial warps (we_fwd_mixed_kernel) instead of both pipes in every warp;
+                                     measured 12 % slower at N = 16384, kept for comparison (default 0) */
     PAI_TUNE_COUNT = 9
 };
 int pai_tune_set(int key, int value);

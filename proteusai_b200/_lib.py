@@ -52,8 +52,8 @@ SIGNATURES = {
 # enum pai_we_flags / enum pai_tune_key of the header
 WE_REPRODUCIBLE = 1
 TUNE = {"we_ks": 0, "we_tj": 1, "we_waves": 2, "we_range_reduce": 3, "we_poly_pairs": 4, "we_no_tma": 5,
-        "ga_no_far_skip": 6, "ga_no_order": 7, "we_no_mixed": 8}
-TUNE_DEFAULTS = {"we_poly_pairs": 1}
+        "ga_no_far_skip": 6, "ga_no_order": 7, "we_mixed": 8}
+TUNE_DEFAULTS = {"we_poly_pairs": 2}
 
 _lib = None
 

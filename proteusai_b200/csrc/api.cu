@@ -86,8 +86,8 @@ int require_sm100() {
 // them without any environment lookup).  Defaults are what the library ships with.
 int g_tune[PAI_TUNE_COUNT] = {
     /* PAI_TUNE_WE_KS */ 0,        /* PAI_TUNE_WE_TJ */ 0,          /* PAI_TUNE_WE_WAVES */ 0,
-    /* PAI_TUNE_WE_RANGE_REDUCE */ 0, /* PAI_TUNE_WE_POLY_PAIRS */ 1, /* PAI_TUNE_WE_NO_TMA */ 0,
-    /* PAI_TUNE_GA_NO_FAR_SKIP */ 0,  /* PAI_TUNE_GA_NO_ORDER */ 0,   /* PAI_TUNE_WE_NO_MIXED */ 0,
+    /* PAI_TUNE_WE_RANGE_REDUCE */ 0, /* PAI_TUNE_WE_POLY_PAIRS */ 2, /* PAI_TUNE_WE_NO_TMA */ 0,
+    /* PAI_TUNE_GA_NO_FAR_SKIP */ 0,  /* PAI_TUNE_GA_NO_ORDER */ 0,   /* PAI_TUNE_WE_MIXED */ 0,
 };
 
 // register-only sin+cos loop: 8 independent chains per thread
@@ -212,7 +212,7 @@ int pai_we_fwd(const float *coords_soa, const uint8_t *valid, const float *waven
     if (int e = next_we_counter(&counter)) return e;
     return pai::we_fwd_launch(p, Z, g_tune[PAI_TUNE_WE_KS], g_tune[PAI_TUNE_WE_TJ], g_tune[PAI_TUNE_WE_WAVES],
                               (flags & PAI_WE_REPRODUCIBLE) != 0, g_tune[PAI_TUNE_WE_RANGE_REDUCE] != 0,
-                              g_tune[PAI_TUNE_WE_POLY_PAIRS], g_tune[PAI_TUNE_WE_NO_MIXED] == 0, sms, counter, st);
+                              g_tune[PAI_TUNE_WE_POLY_PAIRS], g_tune[PAI_TUNE_WE_MIXED] != 0, sms, counter, st);
 }
 
 size_t pai_we_bwd_dk_workspace_bytes(int Z, int N, int K) {

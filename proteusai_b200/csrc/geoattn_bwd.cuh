@@ -11,24 +11,29 @@
 //     dS    = dSR (1 + R) scale        -> dQ_i = sum_j dS_ij K_j,   dK_j = sum_i dS_ij Q_i
 //     dsigma_h = sum_{z,i,j} dSR S R d^2 / sigma_h^3
 //
-// One CTA = 128 keys of one (batch, head); it loops over the live 128-row query tiles.  The logit tile is
-// computed TRANSPOSED, keys on the TMEM lanes and queries along the columns, so that a math thread owns a key:
-//     S^T  = K_j Q_i^T     A, B K-major                          -> TMEM [128 keys x 128 queries]
-//     dP^T = V_j dO_i^T    A, B K-major                          -> TMEM [128 x 128]
+// One work item = 128 keys of one (batch, head); the CTA loops over the live 128-row query tiles, 64 queries (a
+// "sub-tile") at a time.  The logit tile is computed TRANSPOSED, keys on the TMEM lanes and queries along the columns,
+// so that a math thread owns a key:
+//     S^T  = K_j Q_i^T     A, B K-major                          -> TMEM [128 keys x 64 queries], two stages
+//     dP^T = V_j dO_i^T    A, B K-major                          -> TMEM [128 x 64], two stages
 //     dV  += P^T dO_i      A = P^T read from TENSOR MEMORY (bf16 pairs written by the math threads), B = dO MN-major
 //     dK  += dS^T Q_i      A = dS^T from shared memory, K-major (the math threads write row j = their key, the
 //                          queries contiguous: 16-byte stores), B = Q MN-major
-//     dQ_i = dS K_j        A = the same dS^T tile read MN-major, B = K MN-major -> TMEM [128 queries x 64], read
-//                          back and added into the global fp32 dQ with 16-byte vector reductions
-// Eight math warps and one producer warp: key row r = TMEM lane r is shared by two math threads (warps w, w + 4),
-// each taking 64 of the 128 query columns in two passes of 32.  After the second pass has loaded its
-// columns the S^T / dP^T accumulators are released and the tensor core computes the next query tile's underneath
-// the element-wise work of this one; dV / dK / dQ of tile t run under the element-wise work of tile t + 1, and
-// dQ(t) is read out after tile t + 1 has been handed over, when it has long completed.  Per-query inputs (centred
-// coordinates, log-sum-exp, D, validity, bounding spheres of 16 queries) are staged in shared memory one tile
-// ahead; no row reduction is needed in the backward.  Query groups farther than 5.9 sigma_h from a warp's 32 keys
-// skip the RBF arithmetic (R < 2^-25 there).  Query tiles without a valid query are skipped, a key tile without a
-// valid key only writes zeros.  Every wait is bounded and abortable (tc.cuh).
+//     dQ_i = dS K_j        A = the same dS^T tile read MN-major, B = K MN-major -> TMEM [128 queries x 64], once per
+//                          query tile, read back and added into the global fp32 dQ with vector reductions
+// Sixteen math warps: key row r = TMEM lane r is shared by four math threads (warps w, w + 4, w + 8, w + 12), each
+// taking 16 of the sub-tile's 64 query columns.  A thread reads its S^T and dP^T values into registers and releases
+// the stage at once; with two stages the tensor core is a sub-tile ahead and the warps may drift a sub-tile apart
+// (their work differs: see the far groups below).  Two threads issue the MMAs, one S^T / dP^T of the sub-tiles
+// ahead, one dV / dK / dQ behind and the TMA loads of Q and dO: an MMA holds its issuing thread until the tensor
+// core has taken it, and one thread doing all of it, with its waits in between, was the slowest part of the CTA.
+// A stager warp keeps the per-query inputs (centred coordinates, log-sum-exp, D, validity, bounding spheres of
+// 16 queries) in shared memory up to three query tiles ahead; the pair geometry takes four packed FMAs a pair from
+// them (every lane reads the same entry).  Query groups farther than 5.9 sigma_h from a warp's 32 keys skip the RBF
+// arithmetic (R < 2^-25 there).  dQ reductions and the dK / dV rows leave through per-warp staging so that every
+// instruction covers whole 32-byte sectors.  Query tiles without a valid query are skipped, a key tile without a
+// valid key only writes zeros.  Work items come one per CTA or from a balanced schedule (geoattn_plan.cuh).  Every
+// wait is bounded and abortable (tc.cuh).
 #pragma once
 #include "geoattn_fwd.cuh"
 

@@ -442,14 +442,14 @@ static int we_fwd_launch_ks(WeFwdParams p, int Z, bool rr, int sms, int tj_hint,
 
 // ks_hint: 0 = choose; otherwise 2, 8 or 16.  tj_hint: 0 = choose; otherwise a multiple of 4 in
 // [4, 512].  waves: 0 = choose; otherwise CTAs launched per resident CTA slot.  rr: explicit range reduction.  The three outputs must already be zero over the row range.
-// `mixed_ok`: the caller allows the kernel with separate SFU and polynomial warps (it is used for the 1/r magnitude without
-// dropout or explicit range reduction, when the lane width is the default 16 and npoly is the default 1).
+// `mixed_ok`: the caller asks for the kernel with separate SFU and polynomial warps (it exists for the 1/r magnitude without
+// dropout or explicit range reduction at the default lane width of 16; off by default: it measured 12 % slower at N = 16384).
 static int we_fwd_launch(const WeFwdParams &p, int Z, int ks_hint, int tj_hint, int waves, bool reproducible, bool rr,
                          int npoly, bool mixed_ok, int sms, unsigned *counter, cudaStream_t stream) {
     int ks = ks_hint;
     if (ks == 0) ks = p.K >= 64 ? 16 : (p.K >= 32 ? 8 : 2);
     if (tj_hint < 0 || tj_hint > WE_TJ_MAX || (tj_hint & 3) || waves < 0 || waves > 64) return (int)PAI_ERR_UNSUPPORTED;
-    const bool mixed = mixed_ok && ks == 16 && ks_hint == 0 && p.mag_type == 1 && !rr && p.drop_scale == 0.f && npoly == 1;
+    const bool mixed = mixed_ok && ks == 16 && ks_hint == 0 && p.mag_type == 1 && !rr && p.drop_scale == 0.f;
     switch (ks) {
         case 16: return we_fwd_launch_ks<16>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, mixed, counter, stream);
         case 8: return we_fwd_launch_ks<8>(p, Z, rr, sms, tj_hint, waves, reproducible, npoly, false, counter, stream);

@@ -143,8 +143,8 @@ def test_row_shards_and_code_paths_agree(we, monkeypatch):
     from proteusai_b200 import _lib
     try:
         for knobs in ({"we_no_tma": 1}, {"we_ks": 8}, {"we_ks": 2}, {"we_range_reduce": 1}, {"we_ks": 16}, {"we_tj": 64},
-                      {"we_tj": 512}, {"we_tj": 36, "we_no_tma": 1}, {"we_poly_pairs": 0}, {"we_poly_pairs": 3}, {"we_no_mixed": 1},
-                      {"we_no_mixed": 1, "we_no_tma": 1}):
+                      {"we_tj": 512}, {"we_tj": 36, "we_no_tma": 1}, {"we_poly_pairs": 0}, {"we_poly_pairs": 1}, {"we_poly_pairs": 3}, {"we_mixed": 1},
+                      {"we_mixed": 1, "we_no_tma": 1}):
             _lib.tune_reset()
             _lib.tune(**knobs)
             alt, _, _ = we.we_forward_rows(c_t, wn, 1, m_t)
