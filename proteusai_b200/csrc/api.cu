@@ -449,7 +449,7 @@ int pai_geoattn_bwd(const void *Q, const void *K, const void *V, const void *O, 
     if (q_end > q_begin) {
         const int q_rows = q_end - q_begin;
         const long long rows = (long long)nzh * q_rows;
-        pai::geoattn_bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+        pai::geoattn_bwd_prep_kernel<<<(unsigned)((rows + 31) / 32), 256, 0, st>>>(
             (const __nv_bfloat16 *)O + rows0 * d, (const __nv_bfloat16 *)dO + rows0 * d, dsum, dQ + rows0 * d, N, q_begin, q_rows, rows);
     }
     pai::GaBwdParams p;

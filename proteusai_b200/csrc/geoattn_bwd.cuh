@@ -94,22 +94,34 @@ struct GaBwdParams {
 };
 
 // Pre-pass: D[pair, i] = sum_d O * dO for the query rows [q_begin, q_begin + q_rows) of every (batch, head) pair of
-// the range, and zeros into the same rows of dQ, which the main kernel accumulates with reductions.  One warp per
-// row; o, d_out, dsum and dq point at the first pair of the range.
+// the range, and zeros into the same rows of dQ, which the main kernel accumulates with reductions.  Eight threads
+// per row (16-byte loads of 8 bf16, two 16-byte stores of zeros each), four rows per warp; o, d_out, dsum and dq point
+// at the first pair of the range.
 __global__ void __launch_bounds__(256) geoattn_bwd_prep_kernel(const __nv_bfloat16 *o, const __nv_bfloat16 *d_out, float *dsum,
                                                                float *dq, int N, int q_begin, int q_rows, long long rows) {
-    const long long idx = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // (pair, row inside the range)
-    const int lane = threadIdx.x & 31;
-    if (idx >= rows) return;
-    const long long pair = idx / q_rows;
-    const long long row = pair * N + q_begin + (idx - pair * q_rows);
-    const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162 *>(o + row * GA_D)[lane];
-    const __nv_bfloat162 b = reinterpret_cast<const __nv_bfloat162 *>(d_out + row * GA_D)[lane];
-    float s = __bfloat162float(a.x) * __bfloat162float(b.x) + __bfloat162float(a.y) * __bfloat162float(b.y);
+    const long long idx = (long long)blockIdx.x * 32 + (threadIdx.x >> 3);  // (pair, row inside the range)
+    const int part = threadIdx.x & 7;
+    float s = 0.f;
+    long long row = 0;
+    const bool live = idx < rows;
+    if (live) {
+        const long long pair = idx / q_rows;
+        row = pair * N + q_begin + (idx - pair * q_rows);
+        const uint4 a = reinterpret_cast<const uint4 *>(o + row * GA_D)[part];
+        const uint4 b = reinterpret_cast<const uint4 *>(d_out + row * GA_D)[part];
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-    if (lane == 0) dsum[row] = s;
-    reinterpret_cast<float2 *>(dq + row * GA_D)[lane] = make_float2(0.f, 0.f);
+        for (int i = 0; i < 4; ++i) {  // a bf16 is the upper half of an fp32
+            s = fmaf(__uint_as_float(aw[i] << 16), __uint_as_float(bw[i] << 16), s);
+            s = fmaf(__uint_as_float(aw[i] & 0xffff0000u), __uint_as_float(bw[i] & 0xffff0000u), s);
+        }
+        float4 *z4 = reinterpret_cast<float4 *>(dq + row * GA_D) + part * 2;
+        z4[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        z4[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (live && part == 0) dsum[row] = s;
 }
 
 __device__ __forceinline__ void red_add_v4(float *dst, float a, float b, float c, float d) {

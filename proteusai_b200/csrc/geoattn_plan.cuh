@@ -142,77 +142,95 @@ __host__ __device__ inline const int *ga_sched_dead(const int *sched) {
 // One CTA of 1024 threads; thread b keeps the load of bin b.  `tile_cost`, `item_cost`: cost of one non-empty tile
 // of the sample and fixed cost of an item, in the same (arbitrary) unit.
 // The items are packed by first fit, longest first, into bins of capacity C, and C is bisected down to the smallest
-// capacity for which every item finds a bin (MULTIFIT).  With `pair` the bins of the packing are SMs that run two
-// CTAs each: the items of SM b are dealt, longest first, to the lighter of CTAs b and b + bins / 2 (the launch
-// places them on one SM when it fills the machine in order; if it does not, only the balance suffers).
+// capacity for which every item finds a bin (MULTIFIT).  The H x count[z] items of a sample cost the same, and first fit
+// places a run of equal items by filling the bins in index order with as many as each has room for: one prefix sum
+// over the bins per sample instead of one search per item, which keeps the kernel at a few tens of microseconds
+// (it runs once per mask, head count and direction).
+// With `pair` the bins of the packing are SMs that run two CTAs each: the items of SM b are dealt, longest first, to the
+// lighter of CTAs b and b + bins / 2 (a guess at which CTAs share an SM; where it is wrong only the balance suffers).
+__device__ inline int ga_block_scan_1024(int v, int *warp_sums, int &total) {  // exclusive prefix sum over the CTA
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += n;
+    }
+    __syncthreads();  // (the previous scan's sums have been read)
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    int w = warp_sums[lane];
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, w, off);
+        if (lane >= off) w += n;
+    }
+    total = __shfl_sync(0xffffffffu, w, 31);
+    const int before = __shfl_sync(0xffffffffu, w, max(warp - 1, 0));
+    return incl - v + (warp > 0 ? before : 0);
+}
+
 __global__ void __launch_bounds__(1024) geoattn_schedule_kernel(const int *plan, int *sched, int Z, int N, int H, int bins, int tile_cost,
                                                                 int item_cost, int pair) {
-    __shared__ unsigned int best[2][32];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    __shared__ int warp_sums[32];
+    __shared__ int dead_n;
+    const int tid = threadIdx.x;
     const int T = ga_plan_tiles_per_sample(N);
     const int cap = ga_sched_cap(Z, N, H, bins);
-    const int nb = pair ? bins / 2 : bins;  // bins of the packing
+    const int nb = pair ? bins / 2 : bins;        // bins of the packing
+    const int limit = pair ? 2 * cap - 2 : cap;   // items a bin of the packing can list
     int *count = sched + GA_SCHED_HEADER, *items = count + bins, *dead = items + (size_t)bins * cap;
     const int *order = ga_plan_order(plan), *cnt = ga_plan_count(plan, Z);
     // totals: lower bound of the capacity
-    long long total = 0;
-    int biggest = 0, n_live = 0, n_dead = 0;
+    long long total_cost = 0;
+    int biggest = 0, n_live = 0;
     for (int s = 0; s < Z; ++s) {
-        const int z = order[s], c = cnt[z];
+        const int c = cnt[order[s]];
         const int cost = c * tile_cost + item_cost;
         n_live += c * H;
-        n_dead += (T - c) * H;
-        total += (long long)c * H * cost;
+        total_cost += (long long)c * H * cost;
         if (c > 0) biggest = max(biggest, cost);
     }
-    unsigned int lo = (unsigned int)max((long long)biggest, (total + nb - 1) / nb), hi = 2 * lo + 1;  // first fit never needs more than 2 x optimum
-    int it = 0;
-    // pass < 12: bisection (nothing is written); the last pass packs with the capacity found and writes the lists
-    for (int pass = 0; pass <= 12; ++pass) {
+    // first fit with capacity 2 x (lower bound) + 1 always succeeds: a bin that refuses an item is more than half full
+    int lo = (int)max((long long)biggest, (total_cost + nb - 1) / nb), hi = 2 * lo + 1;
+    for (int pass = 0; pass <= 12; ++pass) {  // pass < 12: bisection (nothing is written); the last pass writes the lists
         const bool last = pass == 12;
-        const unsigned int C = last ? hi : (lo + hi) / 2;
-        unsigned int load = 0, load2[2] = {0, 0};
-        int mine = 0, mine2[2] = {0, 0}, nd = 0;
+        const int C = last ? hi : (lo + hi) / 2;
+        int load = 0, mine = 0, load2[2] = {0, 0}, mine2[2] = {0, 0};
         bool fail = false;
-        for (int s = 0; s < Z && !fail; ++s) {  // samples, longest first
+        for (int s = 0; s < Z && !fail; ++s) {  // samples, longest first: a run of c * H equal items
             const int z = order[s], c = cnt[z];
-            const int *info = ga_plan_info(plan, Z, N, z);
-            const unsigned int cost = (unsigned int)(c * tile_cost + item_cost);
-            for (int h = 0; h < H && !fail; ++h)
-                for (int x = 0; x < T; ++x) {
-                    const int item = ((z * H + h) << 10) | x;
-                    if (info[x] < 0) {
-                        if (last && tid == 0) dead[nd] = item;
-                        ++nd;
-                        continue;
-                    }
-                    // the first bin with room (a full list does not bid)
-                    unsigned int key = 0xffffffffu;
-                    if (tid < nb && mine < (pair ? 2 * cap - 2 : cap)) {
-                        if (load + cost <= C) key = (unsigned int)tid;
-                        else if (last) key = 0x80000000u | (unsigned int)tid;  // (never leave an item out: any list with a free slot)
-                    }
-                    key = __reduce_min_sync(0xffffffffu, key);
-                    if (lane == 0) best[it & 1][warp] = key;
-                    __syncthreads();
-                    unsigned int k = best[it & 1][lane];
-                    k = __reduce_min_sync(0xffffffffu, k);
-                    ++it;
-                    if (k == 0xffffffffu) {  // (the same for every thread)
-                        fail = true;
-                        break;
-                    }
-                    if ((int)(k & 0x7fffffffu) == tid) {
-                        ++mine;
-                        load += cost;
-                        if (last) {
+            if (c == 0) continue;
+            const int cost = c * tile_cost + item_cost;
+            int m = c * H, done = 0;
+            // round 0: by capacity; round 1 (last pass only, cannot happen with the capacity found unless the lists are
+            // full): any bin with a free slot, so that no item is ever left out
+            for (int round = 0; round < 2 && m > 0; ++round) {
+                int room = 0;
+                if (tid < nb) room = round == 0 ? (load <= C ? min((C - load) / cost, limit - mine) : 0) : limit - mine;
+                int total;
+                const int before = ga_block_scan_1024(room, warp_sums, total);
+                const int take = max(0, min(room, m - before));
+                if (take > 0) {
+                    if (last) {
+                        const int *tl = ga_plan_tiles(plan, Z, N, z);
+                        for (int i = 0; i < take; ++i) {
+                            const int idx = done + before + i;  // item of the run: head idx / c, its (idx % c)-th non-empty tile
+                            const int item = ((z * H + idx / c) << 10) | (tl[idx % c] & 0x3ff);
                             const int half = (pair && load2[1] < load2[0] && mine2[1] < cap) || (pair && mine2[0] >= cap) ? 1 : 0;
                             items[(size_t)(tid + half * nb) * cap + mine2[half]] = item;
                             ++mine2[half];
                             load2[half] += cost;
                         }
                     }
+                    load += take * cost;
+                    mine += take;
                 }
+                done += min(total, m);
+                m -= min(total, m);
+                if (!last) break;
+            }
+            if (m > 0) fail = true;  // (the same for every thread)
         }
         if (last) {
             if (tid < nb) {
@@ -227,15 +245,23 @@ __global__ void __launch_bounds__(1024) geoattn_schedule_kernel(const int *plan,
         }
         if (!last && lo >= hi) pass = 11;  // converged: the next pass is the last
     }
+    // tiles without a valid token, in any order
+    if (tid == 0) dead_n = 0;
+    __syncthreads();
+    for (int e = tid; e < Z * H * T; e += 1024) {
+        const int x = e % T, zh = e / T, z = zh / H;
+        if (ga_plan_info(plan, Z, N, z)[x] < 0) dead[atomicAdd(&dead_n, 1)] = (zh << 10) | x;
+    }
+    __syncthreads();
     if (tid == 0) {
         sched[0] = bins;
         sched[1] = H;
         sched[2] = Z;
         sched[3] = N;
         sched[4] = cap;
-        sched[5] = n_dead;
+        sched[5] = dead_n;
         sched[6] = n_live;
-        sched[7] = (int)hi;
+        sched[7] = hi;
     }
 }
 

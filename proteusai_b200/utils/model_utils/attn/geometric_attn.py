@@ -120,6 +120,10 @@ class GeoPlan:
             batch, n = self.mask.shape
             sms = torch.cuda.get_device_properties(self.plan.device).multi_processor_count
             bins = min(sms * (1 if backward else 2), 1024)
+            if batch * nheads * ((n + 127) // 128) > 8 * bins:
+                # many items per CTA slot: one CTA per item, issued longest first, balances by itself
+                hit = self.schedules[key] = (None, 0)
+                return hit
             lib = _lib.lib()
             nbytes = lib.pai_geoattn_schedule_bytes(batch, n, nheads, bins)
             sched = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=self.plan.device)
