@@ -1,5 +1,5 @@
 // tcgen05 / TMEM / tiled-TMA helpers for sm_100a (inline PTX), and the host-side tensor-map
-// encoder.  No cluster multicast anywhere: every CTA issues its own plain tiled loads.
+// encoder.  Every CTA issues its own plain tiled loads (no load is shared across a cluster).
 #pragma once
 #include <cuda.h>  // CUtensorMap and enums only; the driver entry point is resolved at run time
 
