@@ -489,7 +489,7 @@ def bench_we_bwd(dev, steps, flush):
             "ms_per_step": ms, "dtype": "f32",
             "config": {"workload": "WE backward dk, Z=8, N=16384, K=256, N(0,1) inputs", "sharding": "rank 0 only",
                        "l2": "flushed between timed calls; inputs 537 MB"},
-            "roofline": {"bound": "hbm", "kernel": "we_bwd_partial_kernel", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "we_bwd_partial2_kernel + we_bwd_final_kernel", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "peak_source": src, "traffic": None,
                          "note": "through the public call: the two kernels plus the workspace allocation"},
             "gpu_launches": 2 * steps}
@@ -700,7 +700,7 @@ def main():
                          "peak_measured_source": "live: register-only sin+cos loop on this GPU (pai_measure_sfu_peak)",
                          "balanced_pipe_peak": balanced / 1e9, "frac_of_balanced": achieved / balanced,
                          "balanced_pipe_note": "bound with SFU and fp32 pipes both busy (12.2 evaluations per clock per SM): applies "
-                                               "because one pair in eight per lane is evaluated by an FMA-pipe polynomial",
+                                               "because two pairs in eight per lane are evaluated by an FMA-pipe polynomial",
                          "kernel": "we_fwd_kernel", "kernel_ms": kern_ms,
                          "evals_per_launch": evals_per_launch},
         }
