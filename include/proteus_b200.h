@@ -49,8 +49,9 @@ int pai_abi_version(void);
 const char *pai_status_str(int status);
 
 /* Synchronises `stream` and returns, then clears, the device-side status word of the
- * current device: PAI_OK, or PAI_ERR_DEVICE_WAIT_TIMEOUT when a kernel gave up on a
- * bounded wait (it then wrote nothing further and returned). */
+ * current device: PAI_OK, PAI_ERR_DEVICE_WAIT_TIMEOUT when a kernel gave up on a
+ * bounded wait (it then wrote nothing further and returned), or PAI_ERR_BAD_SHAPE when an
+ * attention launch was handed a schedule made for another problem (it did nothing). */
 int pai_device_status(void *stream);
 
 /* ---------------------------------------------------------------------------------------
@@ -196,6 +197,8 @@ int pai_geoattn_plan(const uint8_t *valid, int Z, int N, void *plan, size_t plan
  * The attention calls take the schedule as (sched, sched_bins); sched = NULL launches one CTA per item.  A schedule
  *   needs `valid` and its plan, and only applies to a call over the whole problem (zh_begin = 0, zh_end = Z*H,
  *   q_begin = 0, q_end = N): other ranges with a schedule are PAI_ERR_BAD_ROW_RANGE.
+ *   A schedule made for another Z, N, H or number of CTAs is not followed: the launch does nothing and pai_device_status
+ *   reports PAI_ERR_BAD_SHAPE.
  */
 size_t pai_geoattn_schedule_bytes(int Z, int N, int H, int bins);
 int pai_geoattn_schedule(const void *plan, int Z, int N, int H, int bins, int backward, void *sched, size_t sched_bytes,

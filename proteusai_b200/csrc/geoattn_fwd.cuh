@@ -716,7 +716,13 @@ geoattn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     int total = 1;
     if (p.sched != nullptr) {
         const int bins = p.sched[0];
-        total = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins + ga_sched_count(p.sched)[blockIdx.x];
+        if (bins != (int)gridDim.x || p.sched[1] != p.H || p.sched[2] != p.Z || p.sched[3] != p.N) {
+            // not the schedule of this problem: do nothing and say so (pai_device_status)
+            if (threadIdx.x == 0 && blockIdx.x == 0) atomicExch(&g_device_status, (int)PAI_ERR_BAD_SHAPE);
+            total = 0;
+        } else {
+            total = (p.sched[5] - (int)blockIdx.x + bins - 1) / bins + ga_sched_count(p.sched)[blockIdx.x];
+        }
     }
     bool fresh = true;  // the barriers have not been initialised yet
 #pragma unroll 1

@@ -279,6 +279,67 @@ def test_batch_plan_lists_live_tiles_and_orders_samples(ga):
     assert ga.geoattn_plan(mc) is ga.geoattn_plan(mc)                    # the same tensor: one plan for all layers
 
 
+def test_balanced_schedule_covers_every_item_once_and_changes_no_result(ga):
+    """pai_geoattn_schedule: every live (batch, head, tile) item sits in exactly one CTA's list, the tiles without a valid
+    token are all on the dead list, no list is longer than its capacity and the fullest CTA is close to the mean.  The
+    persistent-CTA launch that follows the schedule gives the forward of the one-CTA-per-item launch bit for bit (and
+    the backward up to the order of the dQ reductions)."""
+    import numpy as np
+    from proteusai_b200 import _lib
+    z, h, n = 6, 4, 900
+    lengths = [900, 130, 512, 77, 0, 640]
+    q, k, v, d_out, c, m, sig = (t.cuda() for t in _inputs(z, h, n, lengths, seed=91, std=1.0))
+    gp = ga.geoattn_plan(m)
+    tiles = (n + 127) // 128
+    plan = gp.plan.cpu().numpy()
+    count = plan[4 + z:4 + 2 * z]
+    info = plan[4 + 3 * z + z * tiles:4 + 3 * z + 2 * z * tiles].reshape(z, tiles)
+    want_live = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] >= 0}
+    want_dead = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] < 0}
+    for backward in (False, True):
+        sched, bins = gp.schedule(h, backward)
+        assert sched is not None and bins > 0
+        sw = sched.cpu().numpy()
+        cap = int(sw[4])
+        assert list(sw[:4]) == [bins, h, z, n] and sw[5] == len(want_dead) and sw[6] == len(want_live)
+        cnt = sw[8:8 + bins]
+        lists = sw[8 + bins:8 + bins + bins * cap].reshape(bins, cap)
+        assert cnt.max() <= cap
+        got = [int(x) for b in range(bins) for x in lists[b, :cnt[b]]]
+        assert len(got) == len(set(got)) and set(got) == want_live
+        dead = sw[8 + bins + bins * cap:8 + bins + bins * cap + len(want_dead)]
+        assert set(int(x) for x in dead) == want_dead and len(set(dead.tolist())) == len(want_dead)
+        load = np.array([sum(count[(int(x) >> 10) // h] for x in lists[b, :cnt[b]]) for b in range(bins)])
+        assert load.max() <= max(count.max(), int(np.ceil(load.sum() / bins)) + count.max())
+    o_s, l_s = ga.geoattn_forward(q, k, v, c, sig, m)
+    grads_s = ga.geoattn_backward(q, k, v, o_s, d_out, l_s, c, sig, m)
+    try:
+        _lib.tune(ga_no_order=1)   # one CTA per item, natural order
+        o_1, l_1 = ga.geoattn_forward(q, k, v, c, sig, m)
+        grads_1 = ga.geoattn_backward(q, k, v, o_1, d_out, l_1, c, sig, m)
+    finally:
+        _lib.tune_reset()
+    assert torch.equal(o_s, o_1) and torch.equal(l_s, l_1)
+    scale = max(g.abs().max().item() for g in grads_1[:3])
+    for a, b in zip(grads_s[:3], grads_1[:3]):
+        assert (a - b).abs().max().item() < 1e-4 * scale
+    assert torch.allclose(grads_s[3], grads_1[3], rtol=1e-3, atol=1e-4)
+    # a schedule made for another head count is not followed: nothing runs, the status word says so, the next call is fine
+    q2, k2, v2 = (torch.cat([t, t], dim=1) for t in (q, k, v))
+    sig2 = torch.cat([sig, sig])
+    gp.schedules[(2 * h, False)] = gp.schedules[(h, False)]
+    ga.geoattn_forward(q2, k2, v2, c, sig2, m)
+    with pytest.raises(RuntimeError, match="status -2"):
+        _lib.device_status()
+    del gp.schedules[(2 * h, False)]
+    o_2, _ = ga.geoattn_forward(q2, k2, v2, c, sig2, m)
+    assert torch.equal(o_2[:, :h], o_s) and torch.equal(o_2[:, h:], o_s)
+    # a large batch has many items per CTA slot and runs without a schedule
+    big = torch.zeros(64, 1024, dtype=torch.bool, device="cuda")
+    assert ga.geoattn_plan(big).schedule(8, False) == (None, 0)
+    _lib.device_status()
+
+
 def test_query_row_ranges_shard_forward_and_backward(ga):
     """Sharding by query blocks: the forward on row ranges reproduces the full call bit for bit; in the backward dQ rows
     come from their own shard and dK, dV, d_sigma are partial sums that add up to the full gradients."""
