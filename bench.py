@@ -242,7 +242,9 @@ def bench_geoattn(dev, world, rank, steps, dist, cpu_baseline=False):
     res = {"metric": "geo-attn fwd+bwd TFLOP/s (valid pairs)", "value": valid_flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
            "padded_tflops": padded_flop / (ms * 1e-3) / 1e12, "ms_per_step": ms, "fwd_ms": fwd_ms, "dtype": "bf16",
            "config": {"workload": "geometric attention fwd+bwd, B=8, H=8, N=1024, d_head=64, lengths U{256..1024}, seed 1003",
-                      "sharding": f"(batch, head) pairs over {world} rank(s)"},
+                      "sharding": f"(batch, head) pairs over {world} rank(s)",
+                      "launch": ("persistent CTAs on the balanced schedule of the mask (made once, outside the timed region)" if world == 1
+                                 else "one CTA per work item, samples longest first (a shard of the pairs runs without a schedule)")},
            "roofline": {"bound": "tensor", "achieved": valid_flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                         "frac": valid_flop / (ms * 1e-3) / 1e12 / peak, "peak_source": src, "traffic": None,
                         "note": "compute-bound kernels: DRAM traffic (about 0.1 GB per step) is not the limiter"},

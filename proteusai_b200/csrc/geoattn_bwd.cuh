@@ -614,6 +614,9 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
             if (!(ok = wait_w(&sm.bar_sp[sub], (uint32_t)(t & 1)))) break;  // S^T, dP^T(u) have landed in TMEM
             tc_fence_after();
             const int col0 = sub * GA_SUB + grp * 16;  // first query column (inside the tile) of this thread's 16
+            uint32_t sv[16], dpv[16];
+            tmem_ld16(tm_s + sub * GA_SUB + lane_base + grp * 16, sv);  // (in flight under the far test)
+            tmem_ld16(tm_dp + sub * GA_SUB + lane_base + grp * 16, dpv);
             bool far;
             {  // the thread's group of 16 queries against this warp's keys
                 const float4 sp = rw.sph[col0 / 16];
@@ -622,9 +625,6 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
                 far = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
             }
             const uint32_t qbits = (rw.qbits[col0 / 32] >> (col0 & 16)) & 0xffffu;
-            uint32_t sv[16], dpv[16];
-            tmem_ld16(tm_s + sub * GA_SUB + lane_base + grp * 16, sv);
-            tmem_ld16(tm_dp + sub * GA_SUB + lane_base + grp * 16, dpv);
             tmem_wait_ld();
             tc_fence_before();
             mbar_arrive(&sm.bar_spfree[sub]);  // the stage may be overwritten with sub-tile u + 2

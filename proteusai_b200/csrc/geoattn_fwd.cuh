@@ -589,6 +589,8 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
             if (!(ok = wait_w(&sm.bar_s[sb], (uint32_t)((w >> 1) & 1)))) break;  // S(w), G(w) have landed in TMEM
             tc_fence_after();
             const GaKeyCoords &kc = sm.kc[cb];
+            uint32_t s[32], g[32];
+            tmem_ld32(tmem_s + sb * GA_UNIT + lane_base, s);  // (in flight under the far test)
             bool far[2];
 #pragma unroll
             for (int c = 0; c < 2; ++c) {  // far test of the unit's two key groups against this warp's queries (warp-uniform)
@@ -598,8 +600,6 @@ __device__ __forceinline__ void geoattn_fwd_item(GaFwdSmem &sm, const CUtensorMa
                 far[c] = sp.w < 0.f || (dx * dx + dy * dy + dz * dz > reach * reach && reach > 0.f);
             }
             const uint32_t vbits = kc.vbits[qd];
-            uint32_t s[32], g[32];
-            tmem_ld32(tmem_s + sb * GA_UNIT + lane_base, s);
             if (!(far[0] && far[1])) tmem_ld32(tmem_g + sb * GA_UNIT + lane_base, g);
             tmem_wait_ld();
             tc_fence_before();
