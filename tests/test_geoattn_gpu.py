@@ -289,28 +289,63 @@ def test_balanced_schedule_covers_every_item_once_and_changes_no_result(ga):
     z, h, n = 6, 4, 900
     lengths = [900, 130, 512, 77, 0, 640]
     q, k, v, d_out, c, m, sig = (t.cuda() for t in _inputs(z, h, n, lengths, seed=91, std=1.0))
-    gp = ga.geoattn_plan(m)
-    tiles = (n + 127) // 128
-    plan = gp.plan.cpu().numpy()
-    count = plan[4 + z:4 + 2 * z]
-    info = plan[4 + 3 * z + z * tiles:4 + 3 * z + 2 * z * tiles].reshape(z, tiles)
-    want_live = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] >= 0}
-    want_dead = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] < 0}
-    for backward in (False, True):
-        sched, bins = gp.schedule(h, backward)
-        assert sched is not None and bins > 0
-        sw = sched.cpu().numpy()
-        cap = int(sw[4])
-        assert list(sw[:4]) == [bins, h, z, n] and sw[5] == len(want_dead) and sw[6] == len(want_live)
-        cnt = sw[8:8 + bins]
-        lists = sw[8 + bins:8 + bins + bins * cap].reshape(bins, cap)
-        assert cnt.max() <= cap
-        got = [int(x) for b in range(bins) for x in lists[b, :cnt[b]]]
-        assert len(got) == len(set(got)) and set(got) == want_live
-        dead = sw[8 + bins + bins * cap:8 + bins + bins * cap + len(want_dead)]
-        assert set(int(x) for x in dead) == want_dead and len(set(dead.tolist())) == len(want_dead)
-        load = np.array([sum(count[(int(x) >> 10) // h] for x in lists[b, :cnt[b]]) for b in range(bins)])
-        assert load.max() <= max(count.max(), int(np.ceil(load.sum() / bins)) + count.max())
+    def check_schedule(mask, z, h, n):
+        gp = ga.geoattn_plan(mask)
+        tiles = (n + 127) // 128
+        plan = gp.plan.cpu().numpy()
+        count = plan[4 + z:4 + 2 * z]
+        info = plan[4 + 3 * z + z * tiles:4 + 3 * z + 2 * z * tiles].reshape(z, tiles)
+        want_live = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] >= 0}
+        want_dead = {((b * h + hh) << 10) | t for b in range(z) for hh in range(h) for t in range(tiles) if info[b, t] < 0}
+        for backward in (False, True):
+            sched, bins = gp.schedule(h, backward)
+            assert sched is not None and bins > 0
+            sw = sched.cpu().numpy()
+            cap = int(sw[4])
+            assert list(sw[:4]) == [bins, h, z, n] and sw[5] == len(want_dead) and sw[6] == len(want_live)
+            cnt = sw[8:8 + bins]
+            lists = sw[8 + bins:8 + bins + bins * cap].reshape(bins, cap)
+            assert cnt.max() <= cap
+            got = [int(x) for b in range(bins) for x in lists[b, :cnt[b]]]
+            assert len(got) == len(set(got)) and set(got) == want_live
+            dead = sw[8 + bins + bins * cap:8 + bins + bins * cap + len(want_dead)]
+            assert set(int(x) for x in dead) == want_dead and len(set(dead.tolist())) == len(want_dead)
+            load = np.array([sum(count[(int(x) >> 10) // h] for x in lists[b, :cnt[b]]) for b in range(bins)])
+            assert load.max() <= max(count.max(), int(np.ceil(load.sum() / bins)) + count.max())
+            # the packing itself, restated: first fit, longest first, into bins of capacity C; C bisected to the smallest that fits
+            tile_cost, item_cost = 8, (12 if backward else 5)
+            nb = bins if backward else bins // 2   # the forward packs per SM and deals each SM's items to two CTAs
+            costs = sorted((int(count[b]) * tile_cost + item_cost for b in range(z) for _ in range(int(count[b]) * h) if count[b] > 0), reverse=True)
+
+            def fits(cap_c):
+                loads = [0] * nb
+                for cst in costs:
+                    for i in range(nb):
+                        if loads[i] + cst <= cap_c:
+                            loads[i] += cst
+                            break
+                    else:
+                        return None
+                return loads
+            lo = max(max(costs), -(-sum(costs) // nb))
+            hi_c = 2 * lo + 1
+            while lo < hi_c:
+                mid = (lo + hi_c) // 2
+                if fits(mid) is None:
+                    lo = mid + 1
+                else:
+                    hi_c = mid
+            assert sw[7] == hi_c
+            got_cost = np.array([sum(int(count[(int(x) >> 10) // h]) * tile_cost + item_cost for x in lists[b, :cnt[b]]) for b in range(bins)])
+            per_bin = got_cost if backward else got_cost[:nb] + got_cost[nb:2 * nb]
+            assert sorted(per_bin.tolist()) == sorted(fits(hi_c))
+        return gp
+
+    gp = check_schedule(m, z, h, n)
+    m8 = torch.ones(8, 1024, dtype=torch.bool)
+    for b, length in enumerate([1024, 1000, 900, 770, 650, 512, 400, 300]):
+        m8[b, :length] = False
+    check_schedule(m8.cuda(), 8, 8, 1024)   # several items per CTA: the packing has work to do
     o_s, l_s = ga.geoattn_forward(q, k, v, c, sig, m)
     grads_s = ga.geoattn_backward(q, k, v, o_s, d_out, l_s, c, sig, m)
     try:
