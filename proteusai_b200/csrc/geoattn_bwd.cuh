@@ -652,13 +652,9 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
             }
         }
 
-        // ---- epilogue: the last dQ tile; dV, dK rows of this key tile; dsigma ------------------------------
-        if (ok) ok = wait_w(&sm.bar_dq, (uint32_t)((nt - 1) & 1));
-        if (ok) {
-            tc_fence_after();
-            read_dq(nt - 1);
-            ok = wait_w(&sm.bar_vk, (uint32_t)((nsub - 1) & 1));  // the last dV / dK accumulation has completed
-        }
+        // ---- epilogue: dV, dK rows of this key tile (their last accumulation was issued before the last dQ MMAs, which run
+        // underneath these stores); the last dQ tile; dsigma ---------------------------------------------------------
+        if (ok) ok = wait_w(&sm.bar_vk, (uint32_t)((nsub - 1) & 1));  // the last dV / dK accumulation has completed
         if (ok) {
             tc_fence_after();
             uint32_t a[16], b[16];
@@ -670,6 +666,11 @@ __device__ __forceinline__ void geoattn_bwd_item(GaBwdSmem &sm, const CUtensorMa
             const size_t off = ((size_t)zh * N + row0) * GA_D + grp * 16;
             ga_warp_rows_out<false>(sm.stage[warp], a, lane, p.dv + off, N - row0);
             ga_warp_rows_out<false>(sm.stage[warp], b, lane, p.dk + off, N - row0);
+            ok = wait_w(&sm.bar_dq, (uint32_t)((nt - 1) & 1));
+        }
+        if (ok) {
+            tc_fence_after();
+            read_dq(nt - 1);
         }
         float d0, d1, b0, b1;
         f2_unpack(dsig2, d0, d1);
