@@ -247,7 +247,13 @@ def bench_geoattn(dev, world, rank, steps, dist, cpu_baseline=False):
                                  else "one CTA per work item, samples longest first (a shard of the pairs runs without a schedule)")},
            "roofline": {"bound": "tensor", "achieved": valid_flop / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                         "frac": valid_flop / (ms * 1e-3) / 1e12 / peak, "peak_source": src, "traffic": None,
-                        "note": "compute-bound kernels: DRAM traffic (about 0.1 GB per step) is not the limiter"},
+                        "note": "compute-bound kernels: DRAM traffic (about 0.1 GB per step) is not the limiter",
+                        # every valid pair costs two ex2 in the forward and three in the backward on the SFU (16 results per
+                        # clock per SM): the floor of the step if nothing else took time (far key groups skip some of them)
+                        "sfu_floor_ms": 5.0 * GA_H * float((lengths.astype(np.float64) ** 2).sum()) /
+                                        (16.0 * torch.cuda.get_device_properties(dev).multi_processor_count * 1.965e9) * 1e3 / world,
+                        "frac_of_sfu_floor": 5.0 * GA_H * float((lengths.astype(np.float64) ** 2).sum()) /
+                                             (16.0 * torch.cuda.get_device_properties(dev).multi_processor_count * 1.965e9) * 1e3 / world / ms},
            "gather_check_max_abs": gather_check,
            "gpu_launches": 3 * steps}
     if cpu_baseline and rank == 0:
