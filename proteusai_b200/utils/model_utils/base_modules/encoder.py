@@ -46,11 +46,22 @@ class GeoAttention(nn.Module):
             setattr(self, f"{name}_bias", nn.Parameter(torch.zeros(heads, self.d_k)))
         self.out_proj = nn.Linear(d_model, d_model, bias=False)
 
+    def _cached(self, name, param, build):
+        """``build()`` with gradients recorded; without, its value is kept until the parameter changes (version counter)."""
+        if torch.is_grad_enabled() and param.requires_grad:
+            return build()
+        stamp = (param.data_ptr(), param._version)
+        hit = self._packed.get(name)
+        if hit is None or hit[0] != stamp:
+            hit = (stamp, build())
+            self._packed[name] = hit
+        return hit[1]
+
     def get_spreads(self):
-        return self.min_spread + torch.exp(self.spread_weights)
+        return self._cached("spreads", self.spread_weights, lambda: self.min_spread + torch.exp(self.spread_weights))
 
     def get_betas(self):
-        return torch.exp(self.beta_weights)
+        return self._cached("betas", self.beta_weights, lambda: torch.exp(self.beta_weights))
 
     def _packed_weights(self, names, dtype):
         """``[D, S*H*dk]`` weight and ``[S*H*dk]`` bias of the fused projection for the weight sets ``names`` (``"q"``,
