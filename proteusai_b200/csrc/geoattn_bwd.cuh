@@ -48,7 +48,7 @@ constexpr int GA_SUB = 64;  // queries per sub-tile (two sub-tiles per 128-row q
 struct GaQueryRows {                  // per-query inputs of one query tile, two queries per entry
     float4 qa[GA_BM / 2];             // centred coordinates {x_i, x_i+1, y_i, y_i+1}
     float4 qc[GA_BM / 2];             // {z_i, z_i+1, |q_i|^2, |q_i+1|^2}
-    float4 ld[GA_BM / 2];             // {L_i, L_i+1, D_i, D_i+1}: log-sum-exp in base-2 units (+inf: padded query or row
+    float4 ld[GA_BM / 2];             // {-L_i, -L_i+1, D_i, D_i+1}: minus the log-sum-exp in base-2 units (-inf: padded query or row
                                       // without a valid pair) and D
     uint32_t qbits[GA_BM / 32];       // bit i of word u: query 32 u + i is valid
     float4 sph[GA_BM / 16];           // bounding sphere of each group of 16 queries (radius < 0: no valid query)
@@ -167,7 +167,7 @@ __device__ __forceinline__ void ga_stage_row(GaQueryRows &rw, int i, bool ok, fl
     qa[2 + (i & 1)] = y;
     qc[i & 1] = z;
     qc[2 + (i & 1)] = x * x + y * y + z * z;
-    ld[i & 1] = l2;
+    ld[i & 1] = -l2;  // (the exponent of P is SR - L: stored with its sign, one instruction less per pair)
     ld[2 + (i & 1)] = dsum;
     const uint32_t bits = __ballot_sync(0xffffffffu, ok);
     if ((i & 31) == 0) rw.qbits[i >> 5] = bits;
@@ -240,14 +240,14 @@ __device__ __forceinline__ void ga_bwd_chunk(uint32_t (&sv)[16], uint32_t (&dpv)
         const float4 l = rw.ld[p0 + e];  // {L pair, D pair}
         f2_t x;
         if (FORM == 0) {
-            x = f2_fma(t2, onep, f2_pack(-l.x, -l.y));
+            x = f2_fma(t2, onep, f2_pack(l.x, l.y));
         } else {
             float t0, t1, r0, r1;
             f2_unpack(t2, t0, t1);
             f2_unpack(rb, r0, r1);  // 0 for a far group
             const float s0 = fmaf(fm.beta * fmaf(r0, fm.rn_a, fm.rn_b), fabsf(t0), t0);
             const float s1 = fmaf(fm.beta * fmaf(r1, fm.rn_a, fm.rn_b), fabsf(t1), t1);
-            x = f2_sub(f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY),
+            x = f2_add(f2_pack((r0 >= fm.rmin && r0 <= fm.rmax) ? s0 : -INFINITY, (r1 >= fm.rmin && r1 <= fm.rmax) ? s1 : -INFINITY),
                        f2_pack(l.x, l.y));
         }
         float p0v, p1v;
