@@ -271,8 +271,9 @@ int pai_geoattn_schedule(const void *plan, int Z, int N, int H, int bins, int ba
     if (int e = require_sm100()) return e;
     // cost of a work item in eighths of a (128 x 128) tile: the tiles it visits plus its set-up and epilogue
     // (measured: set-up, first loads and epilogue of an item take as long as 1.5 tiles in the backward, 0.6 in the forward)
+    // (the forward runs two CTAs per SM and packs per SM; a single bin has no second CTA to pair with)
     pai::geoattn_schedule_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const int *)plan, (int *)sched, Z, N, H, bins, 8,
-                                                                       backward ? 12 : 5, backward ? 0 : 1);
+                                                                       backward ? 12 : 5, (backward || bins < 2) ? 0 : 1);
     return (int)cudaPeekAtLastError();
 }
 

@@ -369,6 +369,24 @@ def test_balanced_schedule_covers_every_item_once_and_changes_no_result(ga):
     del gp.schedules[(2 * h, False)]
     o_2, _ = ga.geoattn_forward(q2, k2, v2, c, sig2, m)
     assert torch.equal(o_2[:, :h], o_s) and torch.equal(o_2[:, h:], o_s)
+    # any number of persistent CTAs may follow a schedule: one (no second CTA to pair with) and an odd count
+    lib = _lib.lib()
+    for bins in (1, 3):
+        nbytes = lib.pai_geoattn_schedule_bytes(z, n, h, bins)
+        small = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device="cuda")
+        _lib.check(lib.pai_geoattn_schedule(_lib.ptr(gp.plan), z, n, h, bins, 0, _lib.ptr(small), nbytes, _lib.current_stream()),
+                   "pai_geoattn_schedule")
+        sw = small.cpu().numpy()
+        cap = int(sw[4])
+        assert int(sw[0]) == bins and int(sw[8:8 + bins].sum()) == int(sw[6]) and int(sw[8:8 + bins].max()) <= cap
+        keep = gp.schedules[(h, False)]
+        gp.schedules[(h, False)] = (small, bins)
+        try:
+            o_b, l_b = ga.geoattn_forward(q, k, v, c, sig, m)
+        finally:
+            gp.schedules[(h, False)] = keep
+        _lib.device_status()
+        assert torch.equal(o_b, o_s) and torch.equal(l_b, l_s)
     # a large batch has many items per CTA slot and runs without a schedule
     big = torch.zeros(64, 1024, dtype=torch.bool, device="cuda")
     assert ga.geoattn_plan(big).schedule(8, False) == (None, 0)
